@@ -1,0 +1,241 @@
+/*
+ * shrike_b200 — C ABI of the B200 (sm_100a) implementation of Shrike's
+ * quantised routed-expert MoE feed-forward.
+ *
+ * This header is what the reference's `ShrikeKernelsC` SwiftPM target would
+ * include in place of the Metal encode calls of `sources/Shrike/Kernels/MoE`
+ * and `sources/Shrike/Kernels/Prefill/MoE`. Conventions follow the reference's
+ * own C interface (sources/ShrikeKernelsC/include/shrike_expert_io.h:33-72):
+ * opaque handles, `create` hands the handle back through an out-pointer, every
+ * call returns an int (0 = success, otherwise an errno-style code), nothing
+ * throws or aborts across the boundary. All data pointers are plain device
+ * pointers unless a parameter name ends in `_host`; `stream` is a
+ * `cudaStream_t` passed as `void*` (NULL = the legacy default stream).
+ * Calls only enqueue work; device-side failures surface as a non-zero
+ * `shrike_moe_status` after the stream is synchronised.
+ *
+ * Threading: one host thread per handle at a time (the reference's runner is
+ * single-owner, RealForwardRunner.swift:95-101). One handle per GPU.
+ */
+#ifndef SHRIKE_B200_H
+#define SHRIKE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SHRIKE_MAX_TOP_K 8u          /* MoE.maxStreamedExperts, MoE.swift:42 */
+#define SHRIKE_MAX_EXPERTS 256u      /* MoE.swift:263 */
+#define SHRIKE_MAX_POOL_CHUNKS 8u    /* PoolBases.base[8], moe.metal:297-300 */
+#define SHRIKE_MAX_DECODE_TOKENS 64u /* largest query_count of the decode entry points */
+#define SHRIKE_SLOT_MISS 0xffffffffu /* resolved_slots sentinel, moe.metal:146 */
+
+enum { SHRIKE_DTYPE_BF16 = 0, SHRIKE_DTYPE_FP16 = 1, SHRIKE_DTYPE_FP32 = 2 };
+enum { SHRIKE_ACT_SILU = 0, SHRIKE_ACT_GELU_TANH = 1, SHRIKE_ACT_CLAMPED_SWIGLU = 2 };
+enum { SHRIKE_ROUTER_SOFTMAX = 0, SHRIKE_ROUTER_SIGMOID = 1 };
+enum { SHRIKE_IO_PENDING = 0, SHRIKE_IO_READY = 1, SHRIKE_IO_FAILED = 2 };
+
+enum {
+    SHRIKE_OK = 0,
+    SHRIKE_EINVAL = 22,     /* bad argument or unsupported shape */
+    SHRIKE_ENOMEM = 12,     /* device or host allocation failed */
+    SHRIKE_ERANGE = 34,     /* slot / expert / token count out of range */
+    SHRIKE_EIO = 5,         /* CUDA runtime error; text in shrike_last_error */
+    SHRIKE_ETIMEDOUT = 110  /* a bounded device-side wait gave up */
+};
+
+/* Replaces the arguments of `MoE.init` (MoE.swift:94-106) plus the dtypes the
+ * Metal build fixes at compile time. */
+typedef struct shrike_moe_config {
+    uint32_t d;                 /* hidden size, multiple of 64 */
+    uint32_t f;                 /* routed expert intermediate size, multiple of 64 */
+    uint32_t num_experts;       /* <= 256 */
+    uint32_t top_k;             /* 1..8 */
+    uint32_t weight_bits;       /* 4 or 8 (routedWeightBits) */
+    uint32_t group_size;        /* 64 (the reference's only value) or 32 */
+    uint32_t meta_dtype;        /* dtype of scales and zero-point biases: BF16 (reference) or FP16 */
+    uint32_t act_dtype;         /* dtype of x, y, hidden: BF16, FP16 or FP32 */
+    uint32_t activation;        /* SHRIKE_ACT_* (siluActivation / clampedSwiGLU) */
+    uint32_t expert_bias;       /* expertAdditiveBiases */
+    uint32_t router_kind;       /* SHRIKE_ROUTER_* (sigmoidRouterScores) */
+    float    routed_scaling;    /* routedScalingFactor */
+    uint32_t router_weight_bits;/* 0 = fp32 rows, 4 or 8 = affine g64 bf16 (routerWeightBits) */
+    uint32_t round_route_weights_f16; /* round route weights through fp16 as the shader does */
+    uint32_t has_shared;        /* a shared expert is passed to the moe calls */
+    uint32_t shared_gated;      /* shared output is multiplied by sigmoid(gate . x) */
+    uint32_t shared_f;          /* shared expert intermediate size */
+    uint32_t max_tokens;        /* largest query_count of any call; sizes the workspace */
+} shrike_moe_config;
+
+/* Field-for-field `MoEExpertOffsets` (MoE.swift:4-39) = `ExpertOffsets`
+ * (moe.metal:240-255): byte offsets inside one packed expert block. */
+typedef struct shrike_expert_offsets {
+    uint32_t gate_w, gate_s, gate_b;
+    uint32_t up_w, up_s, up_b;
+    uint32_t down_w, down_s, down_b;
+    uint32_t gate_ab, up_ab, down_ab;
+} shrike_expert_offsets;
+
+/* Operands of `MoE.encodeRouter` (MoE.swift:249-261). `weights` is fp32
+ * [num_experts x d] when router_weight_bits == 0, else packed affine rows with
+ * bf16 `scales`/`biases` [num_experts x d/64]. The three bf16 vectors may be
+ * NULL (ones / ones / zeros). `shared_gate` is the shared expert's scalar gate
+ * row, fp32 [d], or NULL. */
+typedef struct shrike_router_operands {
+    const void*     weights;
+    const uint16_t* scales;
+    const uint16_t* biases;
+    const uint16_t* effective_scale;   /* bf16 [d] */
+    const uint16_t* per_expert_scale;  /* bf16 [num_experts] */
+    const uint16_t* logit_bias;        /* bf16 [num_experts] */
+    const float*    shared_gate;       /* fp32 [d] */
+} shrike_router_operands;
+
+/* The resident shared expert (SharedExpertRuntime, SharedExpertInt4.swift:251-342):
+ * one packed block in the routed experts' format with its own offsets. */
+typedef struct shrike_shared_expert {
+    const void*           block;
+    shrike_expert_offsets offsets;
+} shrike_shared_expert;
+
+typedef struct shrike_moe shrike_moe;     /* replaces `final class MoE` + PrefillGroupedRoutedMoE */
+typedef struct shrike_pool shrike_pool;   /* replaces ExpertCellArena (ExpertCellArena.swift:16-132) */
+
+/* ---- lifetime ---------------------------------------------------------- */
+
+/* MoE.init (MoE.swift:94-143). Allocates the workspace for max_tokens; no
+ * later call allocates. */
+int shrike_moe_create(const shrike_moe_config* config, int device, shrike_moe** out);
+void shrike_moe_destroy(shrike_moe* moe);
+
+/* Text of the last failure on this handle (or of the last failed create when
+ * moe is NULL). Never NULL. */
+const char* shrike_last_error(const shrike_moe* moe);
+
+/* Synchronises `stream`, then returns SHRIKE_OK, SHRIKE_ETIMEDOUT when a
+ * kernel's bounded wait gave up, or SHRIKE_EIO for a CUDA error
+ * (the reference inspects commandBuffer.error, RealForwardRunner.swift:5360-5363). */
+int shrike_moe_status(shrike_moe* moe, void* stream);
+
+/* CPUExpertFFN.Offsets (CPUExpertFFN.swift:34-61) / Model.routedExpertOffsets
+ * (ModelExpertIO.swift:69-94): offsets and unpadded size of one block. */
+int shrike_expert_offsets_make(const shrike_moe_config* config, int shared,
+                               shrike_expert_offsets* out, uint64_t* block_bytes);
+
+/* ---- HBM slot pool ------------------------------------------------------ */
+
+/* ExpertCellArena.init: `cells` cells of `cell_stride` bytes (multiple of 256)
+ * in `chunks` (1..8) device allocations. */
+int shrike_pool_create(shrike_moe* moe, uint32_t cells, uint64_t cell_stride, uint32_t chunks,
+                       shrike_pool** out);
+void shrike_pool_destroy(shrike_pool* pool);
+/* Copies one unmodified packed expert block from host memory into a cell. */
+int shrike_pool_upload(shrike_pool* pool, uint32_t cell, const void* block_host, uint64_t bytes,
+                       void* stream);
+int shrike_pool_download(shrike_pool* pool, uint32_t cell, void* block_host, uint64_t bytes,
+                         void* stream);
+/* pool_cell_base (moe.metal:302-305): device address of a cell. */
+int shrike_pool_cell_address(const shrike_pool* pool, uint32_t cell, void** out);
+/* Benchmark/test utility: fills `count` cells starting at `first_cell` with
+ * seeded synthetic blocks of experts first_expert.. of `layer` (counter-mode
+ * SplitMix64; nibbles uniform, scale U(0.5,1.5)*0.02/7.5, bias -8*scale). */
+int shrike_pool_fill_synthetic(shrike_moe* moe, shrike_pool* pool, uint32_t first_cell,
+                               uint32_t count, uint64_t seed, uint32_t layer,
+                               uint32_t first_expert, int shared, void* stream);
+
+/* ---- residency table ----------------------------------------------------- */
+
+/* ExpertResidencyEntry (ExpertResidencyTable.swift:4-19): one u64 per expert,
+ * slot in the low 32 bits, state in the high 32 (2 = resident). `table` is a
+ * device array of `layers * num_experts` words owned by the handle. */
+int shrike_residency_create(shrike_moe* moe, uint32_t layers, uint64_t** table_out);
+int shrike_residency_set(shrike_moe* moe, uint32_t layer, uint32_t expert, uint32_t slot,
+                         uint32_t state, void* stream);
+/* Marks experts [0, num_experts) of `layer` resident in cells first_cell.. */
+int shrike_residency_set_layer_identity(shrike_moe* moe, uint32_t layer, uint32_t first_cell,
+                                        void* stream);
+
+/* ---- the path ------------------------------------------------------------ */
+
+/* MoE.encodeRouter (MoE.swift:249-316: router_gemv_r4 + router_topk_select_k8,
+ * moe.metal:324-582) and PrefillRouter.encodeBlock (PrefillRouter.swift:75-152)
+ * for `query_count` rows of `hidden` spaced `hidden_stride_elements` apart.
+ * Writes ids u32 [query_count x top_k], weights fp32 [query_count x top_k] and,
+ * when operands->shared_gate is set, sigmoid(gate . x) fp32 [query_count]. */
+int shrike_encode_router(shrike_moe* moe, void* stream, const shrike_router_operands* operands,
+                         const void* hidden, uint32_t query_count,
+                         uint32_t hidden_stride_elements, uint32_t* out_indices,
+                         float* out_weights, float* out_shared_gate);
+
+/* MoE.encodeResidencyClassification (MoE.swift:552-613;
+ * moe_classify_expert_residency_spec, moe.metal:194-231) for query_count rows.
+ * resolved_slots u32 [query_count x top_k]; counts[0] = hits, counts[1] =
+ * misses; miss_positions / miss_experts hold (row*top_k+rank, expert) per miss
+ * in row order (either may be NULL). */
+int shrike_encode_residency_classification(shrike_moe* moe, void* stream,
+                                           const uint32_t* topk_indices,
+                                           const uint64_t* residency_table_row,
+                                           uint32_t query_count, uint32_t* resolved_slots,
+                                           uint32_t* counts, uint32_t* miss_positions,
+                                           uint32_t* miss_experts);
+
+/* Decode, query_count <= SHRIKE_MAX_DECODE_TOKENS rows. One call stands for
+ * encodeSharedExpertWork (RealForwardRunner.swift:5436-5497),
+ * MoE.encodeSpecPhase1U16Load (MoE.swift:906-948) and
+ * MoE.encodeSpecPhase2Reduce (MoE.swift:992-1049):
+ *   y[t] = sg[t] * shared(x[t]) + sum_k w[t,k] * expert(slot[t,k])(x[t]);
+ *   hidden[t] += y[t]   (hidden may be NULL)
+ * A row whose slot is SHRIKE_SLOT_MISS contributes nothing. When io_status is
+ * given and *io_status is neither READY nor 3, y is the shared term alone
+ * (moe.metal:36-39, 918-921). shared may be NULL when has_shared == 0;
+ * shared_gate is the router call's out_shared_gate (NULL = ungated). */
+int shrike_encode_moe_decode(shrike_moe* moe, void* stream, const shrike_pool* pool,
+                             const shrike_expert_offsets* routed_offsets,
+                             const uint32_t* resolved_slots, const float* routing_weights,
+                             const void* x, uint32_t query_count,
+                             const shrike_shared_expert* shared, const float* shared_gate,
+                             const uint32_t* io_status, void* y, void* hidden);
+
+/* Prefill, any query_count <= max_tokens. Stands for buildPrefillRoutes
+ * (RealForwardRunner.swift:4305), encodeGroupedExpertGEMMs
+ * (PrefillGroupedRoutedMoE.swift:925-1035), PrefillSharedExpert.encodeChunk
+ * (PrefillSharedExpert.swift:105-161), encodeReduceTokenMajor (PrefillMoE.swift:11-20)
+ * and the two residual adds (RealForwardRunner.swift:4658-4665). Same
+ * arithmetic contract as the decode call; rows are grouped by topk_indices
+ * (the expert ids), and every pair of one expert must resolve to one cell. */
+int shrike_encode_moe_prefill(shrike_moe* moe, void* stream, const shrike_pool* pool,
+                              const shrike_expert_offsets* routed_offsets,
+                              const uint32_t* topk_indices, const uint32_t* resolved_slots,
+                              const float* routing_weights,
+                              const void* x, uint32_t query_count,
+                              const shrike_shared_expert* shared, const float* shared_gate,
+                              void* y, void* hidden);
+
+/* PrefillMoEGrouping.groupTokenExpertPairs (PrefillMoEGrouping.swift:269-370)
+ * on the device: sorts the query_count*top_k (token, expert, rank, weight bits)
+ * pairs by (expert, token, rank). sorted_pairs: 4 u32 per pair
+ * (PrefillTokenExpertPair, PrefillRouter.swift:5-28); offsets/counts u32
+ * [num_experts] (offset 0xffffffff for an unrouted expert). */
+int shrike_encode_group_pairs(shrike_moe* moe, void* stream, const uint32_t* topk_indices,
+                              const float* routing_weights, uint32_t query_count,
+                              uint32_t* sorted_pairs, uint32_t* per_expert_offsets,
+                              uint32_t* per_expert_counts);
+
+/* End-to-end convenience for hosts that keep activations in host memory:
+ * copies x_host in, runs router -> classification -> decode/prefill for one
+ * layer, copies y (and hidden) back, and synchronises. */
+int shrike_moe_layer_forward_host(shrike_moe* moe, void* stream, const shrike_pool* pool,
+                                  const shrike_expert_offsets* routed_offsets,
+                                  const uint64_t* residency_table_row,
+                                  const shrike_router_operands* router,
+                                  const shrike_shared_expert* shared,
+                                  const void* x_host, uint32_t query_count, void* y_host,
+                                  uint32_t* ids_host, float* weights_host);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SHRIKE_B200_H */

@@ -1,0 +1,501 @@
+// The C ABI: argument validation, handle lifetime, launch sequencing.
+// No entry point below allocates after shrike_moe_create / shrike_pool_create /
+// shrike_residency_create.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <new>
+
+#include "internal.h"
+
+using namespace shrike;
+
+namespace {
+
+thread_local std::string g_create_error;
+
+int fail(shrike_moe* m, int code, const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    if (m) m->err = buf; else g_create_error = buf;
+    return code;
+}
+
+int cuda_fail(shrike_moe* m, cudaError_t e, const char* what) {
+    return fail(m, SHRIKE_EIO, "%s: %s", what, cudaGetErrorString(e));
+}
+
+#define CU(call)                                                  \
+    do {                                                          \
+        cudaError_t e_ = (call);                                  \
+        if (e_ != cudaSuccess) return cuda_fail(m, e_, #call);    \
+    } while (0)
+
+bool valid_config(const shrike_moe_config& c, std::string& why) {
+    auto bad = [&](const char* s) { why = s; return false; };
+    if (c.d == 0 || c.d % 64 != 0 || c.d > 2944) return bad("d must be a multiple of 64, at most 2944");
+    if (c.f == 0 || c.f % 64 != 0) return bad("f must be a multiple of 64");
+    if (c.num_experts == 0 || c.num_experts > SHRIKE_MAX_EXPERTS) return bad("num_experts must be 1..256");
+    if (c.top_k == 0 || c.top_k > SHRIKE_MAX_TOP_K || c.top_k > c.num_experts) return bad("top_k must be 1..8 and <= num_experts");
+    if (c.weight_bits != 4 && c.weight_bits != 8) return bad("weight_bits must be 4 or 8");
+    if (c.group_size != 32 && c.group_size != 64) return bad("group_size must be 32 or 64");
+    if (c.meta_dtype > SHRIKE_DTYPE_FP16) return bad("meta_dtype must be BF16 or FP16");
+    if (c.act_dtype > SHRIKE_DTYPE_FP32) return bad("act_dtype must be BF16, FP16 or FP32");
+    if (c.activation > SHRIKE_ACT_CLAMPED_SWIGLU) return bad("unknown activation");
+    if (c.router_kind > SHRIKE_ROUTER_SIGMOID) return bad("unknown router_kind");
+    if (c.router_weight_bits != 0 && c.router_weight_bits != 4 && c.router_weight_bits != 8) return bad("router_weight_bits must be 0, 4 or 8");
+    if (c.has_shared && (c.shared_f == 0 || c.shared_f % 64 != 0)) return bad("shared_f must be a multiple of 64");
+    if (c.shared_gated && !c.has_shared) return bad("shared_gated needs has_shared");
+    if (c.max_tokens == 0 || c.max_tokens > 65536) return bad("max_tokens must be 1..65536");
+    return true;
+}
+
+void make_offsets(const shrike_moe_config& c, bool shared, shrike_expert_offsets& o, uint64_t& bytes) {
+    const uint32_t f = shared ? c.shared_f : c.f;
+    const uint32_t rows[3] = {f, f, c.d}, cols[3] = {c.d, c.d, f};
+    uint32_t w[3], s[3], b[3], ab[3];
+    uint64_t cur = 0;
+    for (int p = 0; p < 3; ++p) {
+        const uint64_t wb = (uint64_t)rows[p] * (cols[p] * c.weight_bits / 8);
+        const uint64_t mb = (uint64_t)rows[p] * (cols[p] / c.group_size) * 2;
+        w[p] = (uint32_t)cur; cur += wb;
+        s[p] = (uint32_t)cur; cur += mb;
+        b[p] = (uint32_t)cur; cur += mb;
+        if (c.expert_bias) { ab[p] = (uint32_t)cur; cur += rows[p] * 2; } else ab[p] = 0;
+    }
+    o.gate_w = w[0]; o.gate_s = s[0]; o.gate_b = b[0]; o.gate_ab = ab[0];
+    o.up_w = w[1]; o.up_s = s[1]; o.up_b = b[1]; o.up_ab = ab[1];
+    o.down_w = w[2]; o.down_s = s[2]; o.down_b = b[2]; o.down_ab = ab[2];
+    bytes = cur;
+}
+
+bool offsets_aligned(const shrike_expert_offsets& o) {
+    const uint32_t* p = &o.gate_w;
+    for (int i = 0; i < 12; ++i)
+        if (p[i] % 16 != 0) return false;
+    return true;
+}
+
+uint32_t max_instances(const shrike_moe_config& c, uint32_t T) {
+    const uint32_t pairs = T * c.top_k;
+    uint32_t routed = c.num_experts + pairs / 8;
+    if (routed > pairs) routed = pairs;
+    return routed + (c.has_shared ? (T + 7) / 8 : 0);
+}
+
+template <typename P>
+cudaError_t dev_alloc(P** p, size_t bytes) {
+    return cudaMalloc((void**)p, bytes ? bytes : 16);
+}
+
+void free_workspace(Workspace& w) {
+    void* ptrs[] = {w.logits, w.xh, w.acts, w.acts_shared, w.sorted, w.inst, w.n_inst, w.status, w.block_hist,
+                    w.expert_offsets, w.expert_counts, w.slot_of_expert, w.partials, w.x_dev, w.y_dev,
+                    w.ids_dev, w.w_dev, w.gate_dev, w.slots_dev, w.counts_dev};
+    for (void* p : ptrs)
+        if (p) cudaFree(p);
+    w = Workspace();
+}
+
+int fill_expert_args(shrike_moe* m, const shrike_pool* pool, const shrike_expert_offsets* ro,
+                     const shrike_shared_expert* shared, const float* weights, const float* shared_gate,
+                     ExpertArgs& a) {
+    const shrike_moe_config& c = m->cfg;
+    if (!pool || !ro) return fail(m, SHRIKE_EINVAL, "pool and routed_offsets are required");
+    if (!offsets_aligned(*ro)) return fail(m, SHRIKE_EINVAL, "routed offsets must be multiples of 16 bytes");
+    if (c.has_shared) {
+        if (!shared || !shared->block) return fail(m, SHRIKE_EINVAL, "this handle was created with a shared expert; pass it");
+        if (!offsets_aligned(shared->offsets) || ((uintptr_t)shared->block & 15))
+            return fail(m, SHRIKE_EINVAL, "shared expert block and offsets must be 16-byte aligned");
+    }
+    if (shared_gate && !c.shared_gated) return fail(m, SHRIKE_EINVAL, "shared_gate given but the handle is not shared_gated");
+    if (c.shared_gated && !shared_gate) return fail(m, SHRIKE_EINVAL, "shared_gated handle needs the router's shared_gate output");
+    memset(&a, 0, sizeof a);
+    a.pool = pool->view;
+    a.routed = to_offsets3(*ro);
+    if (c.has_shared) {
+        a.shared = to_offsets3(shared->offsets);
+        a.shared_block = (const uint8_t*)shared->block;
+    }
+    a.d = c.d; a.f = c.f; a.f_shared = c.has_shared ? c.shared_f : 0; a.top_k = c.top_k;
+    a.activation = c.activation; a.expert_bias = c.expert_bias; a.act_dtype = c.act_dtype;
+    a.inst = m->ws.inst; a.n_inst = m->ws.n_inst; a.sorted = m->ws.sorted; a.xh = m->ws.xh;
+    a.acts = m->ws.acts; a.acts_shared = m->ws.acts_shared;
+    a.route_w = weights; a.shared_gate = shared_gate; a.status = m->ws.status;
+    return SHRIKE_OK;
+}
+
+}  // namespace
+
+namespace shrike {
+size_t act_bytes(uint32_t dt) { return dt == SHRIKE_DTYPE_FP32 ? 4 : 2; }
+}
+
+extern "C" {
+
+const char* shrike_last_error(const shrike_moe* moe) {
+    return moe ? moe->err.c_str() : g_create_error.c_str();
+}
+
+int shrike_expert_offsets_make(const shrike_moe_config* config, int shared, shrike_expert_offsets* out,
+                               uint64_t* block_bytes) {
+    std::string why;
+    if (!config || !out) return fail(nullptr, SHRIKE_EINVAL, "null argument");
+    if (!valid_config(*config, why)) return fail(nullptr, SHRIKE_EINVAL, "%s", why.c_str());
+    if (shared && !config->has_shared) return fail(nullptr, SHRIKE_EINVAL, "config has no shared expert");
+    uint64_t bytes;
+    make_offsets(*config, shared != 0, *out, bytes);
+    if (block_bytes) *block_bytes = bytes;
+    return SHRIKE_OK;
+}
+
+int shrike_moe_create(const shrike_moe_config* config, int device, shrike_moe** out) {
+    if (!config || !out) return fail(nullptr, SHRIKE_EINVAL, "null argument");
+    *out = nullptr;
+    std::string why;
+    if (!valid_config(*config, why)) return fail(nullptr, SHRIKE_EINVAL, "%s", why.c_str());
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess || count == 0)
+        return fail(nullptr, SHRIKE_EIO, "no CUDA device: %s (this library has no CPU path)",
+                    cudaGetErrorString(e));
+    if (device < 0 || device >= count) return fail(nullptr, SHRIKE_ERANGE, "device %d out of range", device);
+    e = cudaSetDevice(device);
+    if (e != cudaSuccess) return cuda_fail(nullptr, e, "cudaSetDevice");
+    shrike_moe* m = new (std::nothrow) shrike_moe();
+    if (!m) return fail(nullptr, SHRIKE_ENOMEM, "host allocation failed");
+    m->cfg = *config;
+    m->device = device;
+    cudaDeviceGetAttribute(&m->sm_count, cudaDevAttrMultiProcessorCount, device);
+    const shrike_moe_config& c = m->cfg;
+    Workspace& w = m->ws;
+    const size_t T = c.max_tokens, K = c.top_k;
+    w.max_inst = max_instances(c, c.max_tokens);
+    const size_t ab = act_bytes(c.act_dtype);
+    bool ok = true;
+    auto A = [&](auto** p, size_t bytes) { if (ok && dev_alloc(p, bytes) != cudaSuccess) ok = false; };
+    A(&w.logits, T * c.num_experts * 4);
+    A(&w.xh, T * c.d * 2);
+    A(&w.acts, T * K * c.f * 2);
+    A(&w.acts_shared, c.has_shared ? T * c.shared_f * 2 : 0);
+    A(&w.sorted, T * K * 4);
+    A(&w.inst, (size_t)w.max_inst * sizeof(Instance));
+    A(&w.n_inst, 4);
+    A(&w.status, 4);
+    A(&w.block_hist, ((T + 127) / 128) * c.num_experts * 4);
+    A(&w.expert_offsets, c.num_experts * 4);
+    A(&w.expert_counts, c.num_experts * 4);
+    A(&w.slot_of_expert, c.num_experts * 4);
+    A(&w.partials, T > SHRIKE_MAX_DECODE_TOKENS ? (T * K + (c.has_shared ? T : 0)) * c.d * 4 : 0);
+    A(&w.x_dev, T * c.d * ab);
+    A(&w.y_dev, T * c.d * ab);
+    A(&w.ids_dev, T * K * 4);
+    A(&w.w_dev, T * K * 4);
+    A(&w.gate_dev, T * 4);
+    A(&w.slots_dev, T * K * 4);
+    A(&w.counts_dev, 8);
+    if (!ok) {
+        free_workspace(w);
+        delete m;
+        cudaGetLastError();
+        return fail(nullptr, SHRIKE_ENOMEM, "device allocation of the workspace failed");
+    }
+    cudaMemset(w.status, 0, 4);
+    cudaMemset(w.n_inst, 0, 4);
+    *out = m;
+    return SHRIKE_OK;
+}
+
+void shrike_moe_destroy(shrike_moe* moe) {
+    if (!moe) return;
+    cudaSetDevice(moe->device);
+    free_workspace(moe->ws);
+    if (moe->residency) cudaFree(moe->residency);
+    delete moe;
+}
+
+int shrike_moe_status(shrike_moe* m, void* stream) {
+    if (!m) return SHRIKE_EINVAL;
+    CU(cudaStreamSynchronize((cudaStream_t)stream));
+    uint32_t st = 0;
+    CU(cudaMemcpy(&st, m->ws.status, 4, cudaMemcpyDeviceToHost));
+    if (st != kStatusOk) {
+        cudaMemset(m->ws.status, 0, 4);
+        if (st == kStatusWaitTimeout) return fail(m, SHRIKE_ETIMEDOUT, "a device-side wait gave up");
+        return fail(m, SHRIKE_ERANGE, "a kernel met a slot id outside the pool");
+    }
+    return SHRIKE_OK;
+}
+
+// ---- pool -------------------------------------------------------------------
+
+int shrike_pool_create(shrike_moe* m, uint32_t cells, uint64_t cell_stride, uint32_t chunks,
+                       shrike_pool** out) {
+    if (!m || !out) return SHRIKE_EINVAL;
+    *out = nullptr;
+    if (cells == 0 || chunks == 0 || chunks > SHRIKE_MAX_POOL_CHUNKS)
+        return fail(m, SHRIKE_EINVAL, "cells must be > 0 and chunks 1..8");
+    if (cell_stride == 0 || cell_stride % 256 != 0)
+        return fail(m, SHRIKE_EINVAL, "cell_stride must be a positive multiple of 256 bytes");
+    CU(cudaSetDevice(m->device));
+    shrike_pool* p = new (std::nothrow) shrike_pool();
+    if (!p) return fail(m, SHRIKE_ENOMEM, "host allocation failed");
+    memset(p, 0, sizeof *p);
+    p->owner = m;
+    p->chunks = chunks;
+    p->view.cells = cells;
+    p->view.stride = cell_stride;
+    p->view.cells_per_chunk = (cells + chunks - 1) / chunks;
+    for (uint32_t i = 0; i < SHRIKE_MAX_POOL_CHUNKS; ++i) p->view.base[i] = nullptr;
+    for (uint32_t i = 0; i < chunks; ++i) {
+        const uint64_t first = (uint64_t)i * p->view.cells_per_chunk;
+        if (first >= cells) { p->chunks = i; break; }
+        const uint64_t n = (first + p->view.cells_per_chunk <= cells) ? p->view.cells_per_chunk : cells - first;
+        cudaError_t e = cudaMalloc(&p->chunk[i], n * cell_stride);
+        if (e != cudaSuccess) {
+            for (uint32_t j = 0; j < i; ++j) cudaFree(p->chunk[j]);
+            delete p;
+            cudaGetLastError();
+            return fail(m, SHRIKE_ENOMEM, "pool chunk of %llu bytes: %s", (unsigned long long)(n * cell_stride),
+                        cudaGetErrorString(e));
+        }
+        p->view.base[i] = (const uint8_t*)p->chunk[i];
+    }
+    *out = p;
+    return SHRIKE_OK;
+}
+
+void shrike_pool_destroy(shrike_pool* pool) {
+    if (!pool) return;
+    cudaSetDevice(pool->owner->device);
+    for (uint32_t i = 0; i < pool->chunks; ++i)
+        if (pool->chunk[i]) cudaFree(pool->chunk[i]);
+    delete pool;
+}
+
+int shrike_pool_cell_address(const shrike_pool* pool, uint32_t cell, void** out) {
+    if (!pool || !out) return SHRIKE_EINVAL;
+    if (cell >= pool->view.cells) return fail(pool->owner, SHRIKE_ERANGE, "cell %u out of range", cell);
+    *out = (void*)pool_cell_base(pool->view, cell);
+    return SHRIKE_OK;
+}
+
+int shrike_pool_upload(shrike_pool* pool, uint32_t cell, const void* block_host, uint64_t bytes, void* stream) {
+    if (!pool || !block_host) return SHRIKE_EINVAL;
+    shrike_moe* m = pool->owner;
+    if (cell >= pool->view.cells) return fail(m, SHRIKE_ERANGE, "cell %u out of range", cell);
+    if (bytes > pool->view.stride) return fail(m, SHRIKE_ERANGE, "block larger than the cell stride");
+    CU(cudaMemcpyAsync((void*)pool_cell_base(pool->view, cell), block_host, bytes, cudaMemcpyHostToDevice,
+                       (cudaStream_t)stream));
+    return SHRIKE_OK;
+}
+
+int shrike_pool_download(shrike_pool* pool, uint32_t cell, void* block_host, uint64_t bytes, void* stream) {
+    if (!pool || !block_host) return SHRIKE_EINVAL;
+    shrike_moe* m = pool->owner;
+    if (cell >= pool->view.cells) return fail(m, SHRIKE_ERANGE, "cell %u out of range", cell);
+    if (bytes > pool->view.stride) return fail(m, SHRIKE_ERANGE, "block larger than the cell stride");
+    CU(cudaMemcpyAsync(block_host, pool_cell_base(pool->view, cell), bytes, cudaMemcpyDeviceToHost,
+                       (cudaStream_t)stream));
+    CU(cudaStreamSynchronize((cudaStream_t)stream));
+    return SHRIKE_OK;
+}
+
+int shrike_pool_fill_synthetic(shrike_moe* m, shrike_pool* pool, uint32_t first_cell, uint32_t count,
+                               uint64_t seed, uint32_t layer, uint32_t first_expert, int shared, void* stream) {
+    if (!m || !pool) return SHRIKE_EINVAL;
+    if ((uint64_t)first_cell + count > pool->view.cells) return fail(m, SHRIKE_ERANGE, "cells out of range");
+    if (shared && !m->cfg.has_shared) return fail(m, SHRIKE_EINVAL, "no shared expert in this config");
+    shrike_expert_offsets o;
+    uint64_t bytes;
+    make_offsets(m->cfg, shared != 0, o, bytes);
+    if (bytes > pool->view.stride) return fail(m, SHRIKE_ERANGE, "block larger than the cell stride");
+    if (count == 0) return SHRIKE_OK;
+    CU(launch_synth_fill(m, (cudaStream_t)stream, pool->view, first_cell, count, seed, layer, first_expert,
+                         shared != 0, to_offsets3(o)));
+    return SHRIKE_OK;
+}
+
+// ---- residency ----------------------------------------------------------------
+
+int shrike_residency_create(shrike_moe* m, uint32_t layers, uint64_t** table_out) {
+    if (!m || layers == 0) return SHRIKE_EINVAL;
+    CU(cudaSetDevice(m->device));
+    if (m->residency) { cudaFree(m->residency); m->residency = nullptr; }
+    const size_t n = (size_t)layers * m->cfg.num_experts;
+    cudaError_t e = cudaMalloc((void**)&m->residency, n * 8);
+    if (e != cudaSuccess) { cudaGetLastError(); return fail(m, SHRIKE_ENOMEM, "residency table: %s", cudaGetErrorString(e)); }
+    // every entry: state 0 (absent)
+    CU(cudaMemset(m->residency, 0, n * 8));
+    m->residency_layers = layers;
+    if (table_out) *table_out = m->residency;
+    return SHRIKE_OK;
+}
+
+__global__ void residency_identity_kernel(uint64_t* row, uint32_t ne, uint32_t first_cell) {
+    const uint32_t e = blockIdx.x * blockDim.x + threadIdx.x;
+    if (e < ne) row[e] = ((uint64_t)2 << 32) | (uint64_t)(first_cell + e);
+}
+
+__global__ void residency_set_kernel(uint64_t* word, uint64_t value) {
+    // one 64-bit store: the reader sees the old or the new {slot, state}, never a mix
+    *(volatile uint64_t*)word = value;
+}
+
+int shrike_residency_set(shrike_moe* m, uint32_t layer, uint32_t expert, uint32_t slot, uint32_t state,
+                         void* stream) {
+    if (!m || !m->residency) return SHRIKE_EINVAL;
+    if (layer >= m->residency_layers || expert >= m->cfg.num_experts)
+        return fail(m, SHRIKE_ERANGE, "layer %u / expert %u out of range", layer, expert);
+    const uint64_t v = ((uint64_t)state << 32) | slot;
+    residency_set_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(
+        m->residency + (size_t)layer * m->cfg.num_experts + expert, v);
+    CU(cudaGetLastError());
+    return SHRIKE_OK;
+}
+
+int shrike_residency_set_layer_identity(shrike_moe* m, uint32_t layer, uint32_t first_cell, void* stream) {
+    if (!m || !m->residency) return SHRIKE_EINVAL;
+    if (layer >= m->residency_layers) return fail(m, SHRIKE_ERANGE, "layer %u out of range", layer);
+    residency_identity_kernel<<<1, 256, 0, (cudaStream_t)stream>>>(
+        m->residency + (size_t)layer * m->cfg.num_experts, m->cfg.num_experts, first_cell);
+    CU(cudaGetLastError());
+    return SHRIKE_OK;
+}
+
+// ---- the path -------------------------------------------------------------------
+
+int shrike_encode_router(shrike_moe* m, void* stream, const shrike_router_operands* ops, const void* hidden,
+                         uint32_t query_count, uint32_t hidden_stride_elements, uint32_t* out_indices,
+                         float* out_weights, float* out_shared_gate) {
+    if (!m) return SHRIKE_EINVAL;
+    if (!ops || !ops->weights || !hidden || !out_indices || !out_weights)
+        return fail(m, SHRIKE_EINVAL, "router: null operand");
+    const shrike_moe_config& c = m->cfg;
+    if (c.router_weight_bits != 0 && (!ops->scales || !ops->biases))
+        return fail(m, SHRIKE_EINVAL, "router: affine weights need scales and biases");
+    if (query_count > c.max_tokens) return fail(m, SHRIKE_ERANGE, "query_count %u exceeds max_tokens %u", query_count, c.max_tokens);
+    if (hidden_stride_elements < c.d || hidden_stride_elements % 4 != 0)
+        return fail(m, SHRIKE_EINVAL, "hidden stride must be >= d and a multiple of 4 elements");
+    if (c.shared_gated && (!ops->shared_gate || !out_shared_gate))
+        return fail(m, SHRIKE_EINVAL, "router: a shared_gated handle needs shared_gate and out_shared_gate");
+    if (query_count == 0) return SHRIKE_OK;
+    CU(launch_router(m, (cudaStream_t)stream, *ops, hidden, query_count, hidden_stride_elements, out_indices,
+                     out_weights, out_shared_gate));
+    return SHRIKE_OK;
+}
+
+int shrike_encode_residency_classification(shrike_moe* m, void* stream, const uint32_t* topk_indices,
+                                           const uint64_t* residency_table_row, uint32_t query_count,
+                                           uint32_t* resolved_slots, uint32_t* counts,
+                                           uint32_t* miss_positions, uint32_t* miss_experts) {
+    if (!m) return SHRIKE_EINVAL;
+    if (!topk_indices || !residency_table_row || !resolved_slots)
+        return fail(m, SHRIKE_EINVAL, "classification: null operand");
+    if (query_count > m->cfg.max_tokens) return fail(m, SHRIKE_ERANGE, "query_count exceeds max_tokens");
+    if (query_count == 0) {
+        if (counts) CU(cudaMemsetAsync(counts, 0, 8, (cudaStream_t)stream));
+        return SHRIKE_OK;
+    }
+    CU(launch_classify(m, (cudaStream_t)stream, topk_indices, residency_table_row, query_count, resolved_slots,
+                       counts, miss_positions, miss_experts));
+    return SHRIKE_OK;
+}
+
+int shrike_encode_moe_decode(shrike_moe* m, void* stream, const shrike_pool* pool,
+                             const shrike_expert_offsets* routed_offsets, const uint32_t* resolved_slots,
+                             const float* routing_weights, const void* x, uint32_t query_count,
+                             const shrike_shared_expert* shared, const float* shared_gate,
+                             const uint32_t* io_status, void* y, void* hidden) {
+    if (!m) return SHRIKE_EINVAL;
+    if (!resolved_slots || !routing_weights || !x || !y) return fail(m, SHRIKE_EINVAL, "decode: null operand");
+    if (query_count > SHRIKE_MAX_DECODE_TOKENS || query_count > m->cfg.max_tokens)
+        return fail(m, SHRIKE_ERANGE, "decode handles at most %u rows (max_tokens %u); use the prefill call",
+                    SHRIKE_MAX_DECODE_TOKENS, m->cfg.max_tokens);
+    if (query_count == 0) return SHRIKE_OK;
+    ExpertArgs a;
+    int rc = fill_expert_args(m, pool, routed_offsets, shared, routing_weights, shared_gate, a);
+    if (rc) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    CU(launch_decode_plan(m, st, resolved_slots, x, query_count, io_status, m->cfg.has_shared != 0,
+                          pool->view.cells));
+    CU(launch_phase1(m, st, a, max_instances(m->cfg, query_count)));
+    CU(launch_phase2(m, st, a, query_count, y, hidden));
+    return SHRIKE_OK;
+}
+
+int shrike_encode_moe_prefill(shrike_moe* m, void* stream, const shrike_pool* pool,
+                              const shrike_expert_offsets* routed_offsets, const uint32_t* topk_indices,
+                              const uint32_t* resolved_slots, const float* routing_weights, const void* x,
+                              uint32_t query_count, const shrike_shared_expert* shared,
+                              const float* shared_gate, void* y, void* hidden) {
+    if (!m) return SHRIKE_EINVAL;
+    if (!topk_indices || !resolved_slots || !routing_weights || !x || !y)
+        return fail(m, SHRIKE_EINVAL, "prefill: null operand");
+    if (query_count > m->cfg.max_tokens) return fail(m, SHRIKE_ERANGE, "query_count exceeds max_tokens");
+    if (m->cfg.max_tokens <= SHRIKE_MAX_DECODE_TOKENS)
+        return fail(m, SHRIKE_EINVAL, "handle was created for decode only (max_tokens <= %u)", SHRIKE_MAX_DECODE_TOKENS);
+    if (query_count == 0) return SHRIKE_OK;
+    ExpertArgs a;
+    int rc = fill_expert_args(m, pool, routed_offsets, shared, routing_weights, shared_gate, a);
+    if (rc) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    const uint32_t mi = max_instances(m->cfg, query_count);
+    CU(launch_prefill_plan(m, st, topk_indices, resolved_slots, x, query_count, m->cfg.has_shared != 0,
+                           pool->view.cells));
+    CU(launch_phase1(m, st, a, mi));
+    float* partial_shared = m->ws.partials + (size_t)m->cfg.max_tokens * m->cfg.top_k * m->cfg.d;
+    CU(launch_phase2_partials(m, st, a, mi, m->ws.partials, partial_shared));
+    CU(launch_prefill_combine(m, st, routing_weights, shared_gate, resolved_slots, query_count, y, hidden));
+    return SHRIKE_OK;
+}
+
+int shrike_encode_group_pairs(shrike_moe* m, void* stream, const uint32_t* topk_indices,
+                              const float* routing_weights, uint32_t query_count, uint32_t* sorted_pairs,
+                              uint32_t* per_expert_offsets, uint32_t* per_expert_counts) {
+    if (!m) return SHRIKE_EINVAL;
+    if (!topk_indices || !sorted_pairs || !per_expert_offsets || !per_expert_counts)
+        return fail(m, SHRIKE_EINVAL, "group_pairs: null operand");
+    if (query_count > m->cfg.max_tokens) return fail(m, SHRIKE_ERANGE, "query_count exceeds max_tokens");
+    CU(launch_group_pairs(m, (cudaStream_t)stream, topk_indices, routing_weights, query_count, sorted_pairs,
+                          per_expert_offsets, per_expert_counts));
+    return SHRIKE_OK;
+}
+
+int shrike_moe_layer_forward_host(shrike_moe* m, void* stream, const shrike_pool* pool,
+                                  const shrike_expert_offsets* routed_offsets,
+                                  const uint64_t* residency_table_row, const shrike_router_operands* router,
+                                  const shrike_shared_expert* shared, const void* x_host,
+                                  uint32_t query_count, void* y_host, uint32_t* ids_host, float* weights_host) {
+    if (!m) return SHRIKE_EINVAL;
+    if (!x_host || !y_host || !router || !residency_table_row) return fail(m, SHRIKE_EINVAL, "forward_host: null operand");
+    const shrike_moe_config& c = m->cfg;
+    if (query_count == 0) return SHRIKE_OK;
+    if (query_count > c.max_tokens) return fail(m, SHRIKE_ERANGE, "query_count exceeds max_tokens");
+    cudaStream_t st = (cudaStream_t)stream;
+    Workspace& w = m->ws;
+    const size_t bytes = (size_t)query_count * c.d * act_bytes(c.act_dtype);
+    CU(cudaMemcpyAsync(w.x_dev, x_host, bytes, cudaMemcpyHostToDevice, st));
+    float* gate = c.shared_gated ? w.gate_dev : nullptr;
+    int rc = shrike_encode_router(m, stream, router, w.x_dev, query_count, c.d, w.ids_dev, w.w_dev, gate);
+    if (rc) return rc;
+    rc = shrike_encode_residency_classification(m, stream, w.ids_dev, residency_table_row, query_count,
+                                                w.slots_dev, w.counts_dev, nullptr, nullptr);
+    if (rc) return rc;
+    if (query_count <= SHRIKE_MAX_DECODE_TOKENS)
+        rc = shrike_encode_moe_decode(m, stream, pool, routed_offsets, w.slots_dev, w.w_dev, w.x_dev, query_count,
+                                      shared, gate, nullptr, w.y_dev, nullptr);
+    else
+        rc = shrike_encode_moe_prefill(m, stream, pool, routed_offsets, w.ids_dev, w.slots_dev, w.w_dev, w.x_dev,
+                                       query_count, shared, gate, w.y_dev, nullptr);
+    if (rc) return rc;
+    CU(cudaMemcpyAsync(y_host, w.y_dev, bytes, cudaMemcpyDeviceToHost, st));
+    if (ids_host) CU(cudaMemcpyAsync(ids_host, w.ids_dev, (size_t)query_count * c.top_k * 4, cudaMemcpyDeviceToHost, st));
+    if (weights_host) CU(cudaMemcpyAsync(weights_host, w.w_dev, (size_t)query_count * c.top_k * 4, cudaMemcpyDeviceToHost, st));
+    return shrike_moe_status(m, stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,155 @@
+// Shared device helpers: dtype conversion, PTX wrappers (mma.sync, bulk copy,
+// mbarrier with bounded waits, streaming loads) and the handle's internals.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/shrike_b200.h"
+
+namespace shrike {
+
+// ---- status word ------------------------------------------------------------
+// Kernels never trap or spin without bound: a wait that runs out records a
+// code here and the kernel carries on to its exit.
+enum : uint32_t { kStatusOk = 0, kStatusWaitTimeout = 1, kStatusBadIndex = 2 };
+
+__device__ __forceinline__ void report_status(uint32_t* status, uint32_t code) {
+    if (status) atomicMax(status, code);
+}
+
+// ---- dtypes -----------------------------------------------------------------
+__device__ __forceinline__ float bf16_bits_to_f32(uint16_t b) {
+    return __uint_as_float(((uint32_t)b) << 16);
+}
+__device__ __forceinline__ float f16_bits_to_f32(uint16_t b) {
+    return __half2float(__ushort_as_half(b));
+}
+template <int META>
+__device__ __forceinline__ float meta_to_f32(uint16_t b) {
+    return META == SHRIKE_DTYPE_FP16 ? f16_bits_to_f32(b) : bf16_bits_to_f32(b);
+}
+
+// Element `i` of an activation row of dtype `dt`, widened to fp32 exactly.
+__device__ __forceinline__ float load_act(const void* p, size_t i, uint32_t dt) {
+    if (dt == SHRIKE_DTYPE_FP32) return ((const float*)p)[i];
+    if (dt == SHRIKE_DTYPE_FP16) return f16_bits_to_f32(((const uint16_t*)p)[i]);
+    return bf16_bits_to_f32(((const uint16_t*)p)[i]);
+}
+__device__ __forceinline__ void store_act(void* p, size_t i, uint32_t dt, float v) {
+    if (dt == SHRIKE_DTYPE_FP32) ((float*)p)[i] = v;
+    else if (dt == SHRIKE_DTYPE_FP16) ((__half*)p)[i] = __float2half_rn(v);
+    else ((__nv_bfloat16*)p)[i] = __float2bfloat16_rn(v);
+}
+// The value an activation store would leave behind (hidden += y adds the
+// rounded y, as moe_phase2_finish does, moe.metal:889-893).
+__device__ __forceinline__ float round_act(uint32_t dt, float v) {
+    if (dt == SHRIKE_DTYPE_FP32) return v;
+    if (dt == SHRIKE_DTYPE_FP16) return __half2float(__float2half_rn(v));
+    return __bfloat162float(__float2bfloat16_rn(v));
+}
+
+// ---- loads ------------------------------------------------------------------
+// Weight bytes are read exactly once per call: keep them out of L1.
+__device__ __forceinline__ uint32_t ldg_stream_u32(const void* p) {
+    uint32_t v;
+    asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(v) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint2 ldg_stream_u64(const void* p) {
+    uint2 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];"
+                 : "=r"(v.x), "=r"(v.y) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint4 ldg_stream_u128(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
+// ---- tensor core (legacy path used for the skinny decode tiles) -------------
+// D(16x8,f32) += A(16x16,f16,row) * B(16x8,f16,col)
+__device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                          uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 "
+        "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t hsub2_u32(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("sub.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
+__device__ __forceinline__ uint32_t lop3_and_or(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t d;  // (a & b) | c
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+    return d;
+}
+
+// ---- mbarrier + 1-D bulk copy (TMA engine, no tensor map, no multicast) ------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void fence_mbar_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;"
+                 ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// global -> shared; dst, src 16-byte aligned, bytes a multiple of 16.
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+        ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+// Bounded wait: returns false (and the caller reports a timeout) instead of
+// spinning forever if the copy never lands.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
+    const uint32_t addr = smem_u32(bar);
+    for (uint32_t it = 0; it < (1u << 22); ++it) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+
+// ---- programmatic dependent launch ---------------------------------------
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+// ---- layout of the fp16 operand copies ------------------------------------
+// The B operand of the skinny MMA tiles is a copy of the activation row in fp16
+// whose aligned blocks of 8 elements are stored in the order the nibble
+// unpacking produces them: position p of a block holds element kPerm8[p].
+// int8 weights unpack in natural order and use the identity.
+__host__ __device__ __forceinline__ uint32_t perm_index(uint32_t i, bool int4) {
+    // inverse of {0,4,1,5,2,6,3,7}: element e sits at position kInv8[e]
+    const uint32_t e = i & 7u;
+    const uint32_t pos = int4 ? (((e & 3u) << 1) | (e >> 2)) : e;
+    return (i & ~7u) | pos;
+}
+
+}  // namespace shrike

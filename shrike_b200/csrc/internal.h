@@ -1,0 +1,143 @@
+// Internals of the opaque handles and the launch entry points the C ABI calls.
+#pragma once
+
+#include <string>
+
+#include "common.cuh"
+
+namespace shrike {
+
+// One unit of expert work: up to 8 rows (tokens) that all use one expert block.
+struct Instance {
+    uint32_t kind;   // 0 = routed (block = pool cell `slot`), 1 = shared expert
+    uint32_t slot;   // pool cell (routed)
+    uint32_t first;  // routed: index into the sorted pair list; shared: first token
+    uint32_t count;  // 1..8
+};
+
+// PoolBases (moe.metal:297-300) by value as a kernel argument.
+struct PoolView {
+    const uint8_t* base[SHRIKE_MAX_POOL_CHUNKS];
+    uint32_t cells_per_chunk;
+    uint32_t cells;
+    uint64_t stride;
+};
+
+__host__ __device__ __forceinline__ const uint8_t* pool_cell_base(const PoolView& p, uint32_t cell) {
+    return p.base[cell / p.cells_per_chunk] + (uint64_t)(cell % p.cells_per_chunk) * p.stride;
+}
+
+struct Offsets3 {  // gate / up / down
+    uint32_t w[3], s[3], b[3], ab[3];
+};
+
+inline Offsets3 to_offsets3(const shrike_expert_offsets& o) {
+    Offsets3 r;
+    r.w[0] = o.gate_w; r.s[0] = o.gate_s; r.b[0] = o.gate_b; r.ab[0] = o.gate_ab;
+    r.w[1] = o.up_w;   r.s[1] = o.up_s;   r.b[1] = o.up_b;   r.ab[1] = o.up_ab;
+    r.w[2] = o.down_w; r.s[2] = o.down_s; r.b[2] = o.down_b; r.ab[2] = o.down_ab;
+    return r;
+}
+
+// Everything the expert kernels need that does not change between launches of
+// one call.
+struct ExpertArgs {
+    PoolView pool;
+    Offsets3 routed;
+    Offsets3 shared;
+    const uint8_t* shared_block;
+    uint32_t d, f, f_shared, top_k;
+    uint32_t activation, expert_bias;
+    uint32_t act_dtype;
+    const Instance* inst;
+    const uint32_t* n_inst;
+    const uint32_t* sorted;       // sorted pair ids (token*top_k + rank)
+    const uint16_t* xh;           // fp16 operand copy of x, [tokens x d]
+    uint16_t* acts;               // fp16 operand copy of the routed activations [pairs x f]
+    uint16_t* acts_shared;        // [tokens x f_shared]
+    const float* route_w;         // [tokens x top_k]
+    const float* shared_gate;     // [tokens] or NULL
+    uint32_t* status;
+};
+
+struct Workspace {
+    float* logits = nullptr;        // [max_tokens x num_experts]
+    uint16_t* xh = nullptr;
+    uint16_t* acts = nullptr;
+    uint16_t* acts_shared = nullptr;
+    uint32_t* sorted = nullptr;     // [max_tokens x top_k]
+    Instance* inst = nullptr;
+    uint32_t* n_inst = nullptr;
+    uint32_t* status = nullptr;     // device status word
+    uint32_t* block_hist = nullptr; // prefill grouping scratch
+    uint32_t* expert_offsets = nullptr;
+    uint32_t* expert_counts = nullptr;
+    uint32_t* slot_of_expert = nullptr;
+    float* partials = nullptr;      // prefill: per-pair down outputs
+    // forward_host staging
+    void* x_dev = nullptr; void* y_dev = nullptr;
+    uint32_t* ids_dev = nullptr; float* w_dev = nullptr; float* gate_dev = nullptr;
+    uint32_t* slots_dev = nullptr; uint32_t* counts_dev = nullptr;
+    uint32_t max_inst = 0;
+};
+
+}  // namespace shrike
+
+struct shrike_pool {
+    shrike_moe* owner;
+    shrike::PoolView view;
+    void* chunk[SHRIKE_MAX_POOL_CHUNKS];
+    uint32_t chunks;
+};
+
+struct shrike_moe {
+    shrike_moe_config cfg;
+    int device;
+    std::string err;
+    shrike::Workspace ws;
+    uint64_t* residency = nullptr;
+    uint32_t residency_layers = 0;
+    int sm_count = 148;
+};
+
+namespace shrike {
+
+size_t act_bytes(uint32_t dt);
+
+// router.cu
+cudaError_t launch_router(const shrike_moe* m, cudaStream_t st, const shrike_router_operands& ops,
+                          const void* hidden, uint32_t T, uint32_t stride, uint32_t* ids,
+                          float* weights, float* shared_gate);
+cudaError_t launch_classify(const shrike_moe* m, cudaStream_t st, const uint32_t* ids,
+                            const uint64_t* table, uint32_t T, uint32_t* slots, uint32_t* counts,
+                            uint32_t* miss_pos, uint32_t* miss_exp);
+// plan.cu
+cudaError_t launch_decode_plan(const shrike_moe* m, cudaStream_t st, const uint32_t* slots,
+                               const void* x, uint32_t T, const uint32_t* io_status,
+                               bool with_shared, uint32_t pool_cells);
+cudaError_t launch_group_pairs(const shrike_moe* m, cudaStream_t st, const uint32_t* ids,
+                               const float* weights, uint32_t T, uint32_t* sorted_pairs,
+                               uint32_t* offsets, uint32_t* counts);
+// decode.cu
+cudaError_t launch_phase1(const shrike_moe* m, cudaStream_t st, const ExpertArgs& a,
+                          uint32_t max_inst);
+cudaError_t launch_phase2(const shrike_moe* m, cudaStream_t st, const ExpertArgs& a, uint32_t T,
+                          void* y, void* hidden);
+// synth.cu
+cudaError_t launch_synth_fill(const shrike_moe* m, cudaStream_t st, const PoolView& pool,
+                              uint32_t first_cell, uint32_t count, uint64_t seed, uint32_t layer,
+                              uint32_t first_expert, bool shared, const Offsets3& off);
+
+}  // namespace shrike
+
+namespace shrike {
+cudaError_t launch_phase2_partials(const shrike_moe* m, cudaStream_t st, const ExpertArgs& a,
+                                   uint32_t max_inst, float* partials, float* partial_shared);
+// prefill.cu
+cudaError_t launch_prefill_plan(const shrike_moe* m, cudaStream_t st, const uint32_t* ids,
+                                const uint32_t* slots, const void* x, uint32_t T, bool with_shared,
+                                uint32_t pool_cells);
+cudaError_t launch_prefill_combine(const shrike_moe* m, cudaStream_t st, const float* route_w,
+                                   const float* shared_gate, const uint32_t* slots, uint32_t T, void* y,
+                                   void* hidden);
+}  // namespace shrike

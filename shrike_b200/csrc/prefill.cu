@@ -1,0 +1,140 @@
+// Prefill path for ragged batches: rows are permuted by expert on the device
+// (plan.cu), every expert's rows run through the dequant-fused tiles in
+// instances of 8, the down projection writes one partial row per (row, rank)
+// pair, and a last pass does the weighted combine
+// (prefill_moe_reduce_token_major, prefill.metal:624-645, plus the two residual
+// adds of RealForwardRunner.swift:4658-4665 in one pass).
+#include "internal.h"
+
+namespace shrike {
+
+// One thread per expert: ceil(count/8) instances each, in expert order.
+__global__ void __launch_bounds__(256)
+prefill_instances_kernel(const uint32_t* __restrict__ offsets, const uint32_t* __restrict__ counts,
+                         const uint32_t* __restrict__ slot_of_expert, uint32_t ne, uint32_t T,
+                         uint32_t with_shared, uint32_t pool_cells, Instance* __restrict__ inst,
+                         uint32_t* __restrict__ n_inst, uint32_t* status) {
+    __shared__ uint32_t warp_sums[8];
+    const uint32_t e = threadIdx.x;
+    uint32_t n = 0, slot = SHRIKE_SLOT_MISS, c = 0;
+    if (e < ne && counts[e] > 0) {
+        c = counts[e];
+        slot = slot_of_expert[e];
+        if (slot != SHRIKE_SLOT_MISS && slot >= pool_cells) {
+            report_status(status, kStatusBadIndex);
+            slot = SHRIKE_SLOT_MISS;
+        }
+        if (slot != SHRIKE_SLOT_MISS) n = (c + 7) / 8;
+    }
+    // exclusive scan over 256 threads
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    uint32_t inc = n;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const uint32_t v = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= (uint32_t)o) inc += v;
+    }
+    if (lane == 31) warp_sums[warp] = inc;
+    __syncthreads();
+    uint32_t base = 0, total = 0;
+    for (uint32_t w = 0; w < 8; ++w) {
+        if (w < warp) base += warp_sums[w];
+        total += warp_sums[w];
+    }
+    base += inc - n;
+    for (uint32_t j = 0; j < n; ++j) {
+        Instance in;
+        in.kind = 0; in.slot = slot; in.first = offsets[e] + 8 * j; in.count = min(8u, c - 8 * j);
+        inst[base + j] = in;
+    }
+    const uint32_t n_shared = with_shared ? (T + 7) / 8 : 0;
+    for (uint32_t j = threadIdx.x; j < n_shared; j += blockDim.x) {
+        Instance in;
+        in.kind = 1; in.slot = 0; in.first = 8 * j; in.count = min(8u, T - 8 * j);
+        inst[total + j] = in;
+    }
+    if (threadIdx.x == 0) *n_inst = total + n_shared;
+}
+
+// x -> fp16 operand layout, all rows.
+__global__ void __launch_bounds__(256)
+prefill_xprep_kernel(const void* __restrict__ x, uint32_t total, uint32_t d, uint32_t act_dtype,
+                     uint32_t int4, uint16_t* __restrict__ xh) {
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+        const uint32_t row = i / d, e = i - row * d;
+        xh[(size_t)row * d + perm_index(e, int4 != 0)] =
+            __half_as_ushort(__float2half_rn(load_act(x, i, act_dtype)));
+    }
+}
+
+// slot_of_expert[e] = the cell every pair of expert e resolved to.
+__global__ void __launch_bounds__(256)
+prefill_slot_of_expert_kernel(const uint32_t* __restrict__ ids, const uint32_t* __restrict__ slots,
+                              uint32_t n_pairs, uint32_t ne, uint32_t* __restrict__ slot_of_expert) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n_pairs) {
+        const uint32_t e = ids[i];
+        if (e < ne) slot_of_expert[e] = slots[i];
+    }
+}
+
+// y[t] = sg[t]*partial_shared[t] + sum_r w[t,r]*partial[t*K+r]; hidden += y.
+// Pairs whose expert had no cell were never written and are skipped by slot.
+__global__ void __launch_bounds__(256)
+prefill_combine_kernel(const float* __restrict__ partials, const float* __restrict__ partial_shared,
+                       const float* __restrict__ route_w, const float* __restrict__ shared_gate,
+                       const uint32_t* __restrict__ slots, uint32_t T, uint32_t top_k, uint32_t d,
+                       uint32_t has_shared, uint32_t act_dtype, void* __restrict__ y,
+                       void* __restrict__ hidden) {
+    const uint32_t t = blockIdx.y;
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= T || i >= d) return;
+    float acc = 0.f;
+    if (has_shared) {
+        const float g = shared_gate ? shared_gate[t] : 1.0f;
+        acc = g * partial_shared[(size_t)t * d + i];
+    }
+    for (uint32_t r = 0; r < top_k; ++r) {
+        const uint32_t p = t * top_k + r;
+        if (slots[p] != SHRIKE_SLOT_MISS) acc = fmaf(route_w[p], partials[(size_t)p * d + i], acc);
+    }
+    const size_t o = (size_t)t * d + i;
+    store_act(y, o, act_dtype, acc);
+    if (hidden) {
+        const float h = load_act(hidden, o, act_dtype) + round_act(act_dtype, acc);
+        store_act(hidden, o, act_dtype, h);
+    }
+}
+
+cudaError_t launch_prefill_plan(const shrike_moe* m, cudaStream_t st, const uint32_t* ids,
+                                const uint32_t* slots, const void* x, uint32_t T, bool with_shared,
+                                uint32_t pool_cells) {
+    const shrike_moe_config& c = m->cfg;
+    const Workspace& ws = m->ws;
+    cudaError_t e = cudaMemsetAsync(ws.slot_of_expert, 0xff, c.num_experts * 4, st);
+    if (e != cudaSuccess) return e;
+    const uint32_t n_pairs = T * c.top_k;
+    prefill_slot_of_expert_kernel<<<(n_pairs + 255) / 256, 256, 0, st>>>(ids, slots, n_pairs, c.num_experts,
+                                                                         ws.slot_of_expert);
+    e = launch_group_pairs(m, st, ids, nullptr, T, nullptr, ws.expert_offsets, ws.expert_counts);
+    if (e != cudaSuccess) return e;
+    prefill_instances_kernel<<<1, 256, 0, st>>>(ws.expert_offsets, ws.expert_counts, ws.slot_of_expert,
+                                                c.num_experts, T, with_shared ? 1u : 0u, pool_cells, ws.inst,
+                                                ws.n_inst, ws.status);
+    const uint32_t total = T * c.d;
+    prefill_xprep_kernel<<<min(2048u, (total + 255) / 256), 256, 0, st>>>(x, total, c.d, c.act_dtype,
+                                                                         c.weight_bits == 4 ? 1u : 0u, ws.xh);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_prefill_combine(const shrike_moe* m, cudaStream_t st, const float* route_w,
+                                   const float* shared_gate, const uint32_t* slots, uint32_t T, void* y,
+                                   void* hidden) {
+    const shrike_moe_config& c = m->cfg;
+    prefill_combine_kernel<<<dim3((c.d + 255) / 256, T), 256, 0, st>>>(
+        m->ws.partials, m->ws.partials + (size_t)c.max_tokens * c.top_k * c.d, route_w, shared_gate, slots, T,
+        c.top_k, c.d, c.has_shared, c.act_dtype, y, hidden);
+    return cudaGetLastError();
+}
+
+}  // namespace shrike

@@ -1,0 +1,280 @@
+"""Host-side mirror of the reference's MoE dispatch surface over the C ABI.
+
+Class and method names follow the Swift wrappers they stand for
+(sources/Shrike/Kernels/MoE/MoE.swift, sources/Shrike/Kernels/Prefill/MoE,
+sources/Shrike/Infrastructure/Streaming/ExpertCellArena.swift); arguments keep
+their meaning. Device memory and streams come from torch; nothing here
+computes: every method validates and forwards to libshrike_b200.so and raises
+`ShrikeError` with the library's message on a non-zero return.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from . import capi
+
+
+class ShrikeError(RuntimeError):
+    def __init__(self, code: int, message: str):
+        super().__init__(f"shrike_b200 error {code}: {message}")
+        self.code = code
+
+
+_TORCH_ACT = {capi.DTYPE_BF16: torch.bfloat16, capi.DTYPE_FP16: torch.float16, capi.DTYPE_FP32: torch.float32}
+
+
+@dataclass
+class MoEConfig:
+    """Arguments of `MoE.init` (MoE.swift:94-106) plus the dtypes."""
+    d: int
+    f: int
+    num_experts: int
+    top_k: int
+    weight_bits: int = 4
+    group_size: int = 64
+    meta_dtype: int = capi.DTYPE_BF16
+    act_dtype: int = capi.DTYPE_BF16
+    activation: int = capi.ACT_SILU
+    expert_bias: bool = False
+    router_kind: int = capi.ROUTER_SOFTMAX
+    routed_scaling: float = 1.0
+    router_weight_bits: int = 0
+    round_route_weights_f16: bool = True
+    has_shared: bool = False
+    shared_gated: bool = False
+    shared_f: int = 0
+    max_tokens: int = 16
+
+    def to_c(self) -> capi.MoEConfig:
+        return capi.MoEConfig(
+            self.d, self.f, self.num_experts, self.top_k, self.weight_bits, self.group_size,
+            self.meta_dtype, self.act_dtype, self.activation, int(self.expert_bias), self.router_kind,
+            float(self.routed_scaling), self.router_weight_bits, int(self.round_route_weights_f16),
+            int(self.has_shared), int(self.shared_gated), self.shared_f if self.has_shared else 0,
+            self.max_tokens)
+
+    @property
+    def torch_act_dtype(self) -> torch.dtype:
+        return _TORCH_ACT[self.act_dtype]
+
+
+def expert_offsets(config: MoEConfig, shared: bool = False) -> tuple[capi.ExpertOffsets, int]:
+    """`CPUExpertFFN.Offsets` / `Model.routedExpertOffsets`: offsets and block size in bytes."""
+    lib = capi.load()
+    off = capi.ExpertOffsets()
+    size = C.c_uint64()
+    cfg = config.to_c()
+    rc = lib.shrike_expert_offsets_make(C.byref(cfg), int(shared), C.byref(off), C.byref(size))
+    if rc:
+        raise ShrikeError(rc, lib.shrike_last_error(None).decode())
+    return off, size.value
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    if t is None:
+        return None
+    if not t.is_cuda or not t.is_contiguous():
+        raise ValueError("device operands must be contiguous CUDA tensors")
+    return t.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+@dataclass
+class RouterOperands:
+    """Buffers of `MoE.encodeRouter` (MoE.swift:249-261); bf16 vectors as int16/bfloat16 tensors."""
+    weights: torch.Tensor
+    scales: Optional[torch.Tensor] = None
+    biases: Optional[torch.Tensor] = None
+    effective_scale: Optional[torch.Tensor] = None
+    per_expert_scale: Optional[torch.Tensor] = None
+    logit_bias: Optional[torch.Tensor] = None
+    shared_gate: Optional[torch.Tensor] = None
+
+    def to_c(self) -> capi.RouterOperands:
+        return capi.RouterOperands(_ptr(self.weights), _ptr(self.scales), _ptr(self.biases),
+                                   _ptr(self.effective_scale), _ptr(self.per_expert_scale),
+                                   _ptr(self.logit_bias), _ptr(self.shared_gate))
+
+
+class MoE:
+    """Stands for `final class MoE` and the prefill MoE wrappers; owns the workspace."""
+
+    def __init__(self, config: MoEConfig, device: int = 0):
+        self._lib = capi.load()
+        self.config = config
+        self.device = device
+        handle = C.c_void_p()
+        cfg = config.to_c()
+        rc = self._lib.shrike_moe_create(C.byref(cfg), device, C.byref(handle))
+        if rc:
+            raise ShrikeError(rc, self._lib.shrike_last_error(None).decode())
+        self._h = handle
+        self._residency_ptr = None
+        self._residency_layers = 0
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            self._lib.shrike_moe_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _check(self, rc: int) -> None:
+        if rc:
+            raise ShrikeError(rc, self._lib.shrike_last_error(self._h).decode())
+
+    def status(self) -> None:
+        """Synchronises the current stream and raises if a kernel reported a failure."""
+        self._check(self._lib.shrike_moe_status(self._h, _stream()))
+
+    # -- residency table (ExpertResidencyTable.swift:4-19) ---------------------
+    def create_residency(self, layers: int) -> None:
+        p = C.c_void_p()
+        self._check(self._lib.shrike_residency_create(self._h, layers, C.byref(p)))
+        self._residency_ptr = p.value
+        self._residency_layers = layers
+
+    def residency_row(self, layer: int) -> int:
+        if self._residency_ptr is None or layer >= self._residency_layers:
+            raise ValueError("residency table not created for this layer")
+        return self._residency_ptr + layer * self.config.num_experts * 8
+
+    def residency_set(self, layer: int, expert: int, slot: int, state: int) -> None:
+        self._check(self._lib.shrike_residency_set(self._h, layer, expert, slot, state, _stream()))
+
+    def residency_set_layer_identity(self, layer: int, first_cell: int) -> None:
+        self._check(self._lib.shrike_residency_set_layer_identity(self._h, layer, first_cell, _stream()))
+
+    # -- the path ------------------------------------------------------------
+    def encode_router(self, operands: RouterOperands, hidden: torch.Tensor, out_indices: torch.Tensor,
+                      out_weights: torch.Tensor, out_shared_gate: Optional[torch.Tensor] = None,
+                      query_count: Optional[int] = None, hidden_stride_elements: Optional[int] = None) -> None:
+        """`MoE.encodeRouter` / `PrefillRouter.encodeBlock`."""
+        q = hidden.shape[0] if query_count is None else query_count
+        stride = hidden.stride(0) if hidden_stride_elements is None else hidden_stride_elements
+        ops = operands.to_c()
+        if not hidden.is_cuda:
+            raise ValueError("hidden must be a CUDA tensor")
+        self._check(self._lib.shrike_encode_router(self._h, _stream(), C.byref(ops), hidden.data_ptr(), q, stride,
+                                                   _ptr(out_indices), _ptr(out_weights), _ptr(out_shared_gate)))
+
+    def encode_residency_classification(self, topk_indices: torch.Tensor, layer: int, resolved_slots: torch.Tensor,
+                                        counts: Optional[torch.Tensor] = None,
+                                        miss_positions: Optional[torch.Tensor] = None,
+                                        miss_experts: Optional[torch.Tensor] = None,
+                                        query_count: Optional[int] = None) -> None:
+        """`MoE.encodeResidencyClassification`."""
+        q = topk_indices.shape[0] if query_count is None else query_count
+        self._check(self._lib.shrike_encode_residency_classification(
+            self._h, _stream(), _ptr(topk_indices), self.residency_row(layer), q, _ptr(resolved_slots),
+            _ptr(counts), _ptr(miss_positions), _ptr(miss_experts)))
+
+    def encode_decode(self, pool: "ExpertCellArena", routed_offsets: capi.ExpertOffsets,
+                      resolved_slots: torch.Tensor, routing_weights: torch.Tensor, x: torch.Tensor,
+                      y: torch.Tensor, hidden: Optional[torch.Tensor] = None,
+                      shared: Optional[capi.SharedExpert] = None, shared_gate: Optional[torch.Tensor] = None,
+                      io_status: Optional[torch.Tensor] = None, query_count: Optional[int] = None) -> None:
+        """encodeSharedExpertWork + `MoE.encodeSpecPhase1U16Load` + `MoE.encodeSpecPhase2Reduce`."""
+        q = x.shape[0] if query_count is None else query_count
+        self._check(self._lib.shrike_encode_moe_decode(
+            self._h, _stream(), pool._h, C.byref(routed_offsets), _ptr(resolved_slots), _ptr(routing_weights),
+            _ptr(x), q, C.byref(shared) if shared is not None else None, _ptr(shared_gate), _ptr(io_status),
+            _ptr(y), _ptr(hidden)))
+
+    def encode_prefill(self, pool: "ExpertCellArena", routed_offsets: capi.ExpertOffsets,
+                       topk_indices: torch.Tensor, resolved_slots: torch.Tensor, routing_weights: torch.Tensor,
+                       x: torch.Tensor, y: torch.Tensor, hidden: Optional[torch.Tensor] = None,
+                       shared: Optional[capi.SharedExpert] = None, shared_gate: Optional[torch.Tensor] = None,
+                       query_count: Optional[int] = None) -> None:
+        """buildPrefillRoutes + encodeGroupedExpertGEMMs + shared chunk + encodeReduceTokenMajor + residual adds."""
+        q = x.shape[0] if query_count is None else query_count
+        self._check(self._lib.shrike_encode_moe_prefill(
+            self._h, _stream(), pool._h, C.byref(routed_offsets), _ptr(topk_indices), _ptr(resolved_slots),
+            _ptr(routing_weights), _ptr(x), q, C.byref(shared) if shared is not None else None,
+            _ptr(shared_gate), _ptr(y), _ptr(hidden)))
+
+    def group_token_expert_pairs(self, topk_indices: torch.Tensor, routing_weights: Optional[torch.Tensor],
+                                 sorted_pairs: torch.Tensor, per_expert_offsets: torch.Tensor,
+                                 per_expert_counts: torch.Tensor, query_count: Optional[int] = None) -> None:
+        """`PrefillMoEGrouping.groupTokenExpertPairs` on the device."""
+        q = topk_indices.shape[0] if query_count is None else query_count
+        self._check(self._lib.shrike_encode_group_pairs(
+            self._h, _stream(), _ptr(topk_indices), _ptr(routing_weights), q, _ptr(sorted_pairs),
+            _ptr(per_expert_offsets), _ptr(per_expert_counts)))
+
+    def layer_forward_host(self, pool: "ExpertCellArena", routed_offsets: capi.ExpertOffsets, layer: int,
+                           router: RouterOperands, x_host: torch.Tensor, y_host: torch.Tensor,
+                           shared: Optional[capi.SharedExpert] = None, ids_host: Optional[torch.Tensor] = None,
+                           weights_host: Optional[torch.Tensor] = None) -> None:
+        """One layer with host activations in and out (copies inside the call)."""
+        for t in (x_host, y_host, ids_host, weights_host):
+            if t is not None and (t.is_cuda or not t.is_contiguous()):
+                raise ValueError("host operands must be contiguous CPU tensors")
+        ops = router.to_c()
+        self._check(self._lib.shrike_moe_layer_forward_host(
+            self._h, _stream(), pool._h, C.byref(routed_offsets), self.residency_row(layer), C.byref(ops),
+            C.byref(shared) if shared is not None else None, x_host.data_ptr(), x_host.shape[0],
+            y_host.data_ptr(), ids_host.data_ptr() if ids_host is not None else None,
+            weights_host.data_ptr() if weights_host is not None else None))
+
+
+class ExpertCellArena:
+    """`ExpertCellArena` (ExpertCellArena.swift:16-132): cells of whole expert blocks in HBM."""
+
+    def __init__(self, moe: MoE, cells: int, cell_stride: int, chunks: int = 1):
+        self._moe = moe
+        self._lib = moe._lib
+        self.cells = cells
+        self.cell_stride = cell_stride
+        h = C.c_void_p()
+        moe._check(self._lib.shrike_pool_create(moe._h, cells, cell_stride, chunks, C.byref(h)))
+        self._h = h
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            self._lib.shrike_pool_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def upload(self, cell: int, block) -> None:
+        """Copies one packed expert block (bytes / numpy uint8 array) into a cell."""
+        import numpy as np
+        buf = np.ascontiguousarray(np.frombuffer(block, dtype=np.uint8) if isinstance(block, (bytes, bytearray)) else block)
+        self._moe._check(self._lib.shrike_pool_upload(self._h, cell, buf.ctypes.data, buf.nbytes, _stream()))
+        torch.cuda.current_stream().synchronize()  # the host buffer may go away after return
+
+    def download(self, cell: int, nbytes: int):
+        import numpy as np
+        out = np.empty(nbytes, dtype=np.uint8)
+        self._moe._check(self._lib.shrike_pool_download(self._h, cell, out.ctypes.data, nbytes, _stream()))
+        return out
+
+    def cell_address(self, cell: int) -> int:
+        p = C.c_void_p()
+        self._moe._check(self._lib.shrike_pool_cell_address(self._h, cell, C.byref(p)))
+        return p.value
+
+    def fill_synthetic(self, first_cell: int, count: int, seed: int, layer: int, first_expert: int = 0,
+                       shared: bool = False) -> None:
+        self._moe._check(self._lib.shrike_pool_fill_synthetic(
+            self._moe._h, self._h, first_cell, count, seed, layer, first_expert, int(shared), _stream()))
+
+
+def round_up(n: int, m: int) -> int:
+    return (n + m - 1) // m * m
