@@ -199,6 +199,25 @@ int shrike_encode_moe_decode(shrike_moe* moe, void* stream, const shrike_pool* p
                              const shrike_shared_expert* shared, const float* shared_gate,
                              const uint32_t* io_status, void* y, void* hidden);
 
+/* The three steps of the decode call, for hosts that encode them separately as
+ * the reference does. They must run in this order on one stream with the same
+ * pool, offsets, shared expert and query_count; the handle's workspace carries
+ * the work lists and activations from one to the next.
+ *   plan:    resolved_slots -> per-expert work lists (the slot lookup at the top
+ *            of the spec kernels, moe.metal:980-984), x -> operand layout
+ *   phase 1: MoE.encodeSpecPhase1U16Load (MoE.swift:906-948) + shared gate/up
+ *   phase 2: MoE.encodeSpecPhase2Reduce (MoE.swift:992-1049) + shared down */
+int shrike_encode_decode_plan(shrike_moe* moe, void* stream, const shrike_pool* pool,
+                              const uint32_t* resolved_slots, const void* x, uint32_t query_count,
+                              const uint32_t* io_status);
+int shrike_encode_phase1(shrike_moe* moe, void* stream, const shrike_pool* pool,
+                         const shrike_expert_offsets* routed_offsets,
+                         const shrike_shared_expert* shared, uint32_t query_count);
+int shrike_encode_phase2_reduce(shrike_moe* moe, void* stream, const shrike_pool* pool,
+                                const shrike_expert_offsets* routed_offsets,
+                                const float* routing_weights, const shrike_shared_expert* shared,
+                                const float* shared_gate, uint32_t query_count, void* y, void* hidden);
+
 /* Prefill, any query_count <= max_tokens. Stands for buildPrefillRoutes
  * (RealForwardRunner.swift:4305), encodeGroupedExpertGEMMs
  * (PrefillGroupedRoutedMoE.swift:925-1035), PrefillSharedExpert.encodeChunk

@@ -71,6 +71,10 @@ SIGNATURES = {
     "shrike_residency_set_layer_identity": (_INT, [_P, _U32, _U32, _P]),
     "shrike_encode_router": (_INT, [_P, _P, C.POINTER(RouterOperands), _P, _U32, _U32, _P, _P, _P]),
     "shrike_encode_residency_classification": (_INT, [_P, _P, _P, _P, _U32, _P, _P, _P, _P]),
+    "shrike_encode_decode_plan": (_INT, [_P, _P, _P, _P, _P, _U32, _P]),
+    "shrike_encode_phase1": (_INT, [_P, _P, _P, C.POINTER(ExpertOffsets), C.POINTER(SharedExpert), _U32]),
+    "shrike_encode_phase2_reduce": (_INT, [_P, _P, _P, C.POINTER(ExpertOffsets), _P, C.POINTER(SharedExpert), _P,
+                                           _U32, _P, _P]),
     "shrike_encode_moe_decode": (_INT, [_P, _P, _P, C.POINTER(ExpertOffsets), _P, _P, _P, _U32,
                                         C.POINTER(SharedExpert), _P, _P, _P, _P]),
     "shrike_encode_moe_prefill": (_INT, [_P, _P, _P, C.POINTER(ExpertOffsets), _P, _P, _P, _P, _U32,

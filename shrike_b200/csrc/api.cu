@@ -102,7 +102,7 @@ void free_workspace(Workspace& w) {
 
 int fill_expert_args(shrike_moe* m, const shrike_pool* pool, const shrike_expert_offsets* ro,
                      const shrike_shared_expert* shared, const float* weights, const float* shared_gate,
-                     ExpertArgs& a) {
+                     ExpertArgs& a, bool check_gate = true) {
     const shrike_moe_config& c = m->cfg;
     if (!pool || !ro) return fail(m, SHRIKE_EINVAL, "pool and routed_offsets are required");
     if (!offsets_aligned(*ro)) return fail(m, SHRIKE_EINVAL, "routed offsets must be multiples of 16 bytes");
@@ -111,8 +111,8 @@ int fill_expert_args(shrike_moe* m, const shrike_pool* pool, const shrike_expert
         if (!offsets_aligned(shared->offsets) || ((uintptr_t)shared->block & 15))
             return fail(m, SHRIKE_EINVAL, "shared expert block and offsets must be 16-byte aligned");
     }
-    if (shared_gate && !c.shared_gated) return fail(m, SHRIKE_EINVAL, "shared_gate given but the handle is not shared_gated");
-    if (c.shared_gated && !shared_gate) return fail(m, SHRIKE_EINVAL, "shared_gated handle needs the router's shared_gate output");
+    if (check_gate && shared_gate && !c.shared_gated) return fail(m, SHRIKE_EINVAL, "shared_gate given but the handle is not shared_gated");
+    if (check_gate && c.shared_gated && !shared_gate) return fail(m, SHRIKE_EINVAL, "shared_gated handle needs the router's shared_gate output");
     memset(&a, 0, sizeof a);
     a.pool = pool->view;
     a.routed = to_offsets3(*ro);
@@ -405,6 +405,47 @@ int shrike_encode_residency_classification(shrike_moe* m, void* stream, const ui
     return SHRIKE_OK;
 }
 
+int shrike_encode_decode_plan(shrike_moe* m, void* stream, const shrike_pool* pool,
+                              const uint32_t* resolved_slots, const void* x, uint32_t query_count,
+                              const uint32_t* io_status) {
+    if (!m) return SHRIKE_EINVAL;
+    if (!pool || !resolved_slots || !x) return fail(m, SHRIKE_EINVAL, "decode plan: null operand");
+    if (query_count == 0 || query_count > SHRIKE_MAX_DECODE_TOKENS || query_count > m->cfg.max_tokens)
+        return fail(m, SHRIKE_ERANGE, "decode handles 1..%u rows (max_tokens %u); use the prefill call",
+                    SHRIKE_MAX_DECODE_TOKENS, m->cfg.max_tokens);
+    CU(launch_decode_plan(m, (cudaStream_t)stream, resolved_slots, x, query_count, io_status,
+                          m->cfg.has_shared != 0, pool->view.cells));
+    return SHRIKE_OK;
+}
+
+int shrike_encode_phase1(shrike_moe* m, void* stream, const shrike_pool* pool,
+                         const shrike_expert_offsets* routed_offsets, const shrike_shared_expert* shared,
+                         uint32_t query_count) {
+    if (!m) return SHRIKE_EINVAL;
+    if (query_count == 0 || query_count > SHRIKE_MAX_DECODE_TOKENS || query_count > m->cfg.max_tokens)
+        return fail(m, SHRIKE_ERANGE, "phase 1: query_count out of range");
+    ExpertArgs a;
+    int rc = fill_expert_args(m, pool, routed_offsets, shared, nullptr, nullptr, a, false);
+    if (rc) return rc;
+    CU(launch_phase1(m, (cudaStream_t)stream, a, max_instances(m->cfg, query_count)));
+    return SHRIKE_OK;
+}
+
+int shrike_encode_phase2_reduce(shrike_moe* m, void* stream, const shrike_pool* pool,
+                                const shrike_expert_offsets* routed_offsets, const float* routing_weights,
+                                const shrike_shared_expert* shared, const float* shared_gate,
+                                uint32_t query_count, void* y, void* hidden) {
+    if (!m) return SHRIKE_EINVAL;
+    if (!routing_weights || !y) return fail(m, SHRIKE_EINVAL, "phase 2: null operand");
+    if (query_count == 0 || query_count > SHRIKE_MAX_DECODE_TOKENS || query_count > m->cfg.max_tokens)
+        return fail(m, SHRIKE_ERANGE, "phase 2: query_count out of range");
+    ExpertArgs a;
+    int rc = fill_expert_args(m, pool, routed_offsets, shared, routing_weights, shared_gate, a, true);
+    if (rc) return rc;
+    CU(launch_phase2(m, (cudaStream_t)stream, a, query_count, y, hidden));
+    return SHRIKE_OK;
+}
+
 int shrike_encode_moe_decode(shrike_moe* m, void* stream, const shrike_pool* pool,
                              const shrike_expert_offsets* routed_offsets, const uint32_t* resolved_slots,
                              const float* routing_weights, const void* x, uint32_t query_count,
@@ -412,19 +453,13 @@ int shrike_encode_moe_decode(shrike_moe* m, void* stream, const shrike_pool* poo
                              const uint32_t* io_status, void* y, void* hidden) {
     if (!m) return SHRIKE_EINVAL;
     if (!resolved_slots || !routing_weights || !x || !y) return fail(m, SHRIKE_EINVAL, "decode: null operand");
-    if (query_count > SHRIKE_MAX_DECODE_TOKENS || query_count > m->cfg.max_tokens)
-        return fail(m, SHRIKE_ERANGE, "decode handles at most %u rows (max_tokens %u); use the prefill call",
-                    SHRIKE_MAX_DECODE_TOKENS, m->cfg.max_tokens);
     if (query_count == 0) return SHRIKE_OK;
-    ExpertArgs a;
-    int rc = fill_expert_args(m, pool, routed_offsets, shared, routing_weights, shared_gate, a);
+    int rc = shrike_encode_decode_plan(m, stream, pool, resolved_slots, x, query_count, io_status);
     if (rc) return rc;
-    cudaStream_t st = (cudaStream_t)stream;
-    CU(launch_decode_plan(m, st, resolved_slots, x, query_count, io_status, m->cfg.has_shared != 0,
-                          pool->view.cells));
-    CU(launch_phase1(m, st, a, max_instances(m->cfg, query_count)));
-    CU(launch_phase2(m, st, a, query_count, y, hidden));
-    return SHRIKE_OK;
+    rc = shrike_encode_phase1(m, stream, pool, routed_offsets, shared, query_count);
+    if (rc) return rc;
+    return shrike_encode_phase2_reduce(m, stream, pool, routed_offsets, routing_weights, shared, shared_gate,
+                                       query_count, y, hidden);
 }
 
 int shrike_encode_moe_prefill(shrike_moe* m, void* stream, const shrike_pool* pool,

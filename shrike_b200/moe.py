@@ -192,6 +192,27 @@ class MoE:
             _ptr(x), q, C.byref(shared) if shared is not None else None, _ptr(shared_gate), _ptr(io_status),
             _ptr(y), _ptr(hidden)))
 
+    def encode_decode_plan(self, pool: "ExpertCellArena", resolved_slots: torch.Tensor, x: torch.Tensor,
+                           io_status: Optional[torch.Tensor] = None, query_count: Optional[int] = None) -> None:
+        q = x.shape[0] if query_count is None else query_count
+        self._check(self._lib.shrike_encode_decode_plan(self._h, _stream(), pool._h, _ptr(resolved_slots), _ptr(x),
+                                                        q, _ptr(io_status)))
+
+    def encode_phase1(self, pool: "ExpertCellArena", routed_offsets: capi.ExpertOffsets, query_count: int,
+                      shared: Optional[capi.SharedExpert] = None) -> None:
+        """`MoE.encodeSpecPhase1U16Load` (+ the shared expert's gate/up grid)."""
+        self._check(self._lib.shrike_encode_phase1(self._h, _stream(), pool._h, C.byref(routed_offsets),
+                                                   C.byref(shared) if shared is not None else None, query_count))
+
+    def encode_phase2_reduce(self, pool: "ExpertCellArena", routed_offsets: capi.ExpertOffsets,
+                             routing_weights: torch.Tensor, y: torch.Tensor, query_count: int,
+                             hidden: Optional[torch.Tensor] = None, shared: Optional[capi.SharedExpert] = None,
+                             shared_gate: Optional[torch.Tensor] = None) -> None:
+        """`MoE.encodeSpecPhase2Reduce` (+ the shared expert's down projection)."""
+        self._check(self._lib.shrike_encode_phase2_reduce(
+            self._h, _stream(), pool._h, C.byref(routed_offsets), _ptr(routing_weights),
+            C.byref(shared) if shared is not None else None, _ptr(shared_gate), query_count, _ptr(y), _ptr(hidden)))
+
     def encode_prefill(self, pool: "ExpertCellArena", routed_offsets: capi.ExpertOffsets,
                        topk_indices: torch.Tensor, resolved_slots: torch.Tensor, routing_weights: torch.Tensor,
                        x: torch.Tensor, y: torch.Tensor, hidden: Optional[torch.Tensor] = None,

@@ -1,0 +1,320 @@
+"""Parity of the CUDA path (through the C ABI) with the CPU oracle.
+
+Bars: top-k ids bit-exact; route weights bit-exact (both sides run the same
+fixed fp32 sequence); layer outputs within 1e-3 relative L2 when activations
+are fp32, and within the rounding of the activation dtype otherwise.
+"""
+import numpy as np
+import pytest
+import torch
+
+import oracle_lib as O
+from gpu_harness import Layer, inputs, rel_l2, small_config, to_act_tensor
+from shrike_b200 import capi, fixtures as fx
+from shrike_b200.moe import ShrikeError
+
+pytestmark = pytest.mark.gpu
+
+TOL = 1e-3  # relative L2, fp32 accumulation (the bar the workload definition states)
+
+
+def check_layer(layer: Layer, x: np.ndarray, tol: float = TOL, **kw):
+    y, ids, w, _ = layer.forward(x, **kw)
+    ids_ref, w_ref, _ = layer.oracle_route(x)
+    assert (ids == ids_ref).all(), "top-k ids differ from the oracle"
+    assert (w == w_ref).all(), "route weights differ from the oracle"
+    y_ref = layer.oracle_forward(x, ids_ref, w_ref)
+    err = rel_l2(y, y_ref)
+    assert err <= tol, f"relative L2 {err:.3e} > {tol}"
+    return err
+
+
+@pytest.mark.parametrize("T", [1, 2, 5, 8, 9, 16, 33, 64])
+def test_decode_small_token_counts(cuda_device, T):
+    layer = Layer(small_config())
+    check_layer(layer, inputs(T, 128, seed=T))
+    layer.close()
+
+
+@pytest.mark.parametrize("d,f", [(64, 64), (128, 192), (192, 128), (384, 384), (512, 64), (64, 512)])
+@pytest.mark.parametrize("k", [1, 2, 8])
+def test_decode_shape_sweep(cuda_device, d, f, k):
+    layer = Layer(small_config(d=d, f=f, shared_f=f, top_k=k))
+    check_layer(layer, inputs(3, d, seed=d + f + k))
+    layer.close()
+
+
+@pytest.mark.parametrize("bits,group,meta", [(4, 64, 0), (4, 64, 1), (4, 32, 0), (4, 32, 1), (8, 64, 0), (8, 64, 1),
+                                             (8, 32, 0), (8, 32, 1)])
+def test_decode_quantisation_variants(cuda_device, bits, group, meta):
+    layer = Layer(small_config(weight_bits=bits, group_size=group, meta_dtype=meta, d=192, f=128, shared_f=64))
+    check_layer(layer, inputs(4, 192, seed=bits + group + meta))
+    layer.close()
+
+
+@pytest.mark.parametrize("activation,bias", [(capi.ACT_SILU, True), (capi.ACT_GELU_TANH, False),
+                                             (capi.ACT_CLAMPED_SWIGLU, True), (capi.ACT_CLAMPED_SWIGLU, False)])
+def test_decode_activations_and_additive_biases(cuda_device, activation, bias):
+    layer = Layer(small_config(activation=activation, expert_bias=bias, has_shared=False, shared_gated=False))
+    # scale the input up so that the clamp at 7 is exercised
+    check_layer(layer, inputs(5, 128, seed=3) * np.float32(8))
+    layer.close()
+
+
+@pytest.mark.parametrize("shared,gated,shared_f", [(False, False, 0), (True, False, 64), (True, True, 128)])
+def test_decode_shared_expert_forms(cuda_device, shared, gated, shared_f):
+    layer = Layer(small_config(has_shared=shared, shared_gated=gated, shared_f=shared_f))
+    check_layer(layer, inputs(6, 128, seed=11))
+    layer.close()
+
+
+@pytest.mark.parametrize("act_dtype,tol", [(capi.DTYPE_BF16, 4e-3), (capi.DTYPE_FP16, 1e-3)])
+def test_decode_half_precision_io(cuda_device, act_dtype, tol):
+    """y is rounded to the activation dtype on store: bf16 carries 8 bits (2^-9 relative per element,
+    about 2e-3 relative L2), fp16 11 bits."""
+    layer = Layer(small_config(act_dtype=act_dtype))
+    x = inputs(4, 128, seed=5)
+    check_layer(layer, x, tol=tol)
+    layer.close()
+
+
+def test_hidden_accumulates_the_rounded_output(cuda_device):
+    layer = Layer(small_config(act_dtype=capi.DTYPE_FP16))
+    x = inputs(3, 128, seed=2)
+    h0 = np.random.default_rng(0).normal(0, 1, (3, 128)).astype(np.float16).astype(np.float32)
+    y, _, _, h = layer.forward(x, hidden=h0)
+    expect = (h0 + y).astype(np.float16).astype(np.float32)
+    assert np.abs(h - expect).max() == 0.0
+    layer.close()
+
+
+@pytest.mark.parametrize("router_bits", [0, 8, 4])
+@pytest.mark.parametrize("sigmoid", [False, True])
+def test_router_ids_and_weights_exact(cuda_device, router_bits, sigmoid):
+    ne = 64
+    rng = np.random.default_rng(9)
+    cfg = small_config(d=256, num_experts=ne, top_k=8, router_weight_bits=router_bits,
+                       router_kind=capi.ROUTER_SIGMOID if sigmoid else capi.ROUTER_SOFTMAX,
+                       routed_scaling=2.446 if sigmoid else 1.0, max_tokens=256)
+    layer = Layer(cfg, logit_bias=rng.uniform(-0.1, 0.1, ne).astype(np.float32),
+                  per_expert_scale=rng.uniform(0.6, 1.4, ne).astype(np.float32), router_sigma=0.05)
+    x = inputs(200, 256, seed=4)
+    ids, w, gate = layer.route(to_act_tensor(x, cfg.act_dtype, layer.device))
+    ids_ref, w_ref, _ = layer.oracle_route(x)
+    assert (ids.cpu().numpy().astype(np.uint32) == ids_ref).all()
+    assert (w.cpu().numpy() == w_ref).all()
+    g_ref = 1 / (1 + np.exp(-(x.astype(np.float64) @ layer.gate_w.astype(np.float64))))
+    assert np.abs(gate.cpu().numpy() - g_ref).max() < 1e-5
+    layer.close()
+
+
+def test_router_exact_ties_and_near_ties(cuda_device):
+    """Rows of router weights repeated exactly give equal scores: the lower id must win."""
+    cfg = small_config(d=128, num_experts=16, top_k=8, has_shared=False, shared_gated=False)
+    layer = Layer(cfg)
+    w = layer.router_w.copy()
+    w[5] = w[2]
+    w[9] = w[2]
+    w[12] = w[11] * np.float32(1 + 1e-4)
+    layer.router_w = w
+    layer._rw.copy_(torch.from_numpy(w))
+    x = inputs(16, 128, seed=6)
+    ids, wt, _ = layer.route(to_act_tensor(x, cfg.act_dtype, layer.device))
+    ids_ref, w_ref, _ = layer.oracle_route(x)
+    ids = ids.cpu().numpy().astype(np.uint32)
+    assert (ids == ids_ref).all() and (wt.cpu().numpy() == w_ref).all()
+    for row in ids:
+        pos = {int(e): i for i, e in enumerate(row)}
+        if 2 in pos and 5 in pos:
+            assert pos[2] < pos[5]
+        if 5 in pos and 9 in pos:
+            assert pos[5] < pos[9]
+    layer.close()
+
+
+def test_router_strided_hidden_equals_dense(cuda_device):
+    """PrefillRouterTests: rows spaced by a stride route like the same rows packed densely."""
+    cfg = small_config(max_tokens=64)
+    layer = Layer(cfg)
+    x = inputs(10, 128, seed=8)
+    wide = np.zeros((10, 192), dtype=np.float32)
+    wide[:, :128] = x
+    wide[:, 128:] = 7.0
+    a = layer.route(to_act_tensor(x, cfg.act_dtype, layer.device))
+    b = layer.route(to_act_tensor(wide, cfg.act_dtype, layer.device), stride=192)
+    assert (a[0] == b[0]).all() and (a[1] == b[1]).all() and (a[2] == b[2]).all()
+    layer.close()
+
+
+def test_residency_classification_and_misses(cuda_device):
+    cfg = small_config()
+    layer = Layer(cfg)
+    layer.moe.residency_set(0, 3, 0, 1)            # expert 3: loading, not resident
+    layer.moe.residency_set(0, 7, capi.SLOT_MISS, 2)
+    x = inputs(32, 128, seed=10)
+    x_dev = to_act_tensor(x, cfg.act_dtype, layer.device)
+    ids, w, gate = layer.route(x_dev)
+    slots = torch.empty_like(ids)
+    counts = torch.zeros(2, dtype=torch.int32, device=layer.device)
+    miss_pos = torch.full((32 * 4,), -1, dtype=torch.int32, device=layer.device)
+    miss_exp = torch.full((32 * 4,), -1, dtype=torch.int32, device=layer.device)
+    layer.moe.encode_residency_classification(ids, 0, slots, counts, miss_pos, miss_exp)
+    layer.moe.status()
+    ids_np = ids.cpu().numpy().astype(np.uint32)
+    table = np.array([(2 << 32) | e for e in range(16)], dtype=np.uint64)
+    table[3] = (1 << 32) | 0
+    table[7] = (2 << 32) | 0xFFFFFFFF
+    exp_slots, exp_pos, exp_exp = [], [], []
+    for t in range(32):
+        s, misses, mp, me = O.classify_residency(ids_np[t], table, 16)
+        exp_slots.append(s)
+        exp_pos += [t * 4 + int(p) for p in mp]
+        exp_exp += [int(e) for e in me]
+    assert (slots.cpu().numpy().astype(np.uint32) == np.stack(exp_slots)).all()
+    c = counts.cpu().numpy()
+    assert c[1] == len(exp_pos) and c[0] == 32 * 4 - len(exp_pos) and len(exp_pos) > 0
+    assert list(miss_pos.cpu().numpy()[:c[1]]) == exp_pos and list(miss_exp.cpu().numpy()[:c[1]]) == exp_exp
+    # a missing expert contributes nothing: the oracle with those weights zeroed
+    y = torch.empty_like(x_dev)
+    layer.moe.encode_decode(layer.pool, layer.offsets, slots, w, x_dev, y, None, layer.shared, gate)
+    layer.moe.status()
+    y_ref = layer.oracle_forward(x, ids_np, w.cpu().numpy(), skip_experts={3, 7})
+    assert rel_l2(y.float().cpu().numpy(), y_ref) <= TOL
+    layer.close()
+
+
+@pytest.mark.parametrize("status", [capi.IO_PENDING, capi.IO_FAILED])
+def test_failed_io_status_passes_the_shared_term_through(cuda_device, status):
+    """agreedFixupSkipsOnAFailedStatusWord: a batch that is not ready leaves y = residual."""
+    layer = Layer(small_config())
+    x = inputs(3, 128, seed=12)
+    y, ids, w, _ = layer.forward(x, io_status=status)
+    y_ref = layer.oracle_forward(x, ids, np.zeros_like(w))
+    assert rel_l2(y, y_ref) <= TOL
+    y2, _, _, _ = layer.forward(x, io_status=capi.IO_READY)
+    assert rel_l2(y2, layer.oracle_forward(x)) <= TOL
+    layer.close()
+
+
+def test_constant_block_known_answer(cuda_device):
+    """MoEFusedFFNTests constant block: every output is 2/(1+e^-2)."""
+    from test_oracle_kat import constant_blob
+    for bits in (4, 8):
+        cfg = small_config(weight_bits=bits, num_experts=8, top_k=8, has_shared=False, shared_gated=False)
+        layer = Layer(cfg)
+        blob = constant_blob(bits)
+        for e in range(8):
+            layer.pool.upload(e, blob)
+        x_dev = torch.ones((1, 128), dtype=torch.float32, device=layer.device)
+        slots = torch.arange(8, dtype=torch.int32, device=layer.device).reshape(1, 8)
+        w = torch.full((1, 8), 0.125, dtype=torch.float32, device=layer.device)
+        y = torch.empty_like(x_dev)
+        layer.moe.encode_decode(layer.pool, layer.offsets, slots, w, x_dev, y)
+        layer.moe.status()
+        assert (y.cpu().numpy() - 2 / (1 + np.exp(-2.0))).__abs__().max() < 0.01
+        layer.close()
+
+
+def test_pool_chunks_and_offset_cells(cuda_device):
+    """Cells addressed as base[cell / cells_per_chunk] + (cell % cells_per_chunk) * stride."""
+    layer = Layer(small_config(), first_cell=5, extra_cells=3, chunks=3)
+    check_layer(layer, inputs(4, 128, seed=13))
+    back = layer.pool.download(5 + 9, layer.block_bytes)
+    assert (back == layer.block(9)).all()
+    layer.close()
+
+
+def test_device_fill_is_the_host_function(cuda_device):
+    for kw in (dict(), dict(weight_bits=8), dict(group_size=32, meta_dtype=1, expert_bias=True, has_shared=False,
+                                                 shared_gated=False)):
+        cfg = small_config(**kw)
+        layer = Layer(cfg, seed=77, device_fill=True, layer=0)
+        for e in (0, 7, 15):
+            assert (layer.pool.download(e, layer.block_bytes) == fx.synth_block(cfg, 77, 0, e)).all()
+        layer.close()
+
+
+@pytest.mark.parametrize("T", [65, 100, 257])
+def test_prefill_small(cuda_device, T):
+    layer = Layer(small_config(max_tokens=512))
+    check_layer(layer, inputs(T, 128, seed=T), prefill=True)
+    layer.close()
+
+
+def test_prefill_equals_decode_on_the_same_rows(cuda_device):
+    layer = Layer(small_config(max_tokens=512, d=192, f=128, shared_f=128))
+    x = inputs(40, 192, seed=21)
+    a = layer.forward(x, prefill=False)[0]
+    b = layer.forward(x, prefill=True)[0]
+    assert rel_l2(a, b) <= 1e-6
+    layer.close()
+
+
+def test_prefill_skewed_routing_and_misses(cuda_device):
+    cfg = small_config(max_tokens=512, num_experts=32, top_k=4)
+    layer = Layer(cfg, logit_bias=fx.zipf_logit_bias(32, 1.1) * np.float32(0.05), router_sigma=0.01)
+    x = inputs(300, 128, seed=22)
+    check_layer(layer, x, prefill=True)
+    layer.close()
+
+
+def test_group_pairs_matches_the_oracle(cuda_device):
+    cfg = small_config(num_experts=256, top_k=8, d=128, max_tokens=4096)
+    layer = Layer(cfg, logit_bias=fx.zipf_logit_bias(256, 1.1), router_sigma=0.05)
+    T = 4096
+    x = inputs(T, 128, seed=23)
+    ids, w, _ = layer.route(to_act_tensor(x, cfg.act_dtype, layer.device))
+    sorted_pairs = torch.zeros((T * 8, 4), dtype=torch.int32, device=layer.device)
+    off = torch.zeros(256, dtype=torch.int32, device=layer.device)
+    cnt = torch.zeros(256, dtype=torch.int32, device=layer.device)
+    layer.moe.group_token_expert_pairs(ids, w, sorted_pairs, off, cnt)
+    layer.moe.status()
+    ids_np = ids.cpu().numpy().astype(np.uint32)
+    w16 = w.cpu().numpy().astype(np.float16).view(np.uint16).astype(np.uint32)
+    pairs = np.stack([np.repeat(np.arange(T, dtype=np.uint32), 8), ids_np.ravel(),
+                      np.tile(np.arange(8, dtype=np.uint32), T), w16.ravel()], axis=1)
+    rc, ref_sorted, ref_off, ref_cnt = O.group_pairs(pairs, T, 8, 256)
+    assert rc == 0
+    assert (sorted_pairs.cpu().numpy().astype(np.uint32) == ref_sorted).all()
+    assert (off.cpu().numpy().astype(np.uint32) == ref_off).all()
+    assert (cnt.cpu().numpy().astype(np.uint32) == ref_cnt).all()
+    assert ref_cnt.max() > 8 * ref_cnt[ref_cnt > 0].min()  # the skew is real
+    layer.close()
+
+
+def test_empty_and_out_of_range_calls(cuda_device):
+    layer = Layer(small_config(max_tokens=16))
+    x_dev = torch.zeros((0, 128), dtype=torch.float32, device=layer.device)
+    ids = torch.zeros((0, 4), dtype=torch.int32, device=layer.device)
+    w = torch.zeros((0, 4), dtype=torch.float32, device=layer.device)
+    g = torch.zeros((0,), dtype=torch.float32, device=layer.device)
+    layer.moe.encode_router(layer.router_ops, x_dev, ids, w, g, query_count=0, hidden_stride_elements=128)
+    layer.moe.encode_decode(layer.pool, layer.offsets, ids, w, x_dev, x_dev, None, layer.shared, g, query_count=0)
+    big = torch.zeros((17, 128), dtype=torch.float32, device=layer.device)
+    with pytest.raises(ShrikeError) as e:
+        layer.route(big)
+    assert e.value.code == capi.ERANGE
+    with pytest.raises(ShrikeError) as e:
+        layer.pool.upload(10_000, layer.block(0))
+    assert e.value.code == capi.ERANGE
+    with pytest.raises(ShrikeError) as e:  # a shared_gated handle must be given the gate
+        y = torch.zeros((1, 128), dtype=torch.float32, device=layer.device)
+        s = torch.zeros((1, 4), dtype=torch.int32, device=layer.device)
+        wt = torch.zeros((1, 4), dtype=torch.float32, device=layer.device)
+        layer.moe.encode_decode(layer.pool, layer.offsets, s, wt, y, y, None, layer.shared, None)
+    assert e.value.code == capi.EINVAL
+    layer.close()
+
+
+def test_slot_outside_the_pool_is_reported_not_followed(cuda_device):
+    layer = Layer(small_config(has_shared=False, shared_gated=False))
+    x_dev = torch.ones((1, 128), dtype=torch.float32, device=layer.device)
+    slots = torch.tensor([[0, 1, 2, 5000]], dtype=torch.int32, device=layer.device)
+    w = torch.full((1, 4), 0.25, dtype=torch.float32, device=layer.device)
+    y = torch.empty_like(x_dev)
+    layer.moe.encode_decode(layer.pool, layer.offsets, slots, w, x_dev, y)
+    with pytest.raises(ShrikeError) as e:
+        layer.moe.status()
+    assert e.value.code == capi.ERANGE
+    layer.moe.status()  # the word was cleared; the handle stays usable
+    layer.close()

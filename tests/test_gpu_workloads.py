@@ -1,0 +1,93 @@
+"""The benchmark workloads at their full layer shapes, against the oracle on the
+expert blocks the routing actually touches (downloaded from the device pool)."""
+import numpy as np
+import pytest
+
+from gpu_harness import Layer, inputs, rel_l2
+from shrike_b200 import capi, fixtures as fx
+
+pytestmark = pytest.mark.gpu
+
+TOL = 1e-3
+
+
+def run(layer: Layer, x, tol=TOL, **kw):
+    y, ids, w, _ = layer.forward(x, **kw)
+    ids_ref, w_ref, logits = layer.oracle_route(x)
+    assert (ids == ids_ref).all() and (w == w_ref).all()
+    y_ref = layer.oracle_forward(x, ids_ref, w_ref)
+    err = rel_l2(y, y_ref)
+    assert err <= tol, f"relative L2 {err:.3e}"
+    # how close the routing came to a flip: gap between the k-th and (k+1)-th score
+    srt = np.sort(logits, axis=1)[:, ::-1]
+    k = layer.cfg.top_k
+    return err, float((srt[:, k - 1] - srt[:, k]).min())
+
+
+@pytest.mark.parametrize("T", [1, 4, 16])
+def test_qwen_layer_decode(cuda_device, T):
+    """Single MoE layer, Qwen3.5-35B-A3B shape: block 1,769,472 B, top-8 of 256 + gated shared expert."""
+    cfg = fx.qwen_config(max_tokens=16, act_dtype=capi.DTYPE_FP32)
+    layer = Layer(cfg, seed=101, device_fill=True)
+    assert layer.block_bytes == 1_769_472
+    err, gap = run(layer, inputs(T, cfg.d, seed=T))
+    print(f"qwen T={T}: rel L2 {err:.2e}, min top-k gap {gap:.2e}")
+    layer.close()
+
+
+def test_qwen_layer_bf16_io_and_fp16_meta(cuda_device):
+    cfg = fx.qwen_config(max_tokens=16, act_dtype=capi.DTYPE_BF16, meta_dtype=capi.DTYPE_FP16)
+    layer = Layer(cfg, seed=102, device_fill=True)
+    run(layer, inputs(2, cfg.d, seed=9), tol=4e-3)  # bf16 store of y: 8 significant bits
+    layer.close()
+
+
+@pytest.mark.parametrize("group,T", [(32, 1), (32, 64), (64, 1)])
+def test_gpt_oss_layer(cuda_device, group, T):
+    """gpt-oss-20B shape: D = F = 2880, 32 experts top-4, additive biases, clamped SwiGLU, no shared expert."""
+    cfg = fx.gpt_oss_config(max_tokens=64, group_size=group, act_dtype=capi.DTYPE_FP32)
+    layer = Layer(cfg, seed=103, device_fill=True)
+    assert layer.block_bytes == (15_569_280 if group == 32 else 14_014_080)
+    err, gap = run(layer, inputs(T, cfg.d, seed=group + T))
+    print(f"gpt-oss g{group} T={T}: rel L2 {err:.2e}, min top-k gap {gap:.2e}")
+    layer.close()
+
+
+def test_kimi_layer_decode_and_prefill(cuda_device):
+    """Kimi-Linear shape: int8 g64, sigmoid router x2.446 with a selection-only bias, ungated shared expert."""
+    rng = np.random.default_rng(5)
+    cfg = fx.kimi_config(max_tokens=512, act_dtype=capi.DTYPE_FP32)
+    layer = Layer(cfg, seed=104, device_fill=True, logit_bias=rng.uniform(-0.1, 0.1, 256).astype(np.float32))
+    assert layer.block_bytes == 7_520_256
+    run(layer, inputs(16, cfg.d, seed=1))
+    run(layer, inputs(96, cfg.d, seed=2), prefill=True)
+    layer.close()
+
+
+def test_qwen_prefill_zipf_chunk(cuda_device):
+    """A slice of the ragged prefill workload: Zipf(1.1) prior on the router logits."""
+    cfg = fx.qwen_config(max_tokens=256, act_dtype=capi.DTYPE_FP32)
+    layer = Layer(cfg, seed=105, device_fill=True, logit_bias=fx.zipf_logit_bias(256, 1.1))
+    y, ids, w, _ = layer.forward(inputs(160, cfg.d, seed=3), prefill=True)
+    counts = np.bincount(ids.ravel(), minlength=256)
+    assert counts.max() >= 20 * max(1, np.median(counts[counts > 0]))
+    run(layer, inputs(160, cfg.d, seed=3), prefill=True)
+    layer.close()
+
+
+def test_layer_forward_host_round_trip(cuda_device):
+    """The host-buffer entry point gives what the device-pointer calls give."""
+    import torch
+    cfg = fx.qwen_config(max_tokens=16, act_dtype=capi.DTYPE_FP32, d=512, f=256, shared_f=256, num_experts=64)
+    layer = Layer(cfg, seed=106, device_fill=True)
+    x = inputs(5, cfg.d, seed=4)
+    y_dev, ids_dev, w_dev, _ = layer.forward(x)
+    x_host = torch.from_numpy(x.copy())
+    y_host = torch.empty_like(x_host)
+    ids_host = torch.zeros((5, 8), dtype=torch.int32)
+    w_host = torch.zeros((5, 8), dtype=torch.float32)
+    layer.moe.layer_forward_host(layer.pool, layer.offsets, 0, layer.router_ops, x_host, y_host, layer.shared,
+                                 ids_host, w_host)
+    assert (y_host.numpy() == y_dev).all()
+    assert (ids_host.numpy().astype(np.uint32) == ids_dev).all() and (w_host.numpy() == w_dev).all()
+    layer.close()
