@@ -372,6 +372,7 @@ int shrike_encode_router(shrike_moe* m, void* stream, const shrike_router_operan
                          uint32_t query_count, uint32_t hidden_stride_elements, uint32_t* out_indices,
                          float* out_weights, float* out_shared_gate) {
     if (!m) return SHRIKE_EINVAL;
+    if (query_count == 0) return SHRIKE_OK;
     if (!ops || !ops->weights || !hidden || !out_indices || !out_weights)
         return fail(m, SHRIKE_EINVAL, "router: null operand");
     const shrike_moe_config& c = m->cfg;
@@ -452,8 +453,8 @@ int shrike_encode_moe_decode(shrike_moe* m, void* stream, const shrike_pool* poo
                              const shrike_shared_expert* shared, const float* shared_gate,
                              const uint32_t* io_status, void* y, void* hidden) {
     if (!m) return SHRIKE_EINVAL;
-    if (!resolved_slots || !routing_weights || !x || !y) return fail(m, SHRIKE_EINVAL, "decode: null operand");
     if (query_count == 0) return SHRIKE_OK;
+    if (!resolved_slots || !routing_weights || !x || !y) return fail(m, SHRIKE_EINVAL, "decode: null operand");
     int rc = shrike_encode_decode_plan(m, stream, pool, resolved_slots, x, query_count, io_status);
     if (rc) return rc;
     rc = shrike_encode_phase1(m, stream, pool, routed_offsets, shared, query_count);
