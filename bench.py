@@ -210,19 +210,14 @@ class Workload:
         self.x0 = self.x_host.to(self.dev)
         self.hidden = torch.zeros_like(self.x0)
         self.y = torch.zeros_like(self.x0)
-        self.launches_per_step = layers * 6
+        self.launches_per_step = layers * 3
         torch.cuda.synchronize()
 
     def layers_on_device(self):
         """router -> classification -> plan -> phase 1 -> phase 2 for every layer; hidden carries on."""
         for l in range(self.L):
-            m = self.moes[l]
-            m.encode_router(self.routers[l], self.hidden, self.ids[l], self.w[l], self.gate[l])
-            m.encode_residency_classification(self.ids[l], 0, self.slots[l])
-            m.encode_decode_plan(self.pool, self.slots[l], self.hidden)
-            m.encode_phase1(self.pool, self.off, self.T, self.shared[l])
-            m.encode_phase2_reduce(self.pool, self.off, self.w[l], self.y, self.T, self.hidden, self.shared[l],
-                                   self.gate[l])
+            self.moes[l].encode_decode_layer(self.pool, self.off, 0, self.routers[l], self.hidden, self.y,
+                                             self.hidden, self.shared[l], self.ids[l], self.w[l])
 
     def step_resident(self):
         self.hidden.copy_(self.x0)
@@ -240,7 +235,7 @@ class Workload:
     def phase2_only(self):
         for l in range(self.L):
             self.moes[l].encode_phase2_reduce(self.pool, self.off, self.w[l], self.y, self.T, None, self.shared[l],
-                                              self.gate[l])
+                                              self.gate[l] if self.cfg.shared_gated else None)
 
     def capture(self, fn):
         torch = self.torch

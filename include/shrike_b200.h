@@ -120,6 +120,12 @@ const char* shrike_last_error(const shrike_moe* moe);
  * (the reference inspects commandBuffer.error, RealForwardRunner.swift:5360-5363). */
 int shrike_moe_status(shrike_moe* moe, void* stream);
 
+/* Diagnostics (the counterpart of SHRIKE_KERNEL_STATS, RealForwardRunner.swift:1305-1415):
+ * when given a device buffer of 4 u64 per phase-1 block, every block records the
+ * nanosecond timer at entry, after issuing its weight loads, after its last
+ * multiply-accumulate and at exit. NULL switches it off. */
+int shrike_debug_set_trace(shrike_moe* moe, uint64_t* trace_device_buffer);
+
 /* CPUExpertFFN.Offsets (CPUExpertFFN.swift:34-61) / Model.routedExpertOffsets
  * (ModelExpertIO.swift:69-94): offsets and unpadded size of one block. */
 int shrike_expert_offsets_make(const shrike_moe_config* config, int shared,
@@ -217,6 +223,33 @@ int shrike_encode_phase2_reduce(shrike_moe* moe, void* stream, const shrike_pool
                                 const shrike_expert_offsets* routed_offsets,
                                 const float* routing_weights, const shrike_shared_expert* shared,
                                 const float* shared_gate, uint32_t query_count, void* y, void* hidden);
+
+/* Decode fast path, query_count <= SHRIKE_MAX_DECODE_TOKENS: encodeRouter +
+ * encodeResidencyClassification + the work lists of the decode plan in ONE
+ * launch (the block that finishes its logits last does the selection; no block
+ * waits on another). Same outputs as the three separate calls, bit for bit;
+ * out_resolved_slots and out_counts may be NULL. Must be followed by
+ * shrike_encode_phase1 / shrike_encode_phase2_reduce on the same handle. */
+int shrike_encode_route_decode(shrike_moe* moe, void* stream, const shrike_router_operands* operands,
+                               const uint64_t* residency_table_row, const shrike_pool* pool,
+                               const void* hidden, uint32_t query_count,
+                               uint32_t hidden_stride_elements, const uint32_t* io_status,
+                               uint32_t* out_indices, float* out_weights, float* out_shared_gate,
+                               uint32_t* out_resolved_slots, uint32_t* out_counts);
+
+/* One decode layer in three launches chained with programmatic dependent
+ * launch (route -> phase 1 -> phase 2; each starts its weight fetch while its
+ * predecessor drains): what encodeDecodeTailStage's router + classification
+ * (RealForwardRunner.swift:2834) and encodeSpeculativeRouted
+ * (RealForwardRunner.swift:5520-5572) encode for one routed layer.
+ * out_indices / out_weights may be NULL. */
+int shrike_encode_decode_layer(shrike_moe* moe, void* stream, const shrike_pool* pool,
+                               const shrike_expert_offsets* routed_offsets,
+                               const uint64_t* residency_table_row,
+                               const shrike_router_operands* router,
+                               const shrike_shared_expert* shared, const void* x, uint32_t query_count,
+                               const uint32_t* io_status, uint32_t* out_indices, float* out_weights,
+                               void* y, void* hidden);
 
 /* Prefill, any query_count <= max_tokens. Stands for buildPrefillRoutes
  * (RealForwardRunner.swift:4305), encodeGroupedExpertGEMMs

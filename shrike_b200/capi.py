@@ -59,6 +59,7 @@ SIGNATURES = {
     "shrike_moe_destroy": (None, [_P]),
     "shrike_last_error": (C.c_char_p, [_P]),
     "shrike_moe_status": (_INT, [_P, _P]),
+    "shrike_debug_set_trace": (_INT, [_P, _P]),
     "shrike_expert_offsets_make": (_INT, [C.POINTER(MoEConfig), _INT, C.POINTER(ExpertOffsets), C.POINTER(_U64)]),
     "shrike_pool_create": (_INT, [_P, _U32, _U64, _U32, C.POINTER(_P)]),
     "shrike_pool_destroy": (None, [_P]),
@@ -77,6 +78,10 @@ SIGNATURES = {
                                            _U32, _P, _P]),
     "shrike_encode_moe_decode": (_INT, [_P, _P, _P, C.POINTER(ExpertOffsets), _P, _P, _P, _U32,
                                         C.POINTER(SharedExpert), _P, _P, _P, _P]),
+    "shrike_encode_route_decode": (_INT, [_P, _P, C.POINTER(RouterOperands), _P, _P, _P, _U32, _U32, _P, _P, _P, _P,
+                                          _P, _P]),
+    "shrike_encode_decode_layer": (_INT, [_P, _P, _P, C.POINTER(ExpertOffsets), _P, C.POINTER(RouterOperands),
+                                          C.POINTER(SharedExpert), _P, _U32, _P, _P, _P, _P, _P]),
     "shrike_encode_moe_prefill": (_INT, [_P, _P, _P, C.POINTER(ExpertOffsets), _P, _P, _P, _P, _U32,
                                          C.POINTER(SharedExpert), _P, _P, _P]),
     "shrike_encode_group_pairs": (_INT, [_P, _P, _P, _P, _U32, _P, _P, _P]),

@@ -92,7 +92,7 @@ cudaError_t dev_alloc(P** p, size_t bytes) {
 }
 
 void free_workspace(Workspace& w) {
-    void* ptrs[] = {w.logits, w.xh, w.acts, w.acts_shared, w.sorted, w.inst, w.n_inst, w.status, w.block_hist,
+    void* ptrs[] = {w.done_counter, w.xsum, w.logits, w.xh, w.acts, w.acts_shared, w.sorted, w.inst, w.n_inst, w.status, w.block_hist,
                     w.expert_offsets, w.expert_counts, w.slot_of_expert, w.partials, w.x_dev, w.y_dev,
                     w.ids_dev, w.w_dev, w.gate_dev, w.slots_dev, w.counts_dev};
     for (void* p : ptrs)
@@ -123,8 +123,10 @@ int fill_expert_args(shrike_moe* m, const shrike_pool* pool, const shrike_expert
     a.d = c.d; a.f = c.f; a.f_shared = c.has_shared ? c.shared_f : 0; a.top_k = c.top_k;
     a.activation = c.activation; a.expert_bias = c.expert_bias; a.act_dtype = c.act_dtype;
     a.inst = m->ws.inst; a.n_inst = m->ws.n_inst; a.sorted = m->ws.sorted; a.xh = m->ws.xh;
+    a.xsum = m->ws.xsum;
     a.acts = m->ws.acts; a.acts_shared = m->ws.acts_shared;
     a.route_w = weights; a.shared_gate = shared_gate; a.status = m->ws.status;
+    a.trace = m->trace;
     return SHRIKE_OK;
 }
 
@@ -179,12 +181,14 @@ int shrike_moe_create(const shrike_moe_config* config, int device, shrike_moe** 
     auto A = [&](auto** p, size_t bytes) { if (ok && dev_alloc(p, bytes) != cudaSuccess) ok = false; };
     A(&w.logits, T * c.num_experts * 4);
     A(&w.xh, T * c.d * 2);
+    A(&w.xsum, T * (c.d / c.group_size) * 4);
     A(&w.acts, T * K * c.f * 2);
     A(&w.acts_shared, c.has_shared ? T * c.shared_f * 2 : 0);
     A(&w.sorted, T * K * 4);
     A(&w.inst, (size_t)w.max_inst * sizeof(Instance));
     A(&w.n_inst, 4);
     A(&w.status, 4);
+    A(&w.done_counter, 4);
     A(&w.block_hist, ((T + 127) / 128) * c.num_experts * 4);
     A(&w.expert_offsets, c.num_experts * 4);
     A(&w.expert_counts, c.num_experts * 4);
@@ -204,6 +208,7 @@ int shrike_moe_create(const shrike_moe_config* config, int device, shrike_moe** 
         return fail(nullptr, SHRIKE_ENOMEM, "device allocation of the workspace failed");
     }
     cudaMemset(w.status, 0, 4);
+    cudaMemset(w.done_counter, 0, 4);
     cudaMemset(w.n_inst, 0, 4);
     *out = m;
     return SHRIKE_OK;
@@ -227,6 +232,12 @@ int shrike_moe_status(shrike_moe* m, void* stream) {
         if (st == kStatusWaitTimeout) return fail(m, SHRIKE_ETIMEDOUT, "a device-side wait gave up");
         return fail(m, SHRIKE_ERANGE, "a kernel met a slot id outside the pool");
     }
+    return SHRIKE_OK;
+}
+
+int shrike_debug_set_trace(shrike_moe* m, uint64_t* trace_device_buffer) {
+    if (!m) return SHRIKE_EINVAL;
+    m->trace = trace_device_buffer;
     return SHRIKE_OK;
 }
 
@@ -428,7 +439,7 @@ int shrike_encode_phase1(shrike_moe* m, void* stream, const shrike_pool* pool,
     ExpertArgs a;
     int rc = fill_expert_args(m, pool, routed_offsets, shared, nullptr, nullptr, a, false);
     if (rc) return rc;
-    CU(launch_phase1(m, (cudaStream_t)stream, a, max_instances(m->cfg, query_count)));
+    CU(launch_phase1(m, (cudaStream_t)stream, a, max_instances(m->cfg, query_count), false));
     return SHRIKE_OK;
 }
 
@@ -443,7 +454,7 @@ int shrike_encode_phase2_reduce(shrike_moe* m, void* stream, const shrike_pool* 
     ExpertArgs a;
     int rc = fill_expert_args(m, pool, routed_offsets, shared, routing_weights, shared_gate, a, true);
     if (rc) return rc;
-    CU(launch_phase2(m, (cudaStream_t)stream, a, query_count, y, hidden));
+    CU(launch_phase2(m, (cudaStream_t)stream, a, query_count, max_instances(m->cfg, query_count), y, hidden, false));
     return SHRIKE_OK;
 }
 
@@ -461,6 +472,56 @@ int shrike_encode_moe_decode(shrike_moe* m, void* stream, const shrike_pool* poo
     if (rc) return rc;
     return shrike_encode_phase2_reduce(m, stream, pool, routed_offsets, routing_weights, shared, shared_gate,
                                        query_count, y, hidden);
+}
+
+int shrike_encode_route_decode(shrike_moe* m, void* stream, const shrike_router_operands* ops,
+                               const uint64_t* residency_table_row, const shrike_pool* pool,
+                               const void* hidden, uint32_t query_count, uint32_t hidden_stride_elements,
+                               const uint32_t* io_status, uint32_t* out_indices, float* out_weights,
+                               float* out_shared_gate, uint32_t* out_resolved_slots, uint32_t* out_counts) {
+    if (!m) return SHRIKE_EINVAL;
+    if (query_count == 0) return SHRIKE_OK;
+    if (!ops || !ops->weights || !hidden || !out_indices || !out_weights || !residency_table_row || !pool)
+        return fail(m, SHRIKE_EINVAL, "route_decode: null operand");
+    const shrike_moe_config& c = m->cfg;
+    if (c.router_weight_bits != 0 && (!ops->scales || !ops->biases))
+        return fail(m, SHRIKE_EINVAL, "router: affine weights need scales and biases");
+    if (query_count > SHRIKE_MAX_DECODE_TOKENS || query_count > c.max_tokens)
+        return fail(m, SHRIKE_ERANGE, "route_decode handles at most %u rows", SHRIKE_MAX_DECODE_TOKENS);
+    if (hidden_stride_elements < c.d || hidden_stride_elements % 4 != 0)
+        return fail(m, SHRIKE_EINVAL, "hidden stride must be >= d and a multiple of 4 elements");
+    if (c.shared_gated && (!ops->shared_gate || !out_shared_gate))
+        return fail(m, SHRIKE_EINVAL, "router: a shared_gated handle needs shared_gate and out_shared_gate");
+    CU(launch_route_fused(m, (cudaStream_t)stream, *ops, hidden, query_count, hidden_stride_elements,
+                          residency_table_row, pool->view.cells, io_status, out_indices, out_weights,
+                          out_shared_gate, out_resolved_slots, out_counts, true));
+    return SHRIKE_OK;
+}
+
+int shrike_encode_decode_layer(shrike_moe* m, void* stream, const shrike_pool* pool,
+                               const shrike_expert_offsets* routed_offsets,
+                               const uint64_t* residency_table_row, const shrike_router_operands* router,
+                               const shrike_shared_expert* shared, const void* x, uint32_t query_count,
+                               const uint32_t* io_status, uint32_t* out_indices, float* out_weights, void* y,
+                               void* hidden) {
+    if (!m) return SHRIKE_EINVAL;
+    if (query_count == 0) return SHRIKE_OK;
+    if (!x || !y) return fail(m, SHRIKE_EINVAL, "decode_layer: null operand");
+    Workspace& w = m->ws;
+    uint32_t* ids = out_indices ? out_indices : w.ids_dev;
+    float* wt = out_weights ? out_weights : w.w_dev;
+    float* gate = m->cfg.shared_gated ? w.gate_dev : nullptr;
+    int rc = shrike_encode_route_decode(m, stream, router, residency_table_row, pool, x, query_count, m->cfg.d,
+                                        io_status, ids, wt, gate, w.slots_dev, nullptr);
+    if (rc) return rc;
+    ExpertArgs a;
+    rc = fill_expert_args(m, pool, routed_offsets, shared, wt, gate, a);
+    if (rc) return rc;
+    const uint32_t mi = max_instances(m->cfg, query_count);
+    // phase 1 and phase 2 may start before their predecessor has drained
+    CU(launch_phase1(m, (cudaStream_t)stream, a, mi, true));
+    CU(launch_phase2(m, (cudaStream_t)stream, a, query_count, mi, y, hidden, true));
+    return SHRIKE_OK;
 }
 
 int shrike_encode_moe_prefill(shrike_moe* m, void* stream, const shrike_pool* pool,
@@ -482,7 +543,7 @@ int shrike_encode_moe_prefill(shrike_moe* m, void* stream, const shrike_pool* po
     const uint32_t mi = max_instances(m->cfg, query_count);
     CU(launch_prefill_plan(m, st, topk_indices, resolved_slots, x, query_count, m->cfg.has_shared != 0,
                            pool->view.cells));
-    CU(launch_phase1(m, st, a, mi));
+    CU(launch_phase1(m, st, a, mi, false));
     float* partial_shared = m->ws.partials + (size_t)m->cfg.max_tokens * m->cfg.top_k * m->cfg.d;
     CU(launch_phase2_partials(m, st, a, mi, m->ws.partials, partial_shared));
     CU(launch_prefill_combine(m, st, routing_weights, shared_gate, resolved_slots, query_count, y, hidden));
@@ -516,17 +577,19 @@ int shrike_moe_layer_forward_host(shrike_moe* m, void* stream, const shrike_pool
     const size_t bytes = (size_t)query_count * c.d * act_bytes(c.act_dtype);
     CU(cudaMemcpyAsync(w.x_dev, x_host, bytes, cudaMemcpyHostToDevice, st));
     float* gate = c.shared_gated ? w.gate_dev : nullptr;
-    int rc = shrike_encode_router(m, stream, router, w.x_dev, query_count, c.d, w.ids_dev, w.w_dev, gate);
-    if (rc) return rc;
-    rc = shrike_encode_residency_classification(m, stream, w.ids_dev, residency_table_row, query_count,
-                                                w.slots_dev, w.counts_dev, nullptr, nullptr);
-    if (rc) return rc;
-    if (query_count <= SHRIKE_MAX_DECODE_TOKENS)
-        rc = shrike_encode_moe_decode(m, stream, pool, routed_offsets, w.slots_dev, w.w_dev, w.x_dev, query_count,
-                                      shared, gate, nullptr, w.y_dev, nullptr);
-    else
+    int rc;
+    if (query_count <= SHRIKE_MAX_DECODE_TOKENS) {
+        rc = shrike_encode_decode_layer(m, stream, pool, routed_offsets, residency_table_row, router, shared,
+                                        w.x_dev, query_count, nullptr, w.ids_dev, w.w_dev, w.y_dev, nullptr);
+    } else {
+        rc = shrike_encode_router(m, stream, router, w.x_dev, query_count, c.d, w.ids_dev, w.w_dev, gate);
+        if (rc) return rc;
+        rc = shrike_encode_residency_classification(m, stream, w.ids_dev, residency_table_row, query_count,
+                                                    w.slots_dev, w.counts_dev, nullptr, nullptr);
+        if (rc) return rc;
         rc = shrike_encode_moe_prefill(m, stream, pool, routed_offsets, w.ids_dev, w.slots_dev, w.w_dev, w.x_dev,
                                        query_count, shared, gate, w.y_dev, nullptr);
+    }
     if (rc) return rc;
     CU(cudaMemcpyAsync(y_host, w.y_dev, bytes, cudaMemcpyDeviceToHost, st));
     if (ids_host) CU(cudaMemcpyAsync(ids_host, w.ids_dev, (size_t)query_count * c.top_k * 4, cudaMemcpyDeviceToHost, st));

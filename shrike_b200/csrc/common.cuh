@@ -134,6 +134,12 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
     return false;
 }
 
+__device__ __forceinline__ uint64_t globaltimer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+
 // ---- programmatic dependent launch ---------------------------------------
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() {
@@ -150,6 +156,51 @@ __host__ __device__ __forceinline__ uint32_t perm_index(uint32_t i, bool int4) {
     const uint32_t e = i & 7u;
     const uint32_t pos = int4 ? (((e & 3u) << 1) | (e >> 2)) : e;
     return (i & ~7u) | pos;
+}
+
+
+// Converts the aligned block of 8 activations `blk` of a row to the fp16
+// operand layout and returns the sum of the 8 rounded values. Thread-to-block
+// assignment is up to the caller; group sums are formed with xprep_group_sum.
+__device__ __forceinline__ float xprep_block8(const void* xrow, uint32_t blk, uint32_t dt, bool int4,
+                                              uint16_t* xh_row) {
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = load_act(xrow, (size_t)blk * 8 + j, dt);
+    __half h[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) h[j] = __float2half_rn(v[j]);
+    float sum = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) sum += __half2float(h[j]);
+    uint16_t o[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[perm_index(j, int4)] = __half_as_ushort(h[j]);
+    uint4 pk;
+    pk.x = o[0] | ((uint32_t)o[1] << 16); pk.y = o[2] | ((uint32_t)o[3] << 16);
+    pk.z = o[4] | ((uint32_t)o[5] << 16); pk.w = o[6] | ((uint32_t)o[7] << 16);
+    *(uint4*)(xh_row + (size_t)blk * 8) = pk;
+    return sum;
+}
+
+// All rows' blocks, block index i = row * (d/8) + blk handled by consecutive
+// threads [lo, hi) of the calling kernel (lo a multiple of 32 per warp), and
+// the per-group sums: the group/8 consecutive lanes of a group add up with
+// shuffles. Every lane of a warp must call this together.
+__device__ __forceinline__ void xprep_item(const void* x, size_t row_stride_bytes, uint32_t d, uint32_t group,
+                                           uint32_t dt, bool int4, uint32_t item, bool valid, uint16_t* xh,
+                                           float* xsum) {
+    const uint32_t per_row = d / 8;
+    float sum = 0.f;
+    uint32_t row = 0, blk = 0;
+    if (valid) {
+        row = item / per_row;
+        blk = item - row * per_row;
+        sum = xprep_block8((const uint8_t*)x + (size_t)row * row_stride_bytes, blk, dt, int4, xh + (size_t)row * d);
+    }
+    const uint32_t lanes = group / 8;  // 8 or 4 lanes per group
+    for (uint32_t o = 1; o < lanes; o <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if (valid && (blk & (lanes - 1)) == 0) xsum[(size_t)row * (d / group) + blk / lanes] = sum;
 }
 
 }  // namespace shrike

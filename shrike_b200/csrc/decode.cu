@@ -24,6 +24,10 @@
 
 namespace shrike {
 
+#ifdef SHRIKE_DEBUG_KNOB
+__device__ uint32_t g_debug_knob = 0;
+#endif
+
 template <int BITS, int GROUP>
 struct QT {
     static constexpr int kWords = GROUP * BITS / 128;  // u32 per thread, row and group
@@ -73,82 +77,141 @@ __device__ __forceinline__ void load_bfrag(const uint16_t* p, uint32_t (&b)[G / 
 }
 
 // One group of NMAT matrices (rows g and g+8 of each) against one B fragment.
-// c[mat] = sum((q-Z)*x), xs = column sums of x (identical in every row).
-template <int BITS, int GROUP, int NMAT>
+// c[mat] = sum((q-Z)*x); with ONES also xs = column sums of x (identical in
+// every row), otherwise the caller supplies them.
+template <int BITS, int GROUP, int NMAT, bool ONES>
 __device__ __forceinline__ void group_mma(const uint32_t (&raw)[NMAT][2][QT<BITS, GROUP>::kWords],
                                           const uint32_t (&b)[QT<BITS, GROUP>::kBRegs],
                                           float (&c)[NMAT][4], float (&xs)[4]) {
     constexpr uint32_t kOnes = 0x3C003C00u;
+#ifdef SHRIKE_DEBUG_KNOB
+    if (g_debug_knob & 2) {  // no dequant, no MMA: keep the loads alive
+#pragma unroll
+        for (int mat = 0; mat < NMAT; ++mat)
+#pragma unroll
+            for (int w = 0; w < QT<BITS, GROUP>::kWords; ++w)
+                c[mat][0] += __uint_as_float((raw[mat][0][w] ^ raw[mat][1][w] ^ b[w]) & 0x3fffffffu);
+        return;
+    }
+#endif
 #pragma unroll
     for (int m = 0; m < QT<BITS, GROUP>::kMmas; ++m) {
         const uint32_t b0 = b[2 * m], b1 = b[2 * m + 1];
-        mma_16816(xs, kOnes, kOnes, kOnes, kOnes, b0, b1);
+        if constexpr (ONES) mma_16816(xs, kOnes, kOnes, kOnes, kOnes, b0, b1);
 #pragma unroll
         for (int mat = 0; mat < NMAT; ++mat) {
             uint32_t lo0, hi0, lo1, hi1;
             unpack_step<BITS>(raw[mat][0], m, lo0, hi0);
             unpack_step<BITS>(raw[mat][1], m, lo1, hi1);
+#ifdef SHRIKE_DEBUG_KNOB
+            if (g_debug_knob & 1) { c[mat][0] += __uint_as_float((lo0 ^ lo1 ^ hi0 ^ hi1 ^ b0 ^ b1) & 0x3fffffffu); continue; }
+#endif
             mma_16816(c[mat], lo0, lo1, hi0, hi1, b0, b1);
+        }
+    }
+}
+
+// Weight words of up to kBatch groups (g0, g0+gstep, ... < gend) of NMAT
+// matrices, rows g and g+8: all loads are issued before any is used.
+template <int BITS, int GROUP, int NMAT>
+__device__ __forceinline__ void load_batch(const uint8_t* (&wrow)[NMAT][2], uint32_t g0, uint32_t gstep,
+                                           uint32_t gend,
+                                           uint32_t (&raw)[QT<BITS, GROUP>::kBatch][NMAT][2][QT<BITS, GROUP>::kWords]) {
+    using Q = QT<BITS, GROUP>;
+    constexpr uint32_t kGroupBytes = GROUP * BITS / 8;
+#pragma unroll
+    for (int i = 0; i < Q::kBatch; ++i) {
+        const uint32_t grp = g0 + i * gstep;
+        if (grp < gend) {
+#pragma unroll
+            for (int mat = 0; mat < NMAT; ++mat) {
+                load_words<Q::kWords>(wrow[mat][0] + (size_t)grp * kGroupBytes, raw[i][mat][0]);
+                load_words<Q::kWords>(wrow[mat][1] + (size_t)grp * kGroupBytes, raw[i][mat][1]);
+            }
+        }
+    }
+}
+
+// The activation fragments of the same groups.
+template <int BITS, int GROUP>
+__device__ __forceinline__ void load_bfrags(const uint16_t* xrow, uint32_t g0, uint32_t gstep, uint32_t gend,
+                                            uint32_t t,
+                                            uint32_t (&bf)[QT<BITS, GROUP>::kBatch][QT<BITS, GROUP>::kBRegs]) {
+#pragma unroll
+    for (int i = 0; i < QT<BITS, GROUP>::kBatch; ++i) {
+        const uint32_t grp = g0 + i * gstep;
+        if (grp < gend) load_bfrag<GROUP>(xrow + (size_t)grp * GROUP + t * (GROUP / 4), bf[i]);
+    }
+}
+
+// tot += scale * sum((q-Z)x) + (bias + Z*scale) * sum(x) for every group of the batch.
+// s_sm/b_sm[mat]: the tile's [16 x G] scales / biases in shared memory.
+template <int BITS, int GROUP, int META, int NMAT, bool ONES>
+__device__ __forceinline__ void compute_batch(
+    const uint32_t (&raw)[QT<BITS, GROUP>::kBatch][NMAT][2][QT<BITS, GROUP>::kWords],
+    const uint32_t (&bf)[QT<BITS, GROUP>::kBatch][QT<BITS, GROUP>::kBRegs],
+    const float (&xsv)[QT<BITS, GROUP>::kBatch][2], const uint16_t* (&s_sm)[NMAT],
+    const uint16_t* (&b_sm)[NMAT], uint32_t G, uint32_t g0, uint32_t gstep, uint32_t gend, uint32_t g,
+    float (&tot)[NMAT][4]) {
+    using Q = QT<BITS, GROUP>;
+#pragma unroll
+    for (int i = 0; i < Q::kBatch; ++i) {
+        const uint32_t grp = g0 + i * gstep;
+        if (grp < gend) {
+            float c[NMAT][4];
+            float xs[4] = {0.f, 0.f, 0.f, 0.f};
+            if constexpr (!ONES) { xs[0] = xsv[i][0]; xs[1] = xsv[i][1]; }
+#pragma unroll
+            for (int mat = 0; mat < NMAT; ++mat) c[mat][0] = c[mat][1] = c[mat][2] = c[mat][3] = 0.f;
+            group_mma<BITS, GROUP, NMAT, ONES>(raw[i], bf[i], c, xs);
+#pragma unroll
+            for (int mat = 0; mat < NMAT; ++mat) {
+                const float s0 = meta_to_f32<META>(s_sm[mat][g * G + grp]);
+                const float s1 = meta_to_f32<META>(s_sm[mat][(g + 8) * G + grp]);
+                const float z0 = fmaf(Q::kZero, s0, meta_to_f32<META>(b_sm[mat][g * G + grp]));
+                const float z1 = fmaf(Q::kZero, s1, meta_to_f32<META>(b_sm[mat][(g + 8) * G + grp]));
+                tot[mat][0] = fmaf(z0, xs[0], fmaf(s0, c[mat][0], tot[mat][0]));
+                tot[mat][1] = fmaf(z0, xs[1], fmaf(s0, c[mat][1], tot[mat][1]));
+                tot[mat][2] = fmaf(z1, xs[0], fmaf(s1, c[mat][2], tot[mat][2]));
+                tot[mat][3] = fmaf(z1, xs[1], fmaf(s1, c[mat][3], tot[mat][3]));
+            }
         }
     }
 }
 
 // Accumulates groups gbeg, gbeg+gstep, ... < gend of NMAT matrices into tot.
 // wrow[mat][r]: this thread's byte pointer into row g+8r of the tile at group 0.
-// s_sm/b_sm[mat]: the tile's [16 x G] scales / biases in shared memory.
-template <int BITS, int GROUP, int META, int NMAT>
-__device__ __forceinline__ void tile_accumulate(const uint8_t* const (&wrow)[NMAT][2],
-                                                const uint16_t* const (&s_sm)[NMAT],
-                                                const uint16_t* const (&b_sm)[NMAT],
-                                                const uint16_t* xrow, uint32_t G, uint32_t gbeg,
-                                                uint32_t gend, uint32_t gstep, uint32_t g, uint32_t t,
-                                                uint64_t* bar, uint32_t parity, uint32_t* status,
-                                                float (&tot)[NMAT][4]) {
+// With `preloaded` the first batch's weight words are already in `raw`.
+// ONES: the per-group activation sums come out of the tensor cores; otherwise
+// they are read from the tables xs0 / xs1 (one fp32 per group, for the two
+// columns this thread accumulates).
+template <int BITS, int GROUP, int META, int NMAT, bool ONES>
+__device__ __forceinline__ void tile_accumulate(
+    const uint8_t* (&wrow)[NMAT][2], const uint16_t* (&s_sm)[NMAT], const uint16_t* (&b_sm)[NMAT],
+    const uint16_t* xrow, uint32_t G, uint32_t gbeg, uint32_t gend, uint32_t gstep, uint32_t g, uint32_t t,
+    uint64_t* bar, uint32_t parity, uint32_t* status, float (&tot)[NMAT][4], bool preloaded,
+    uint32_t (&raw)[QT<BITS, GROUP>::kBatch][NMAT][2][QT<BITS, GROUP>::kWords], const float* xs0 = nullptr,
+    const float* xs1 = nullptr) {
     using Q = QT<BITS, GROUP>;
-    constexpr uint32_t kGroupBytes = GROUP * BITS / 8;
     bool waited = false;
     for (uint32_t g0 = gbeg; g0 < gend; g0 += gstep * Q::kBatch) {
-        uint32_t raw[Q::kBatch][NMAT][2][Q::kWords];
+        if (!(preloaded && g0 == gbeg)) load_batch<BITS, GROUP, NMAT>(wrow, g0, gstep, gend, raw);
+        uint32_t bf[Q::kBatch][Q::kBRegs];
+        load_bfrags<BITS, GROUP>(xrow, g0, gstep, gend, t, bf);
+        float xsv[Q::kBatch][2];
+        if constexpr (!ONES) {
 #pragma unroll
-        for (int i = 0; i < Q::kBatch; ++i) {
-            const uint32_t grp = g0 + i * gstep;
-            if (grp < gend) {
-#pragma unroll
-                for (int mat = 0; mat < NMAT; ++mat) {
-                    load_words<Q::kWords>(wrow[mat][0] + (size_t)grp * kGroupBytes, raw[i][mat][0]);
-                    load_words<Q::kWords>(wrow[mat][1] + (size_t)grp * kGroupBytes, raw[i][mat][1]);
-                }
+            for (int i = 0; i < Q::kBatch; ++i) {
+                const uint32_t grp = g0 + i * gstep;
+                if (grp < gend) { xsv[i][0] = __ldg(xs0 + grp); xsv[i][1] = __ldg(xs1 + grp); }
             }
         }
         if (!waited) {
-            // the scales arrive while the weight loads are in flight
+            // the scales arrive (TMA) while the weight loads are in flight
             if (!mbar_wait_bounded(bar, parity)) report_status(status, kStatusWaitTimeout);
             waited = true;
         }
-#pragma unroll
-        for (int i = 0; i < Q::kBatch; ++i) {
-            const uint32_t grp = g0 + i * gstep;
-            if (grp < gend) {
-                uint32_t bf[Q::kBRegs];
-                load_bfrag<GROUP>(xrow + (size_t)grp * GROUP + t * (GROUP / 4), bf);
-                float c[NMAT][4];
-                float xs[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-                for (int mat = 0; mat < NMAT; ++mat) c[mat][0] = c[mat][1] = c[mat][2] = c[mat][3] = 0.f;
-                group_mma<BITS, GROUP, NMAT>(raw[i], bf, c, xs);
-#pragma unroll
-                for (int mat = 0; mat < NMAT; ++mat) {
-                    const float s0 = meta_to_f32<META>(s_sm[mat][g * G + grp]);
-                    const float s1 = meta_to_f32<META>(s_sm[mat][(g + 8) * G + grp]);
-                    const float z0 = fmaf(Q::kZero, s0, meta_to_f32<META>(b_sm[mat][g * G + grp]));
-                    const float z1 = fmaf(Q::kZero, s1, meta_to_f32<META>(b_sm[mat][(g + 8) * G + grp]));
-                    tot[mat][0] = fmaf(z0, xs[0], fmaf(s0, c[mat][0], tot[mat][0]));
-                    tot[mat][1] = fmaf(z0, xs[1], fmaf(s0, c[mat][1], tot[mat][1]));
-                    tot[mat][2] = fmaf(z1, xs[0], fmaf(s1, c[mat][2], tot[mat][2]));
-                    tot[mat][3] = fmaf(z1, xs[1], fmaf(s1, c[mat][3], tot[mat][3]));
-                }
-            }
-        }
+        compute_batch<BITS, GROUP, META, NMAT, ONES>(raw, bf, xsv, s_sm, b_sm, G, g0, gstep, gend, g, tot);
     }
     if (!waited && !mbar_wait_bounded(bar, parity)) report_status(status, kStatusWaitTimeout);
 }
@@ -171,13 +234,38 @@ __device__ __forceinline__ float glu(float gate, float up, uint32_t activation) 
 
 constexpr int kP1Warps = 8;
 
-// grid (max(f, f_shared)/16, max instances); block 256.
+__device__ __forceinline__ Instance load_instance(const Instance* p) {
+    const uint4* q = (const uint4*)p;
+    const uint4 a = q[0], b = q[1], c = q[2];
+    Instance in;
+    in.kind = a.x; in.slot = a.y; in.first = a.z; in.count = a.w;
+    in.pair[0] = b.x; in.pair[1] = b.y; in.pair[2] = b.z; in.pair[3] = b.w;
+    in.pair[4] = c.x; in.pair[5] = c.y; in.pair[6] = c.z; in.pair[7] = c.w;
+    return in;
+}
+
+__device__ __forceinline__ uint32_t pick(const uint32_t (&v)[8], uint32_t i) {
+    uint32_t r = v[0];
+#pragma unroll
+    for (int j = 1; j < 8; ++j) r = i == (uint32_t)j ? v[j] : r;
+    return r;
+}
+
+// grid (max(f, f_shared)/16, max instances); block 256. The eight warps split
+// K by groups (warp w takes groups w, w+8, ...).
 template <int BITS, int GROUP, int META>
 __global__ void __launch_bounds__(kP1Warps * 32) phase1_kernel(const ExpertArgs a) {
+    using Q = QT<BITS, GROUP>;
     extern __shared__ __align__(16) uint8_t smem[];
     const uint32_t ii = blockIdx.y;
-    if (ii >= *a.n_inst) return;
-    const Instance in = a.inst[ii];
+    const uint64_t t_start = a.trace ? globaltimer_ns() : 0;
+    // the work lists come from the kernel launched just before this one
+    pdl_wait();
+    const uint32_t n_inst = *a.n_inst;
+    const Instance in = load_instance(a.inst + ii);
+    if (ii >= n_inst) return;
+    const uint64_t t_inst = a.trace ? globaltimer_ns() : 0;
+    pdl_launch_dependents();
     const bool shared = in.kind == 1;
     const uint32_t F = shared ? a.f_shared : a.f;
     const uint32_t f0 = blockIdx.x * 16;
@@ -186,6 +274,19 @@ __global__ void __launch_bounds__(kP1Warps * 32) phase1_kernel(const ExpertArgs 
     const uint8_t* base = shared ? a.shared_block : pool_cell_base(a.pool, in.slot);
     const uint32_t D = a.d, G = D / GROUP;
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+
+    // weight words first: they are the long pole
+    const size_t row_bytes = (size_t)D * BITS / 8;
+    const uint32_t toff = t * Q::kWords * 4;
+    const uint8_t* wrow[2][2];
+#pragma unroll
+    for (int mat = 0; mat < 2; ++mat) {
+        wrow[mat][0] = base + off.w[mat] + (size_t)(f0 + g) * row_bytes + toff;
+        wrow[mat][1] = base + off.w[mat] + (size_t)(f0 + g + 8) * row_bytes + toff;
+    }
+    uint32_t raw[Q::kBatch][2][2][Q::kWords];
+    load_batch<BITS, GROUP, 2>(wrow, warp, kP1Warps, G, raw);
+    const uint64_t t_loads = a.trace ? globaltimer_ns() : 0;
 
     // shared memory: [gate s][gate b][up s][up b] (16*G u16 each) | ab gate, ab up (16 u16 each)
     // | mbarrier | cross-warp reduction buffer
@@ -202,9 +303,6 @@ __global__ void __launch_bounds__(kP1Warps * 32) phase1_kernel(const ExpertArgs 
     if (tid == 0) {
         mbar_init(bar, 1);
         fence_mbar_init();
-    }
-    __syncthreads();
-    if (tid == 0) {
         const uint32_t ab_bytes = a.expert_bias ? 64u : 0u;
         mbar_expect_tx(bar, 4 * meta_bytes + ab_bytes);
         const size_t moff = (size_t)f0 * G * 2;
@@ -217,27 +315,27 @@ __global__ void __launch_bounds__(kP1Warps * 32) phase1_kernel(const ExpertArgs 
             bulk_g2s(ab_up, base + off.ab[1] + (size_t)f0 * 2, 32, bar);
         }
     }
+    __syncthreads();  // the barrier word is initialised before anyone polls it
+    const uint64_t t_sync = a.trace ? globaltimer_ns() : 0;
 
     // B operand: column n = g is row `n` of this instance (columns past the
     // count repeat row 0; their results are never stored).
-    const uint32_t col = g < in.count ? g : 0;
-    const uint32_t token = shared ? in.first + col : a.sorted[in.first + col] / a.top_k;
+    const uint32_t pair = pick(in.pair, g < in.count ? g : 0);
+    const uint32_t token = shared ? pair : pair / a.top_k;
     const uint16_t* xrow = a.xh + (size_t)token * D;
 
-    const size_t row_bytes = (size_t)D * BITS / 8;
-    const uint32_t toff = t * QT<BITS, GROUP>::kWords * 4;
-    const uint8_t* wrow[2][2];
-#pragma unroll
-    for (int mat = 0; mat < 2; ++mat) {
-        wrow[mat][0] = base + off.w[mat] + (size_t)(f0 + g) * row_bytes + toff;
-        wrow[mat][1] = base + off.w[mat] + (size_t)(f0 + g + 8) * row_bytes + toff;
-    }
     const uint16_t* s_sm[2] = {s_gate, s_up};
     const uint16_t* b_sm[2] = {b_gate, b_up};
     float tot[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-    tile_accumulate<BITS, GROUP, META, 2>(wrow, s_sm, b_sm, xrow, G, warp, G, kP1Warps, g, t, bar, 0,
-                                          a.status, tot);
+    // per-group sums of x for the two columns this thread accumulates
+    const uint32_t p0 = pick(in.pair, 2 * t < in.count ? 2 * t : 0);
+    const uint32_t p1 = pick(in.pair, 2 * t + 1 < in.count ? 2 * t + 1 : 0);
+    const float* xs0 = a.xsum + (size_t)(shared ? p0 : p0 / a.top_k) * G;
+    const float* xs1 = a.xsum + (size_t)(shared ? p1 : p1 / a.top_k) * G;
+    tile_accumulate<BITS, GROUP, META, 2, false>(wrow, s_sm, b_sm, xrow, G, warp, G, kP1Warps, g, t, bar, 0,
+                                                 a.status, tot, true, raw, xs0, xs1);
 
+    const uint64_t t_acc = a.trace ? globaltimer_ns() : 0;
     // split-K reduction across the warps, fixed order
 #pragma unroll
     for (int mat = 0; mat < 2; ++mat) {
@@ -248,6 +346,7 @@ __global__ void __launch_bounds__(kP1Warps * 32) phase1_kernel(const ExpertArgs 
         r[(g + 8) * 8 + 2 * t + 1] = tot[mat][3];
     }
     __syncthreads();
+    const uint64_t t_red = a.trace ? globaltimer_ns() : 0;
     if (tid < 128) {
         const uint32_t row = tid >> 3, c = tid & 7;
         if (c < in.count) {
@@ -263,25 +362,30 @@ __global__ void __launch_bounds__(kP1Warps * 32) phase1_kernel(const ExpertArgs 
             }
             const float act = glu(gate, up, a.activation);
             const uint32_t fi = perm_index(f0 + row, BITS == 4);
-            if (shared) {
-                a.acts_shared[(size_t)(in.first + c) * F + fi] = __half_as_ushort(__float2half_rn(act));
-            } else {
-                a.acts[(size_t)a.sorted[in.first + c] * F + fi] = __half_as_ushort(__float2half_rn(act));
-            }
+            uint16_t* dst = shared ? a.acts_shared : a.acts;
+            dst[(size_t)pick(in.pair, c) * F + fi] = __half_as_ushort(__float2half_rn(act));
         }
+    }
+    if (a.trace && tid == 0) {
+        uint64_t* tr = a.trace + 8 * (size_t)(blockIdx.y * gridDim.x + blockIdx.x);
+        tr[0] = t_start; tr[1] = t_loads; tr[2] = t_acc; tr[3] = globaltimer_ns();
+        tr[4] = t_inst; tr[5] = t_sync; tr[6] = t_red; tr[7] = 0;
     }
 }
 
-constexpr int kP2Warps = 16;
+constexpr int kP2Warps = 24;  // most warps a block uses; fewer when shared memory is short
 
-// grid d/16; block 512. Warps take (instance, k-split) units round-robin and
+// grid d/16; block 768. Warps take (instance, k-split) units round-robin and
 // add their weighted tiles into private accumulators; a fixed-order sum over
-// the warps finishes y.
+// the warps finishes y. When the launch carries the programmatic-dependency
+// attribute the warp's first unit fetches its weights and scales before it
+// waits for phase 1 (the work lists were complete before phase 1 began).
 template <int BITS, int GROUP, int META>
 __global__ void __launch_bounds__(kP2Warps * 32) phase2_kernel(const ExpertArgs a, uint32_t T,
                                                                uint32_t ksplit, uint32_t gmax,
                                                                void* __restrict__ y,
                                                                void* __restrict__ hidden) {
+    using Q = QT<BITS, GROUP>;
     extern __shared__ __align__(16) uint8_t smem[];
     const uint32_t d0 = blockIdx.x * 16;
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
@@ -295,7 +399,8 @@ __global__ void __launch_bounds__(kP2Warps * 32) phase2_kernel(const ExpertArgs 
     uint16_t* b_sm0 = (uint16_t*)(mine + meta_bytes);
     uint16_t* ab_sm = (uint16_t*)(mine + 2 * meta_bytes);
     uint64_t* bar = (uint64_t*)(mine + 2 * meta_bytes + 32);
-    float* yacc_all = (float*)(smem + kP2Warps * per_warp);
+    const uint32_t nw = blockDim.x >> 5;
+    float* yacc_all = (float*)(smem + nw * per_warp);
     float* yacc = yacc_all + (size_t)warp * T * 16;
 
     for (uint32_t i = lane; i < T * 16; i += 32) yacc[i] = 0.f;
@@ -308,18 +413,26 @@ __global__ void __launch_bounds__(kP2Warps * 32) phase2_kernel(const ExpertArgs 
     const uint32_t n_inst = *a.n_inst;
     const uint32_t units = n_inst * ksplit;
     uint32_t parity = 0;
-    for (uint32_t u = warp; u < units; u += kP2Warps) {
+    bool first = true;
+    for (uint32_t u = warp; u < units; u += nw) {
         const uint32_t ii = u / ksplit, ks = u % ksplit;
-        const Instance in = a.inst[ii];
+        const Instance in = load_instance(a.inst + ii);
         const bool shared = in.kind == 1;
         const uint32_t F = shared ? a.f_shared : a.f;
         const uint32_t G = F / GROUP;
         const Offsets3& off = shared ? a.shared : a.routed;
         const uint8_t* base = shared ? a.shared_block : pool_cell_base(a.pool, in.slot);
-        const uint32_t gper = G / ksplit;
-        const uint32_t gbeg = ks * gper;
-        const uint32_t gend = ks + 1 == ksplit ? G : gbeg + gper;
+        const uint32_t gbeg = (uint32_t)((uint64_t)G * ks / ksplit);
+        const uint32_t gend = (uint32_t)((uint64_t)G * (ks + 1) / ksplit);
         const bool add_bias = a.expert_bias && ks == 0;
+
+        const size_t row_bytes = (size_t)F * BITS / 8;
+        const uint32_t toff = t * Q::kWords * 4;
+        const uint8_t* wrow[1][2];
+        wrow[0][0] = base + off.w[2] + (size_t)(d0 + g) * row_bytes + toff;
+        wrow[0][1] = base + off.w[2] + (size_t)(d0 + g + 8) * row_bytes + toff;
+        uint32_t raw[Q::kBatch][1][2][Q::kWords];
+        load_batch<BITS, GROUP, 1>(wrow, gbeg, 1, gend, raw);
 
         if (lane == 0) {
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -330,21 +443,19 @@ __global__ void __launch_bounds__(kP2Warps * 32) phase2_kernel(const ExpertArgs 
             bulk_g2s(b_sm0, base + off.b[2] + moff, mb, bar);
             if (add_bias) bulk_g2s(ab_sm, base + off.ab[2] + (size_t)d0 * 2, 32, bar);
         }
+        if (first) {
+            pdl_wait();  // the activations of phase 1
+            pdl_launch_dependents();
+            first = false;
+        }
 
-        const uint32_t col = g < in.count ? g : 0;
-        const uint16_t* brow = shared
-            ? a.acts_shared + (size_t)(in.first + col) * F
-            : a.acts + (size_t)a.sorted[in.first + col] * F;
-        const size_t row_bytes = (size_t)F * BITS / 8;
-        const uint32_t toff = t * QT<BITS, GROUP>::kWords * 4;
-        const uint8_t* wrow[1][2];
-        wrow[0][0] = base + off.w[2] + (size_t)(d0 + g) * row_bytes + toff;
-        wrow[0][1] = base + off.w[2] + (size_t)(d0 + g + 8) * row_bytes + toff;
+        const uint32_t bpair = pick(in.pair, g < in.count ? g : 0);
+        const uint16_t* brow = (shared ? a.acts_shared : a.acts) + (size_t)bpair * F;
         const uint16_t* s_sm[1] = {s_sm0};
         const uint16_t* b_sm[1] = {b_sm0};
         float tot[1][4] = {{0.f, 0.f, 0.f, 0.f}};
-        tile_accumulate<BITS, GROUP, META, 1>(wrow, s_sm, b_sm, brow, G, gbeg, gend, 1, g, t, bar,
-                                              parity, a.status, tot);
+        tile_accumulate<BITS, GROUP, META, 1, true>(wrow, s_sm, b_sm, brow, G, gbeg, gend, 1, g, t, bar, parity,
+                                              a.status, tot, true, raw);
         parity ^= 1;
 
         const float ab0 = add_bias ? bf16_bits_to_f32(ab_sm[g]) : 0.f;
@@ -353,13 +464,13 @@ __global__ void __launch_bounds__(kP2Warps * 32) phase2_kernel(const ExpertArgs 
         for (int c = 0; c < 2; ++c) {
             const uint32_t cc = 2 * t + c;
             if (cc < in.count) {
+                const uint32_t pair = pick(in.pair, cc);
                 uint32_t token;
                 float w;
                 if (shared) {
-                    token = in.first + cc;
+                    token = pair;
                     w = a.shared_gate ? a.shared_gate[token] : 1.0f;
                 } else {
-                    const uint32_t pair = a.sorted[in.first + cc];
                     token = pair / a.top_k;
                     w = a.route_w[pair];
                 }
@@ -369,13 +480,16 @@ __global__ void __launch_bounds__(kP2Warps * 32) phase2_kernel(const ExpertArgs 
         }
         __syncwarp();
     }
+    if (first) {
+        pdl_wait();
+        pdl_launch_dependents();
+    }
     __syncthreads();
     // y = sum over warps; hidden += y (moe_phase2_finish, moe.metal:889-893)
-    for (uint32_t i = tid; i < T * 16; i += kP2Warps * 32) {
+    for (uint32_t i = tid; i < T * 16; i += nw * 32) {
         const uint32_t token = i >> 4, row = i & 15;
         float acc = 0.f;
-#pragma unroll
-        for (int w = 0; w < kP2Warps; ++w) acc += yacc_all[(size_t)w * T * 16 + i];
+        for (uint32_t w = 0; w < nw; ++w) acc += yacc_all[(size_t)w * T * 16 + i];
         const size_t o = (size_t)token * a.d + d0 + row;
         store_act(y, o, a.act_dtype, acc);
         if (hidden) {
@@ -395,6 +509,7 @@ template <int BITS, int GROUP, int META>
 __global__ void __launch_bounds__(kP2pWarps * 32) phase2_partials_kernel(const ExpertArgs a, uint32_t gmax,
                                                                         float* __restrict__ partials,
                                                                         float* __restrict__ partial_shared) {
+    using Q = QT<BITS, GROUP>;
     extern __shared__ __align__(16) uint8_t smem[];
     const uint32_t d0 = blockIdx.x * 16;
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
@@ -408,7 +523,7 @@ __global__ void __launch_bounds__(kP2pWarps * 32) phase2_partials_kernel(const E
     uint16_t* ab_sm = (uint16_t*)(mine + 2 * meta_bytes);
     uint64_t* bar = (uint64_t*)(mine + 2 * meta_bytes + 32);
 
-    const Instance in = a.inst[ii];
+    const Instance in = load_instance(a.inst + ii);
     const bool shared = in.kind == 1;
     const uint32_t F = shared ? a.f_shared : a.f;
     const uint32_t G = F / GROUP;
@@ -425,26 +540,26 @@ __global__ void __launch_bounds__(kP2pWarps * 32) phase2_partials_kernel(const E
         if (a.expert_bias) bulk_g2s(ab_sm, base + off.ab[2] + (size_t)d0 * 2, 32, bar);
     }
     __syncwarp();
-    const uint32_t col = g < in.count ? g : 0;
-    const uint16_t* brow = shared ? a.acts_shared + (size_t)(in.first + col) * F
-                                  : a.acts + (size_t)a.sorted[in.first + col] * F;
+    const uint32_t bpair = pick(in.pair, g < in.count ? g : 0);
+    const uint16_t* brow = (shared ? a.acts_shared : a.acts) + (size_t)bpair * F;
     const size_t row_bytes = (size_t)F * BITS / 8;
-    const uint32_t toff = t * QT<BITS, GROUP>::kWords * 4;
+    const uint32_t toff = t * Q::kWords * 4;
     const uint8_t* wrow[1][2];
     wrow[0][0] = base + off.w[2] + (size_t)(d0 + g) * row_bytes + toff;
     wrow[0][1] = base + off.w[2] + (size_t)(d0 + g + 8) * row_bytes + toff;
     const uint16_t* s_sm[1] = {s_sm0};
     const uint16_t* b_sm[1] = {b_sm0};
     float tot[1][4] = {{0.f, 0.f, 0.f, 0.f}};
-    tile_accumulate<BITS, GROUP, META, 1>(wrow, s_sm, b_sm, brow, G, 0, G, 1, g, t, bar, 0, a.status, tot);
+    uint32_t raw[Q::kBatch][1][2][Q::kWords];
+    tile_accumulate<BITS, GROUP, META, 1, true>(wrow, s_sm, b_sm, brow, G, 0, G, 1, g, t, bar, 0, a.status, tot, false,
+                                          raw);
     const float ab0 = a.expert_bias ? bf16_bits_to_f32(ab_sm[g]) : 0.f;
     const float ab1 = a.expert_bias ? bf16_bits_to_f32(ab_sm[g + 8]) : 0.f;
 #pragma unroll
     for (int c = 0; c < 2; ++c) {
         const uint32_t cc = 2 * t + c;
         if (cc < in.count) {
-            float* out = shared ? partial_shared + (size_t)(in.first + cc) * a.d
-                                : partials + (size_t)a.sorted[in.first + cc] * a.d;
+            float* out = (shared ? partial_shared : partials) + (size_t)pick(in.pair, cc) * a.d;
             out[d0 + g] = tot[0][c] + ab0;
             out[d0 + g + 8] = tot[0][2 + c] + ab1;
         }
@@ -452,6 +567,57 @@ __global__ void __launch_bounds__(kP2pWarps * 32) phase2_partials_kernel(const E
 }
 
 // ---- launchers -------------------------------------------------------------
+
+template <typename K, typename... Args>
+static cudaError_t launch_kernel(K kernel, dim3 grid, dim3 block, size_t smem, cudaStream_t st, bool pdl,
+                                 Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = pdl ? attr : nullptr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+
+static inline uint32_t p1_smem(uint32_t G) { return 4 * 32 * G + 80 + kP1Warps * 2 * 128 * 4; }
+static inline uint32_t p2_smem(uint32_t gmax, uint32_t T, uint32_t warps) {
+    return warps * (2 * 32 * gmax + 48) + warps * T * 16 * 4;
+}
+
+template <int BITS, int GROUP, int META>
+static cudaError_t launch_p1_t(cudaStream_t st, const ExpertArgs& a, uint32_t max_inst, bool pdl) {
+    const uint32_t fmax = a.f_shared > a.f ? a.f_shared : a.f;
+    const uint32_t smem = p1_smem(a.d / GROUP);
+    auto k = phase1_kernel<BITS, GROUP, META>;
+    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    return launch_kernel(k, dim3(fmax / 16, max_inst), dim3(kP1Warps * 32), smem, st, pdl, a);
+}
+
+template <int BITS, int GROUP, int META>
+static cudaError_t launch_p2_t(cudaStream_t st, const ExpertArgs& a, uint32_t T, uint32_t max_inst, void* y,
+                               void* hidden, bool pdl) {
+    const uint32_t fmax = a.f_shared > a.f ? a.f_shared : a.f;
+    const uint32_t gmax = fmax / GROUP;
+    const uint32_t gmin = (a.f_shared && a.f_shared < a.f ? a.f_shared : a.f) / GROUP;
+    // few instances (small batches): split K so that every warp has a unit of about one batch
+    uint32_t warps = kP2Warps;
+    while (warps > 4 && p2_smem(gmax, T, warps) > 200 * 1024) warps -= 4;
+    uint32_t ksplit = warps / (max_inst ? max_inst : 1);
+    const uint32_t most = gmin / QT<BITS, GROUP>::kBatch;
+    if (ksplit > most) ksplit = most;
+    if (ksplit < 1) ksplit = 1;
+    const uint32_t smem = p2_smem(gmax, T, warps);
+    auto k = phase2_kernel<BITS, GROUP, META>;
+    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    return launch_kernel(k, dim3(a.d / 16), dim3(warps * 32), smem, st, pdl, a, T, ksplit, gmax, y, hidden);
+}
 
 template <int BITS, int GROUP, int META>
 static cudaError_t launch_p2p_t(cudaStream_t st, const ExpertArgs& a, uint32_t max_inst, float* partials,
@@ -464,41 +630,6 @@ static cudaError_t launch_p2p_t(cudaStream_t st, const ExpertArgs& a, uint32_t m
     if (e != cudaSuccess) return e;
     k<<<dim3(a.d / 16, (max_inst + kP2pWarps - 1) / kP2pWarps), kP2pWarps * 32, smem, st>>>(a, gmax, partials,
                                                                                          partial_shared);
-    return cudaGetLastError();
-}
-
-static inline uint32_t p1_smem(uint32_t G) { return 4 * 32 * G + 80 + kP1Warps * 2 * 128 * 4; }
-static inline uint32_t p2_smem(uint32_t gmax, uint32_t T) {
-    return kP2Warps * (2 * 32 * gmax + 48) + kP2Warps * T * 16 * 4;
-}
-
-template <int BITS, int GROUP, int META>
-static cudaError_t launch_p1_t(cudaStream_t st, const ExpertArgs& a, uint32_t max_inst) {
-    const uint32_t fmax = a.f_shared > a.f ? a.f_shared : a.f;
-    const uint32_t smem = p1_smem(a.d / GROUP);
-    auto k = phase1_kernel<BITS, GROUP, META>;
-    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return e;
-    k<<<dim3(fmax / 16, max_inst), kP1Warps * 32, smem, st>>>(a);
-    return cudaGetLastError();
-}
-
-template <int BITS, int GROUP, int META>
-static cudaError_t launch_p2_t(cudaStream_t st, const ExpertArgs& a, uint32_t T, void* y, void* hidden) {
-    const uint32_t fmax = a.f_shared > a.f ? a.f_shared : a.f;
-    const uint32_t gmax = fmax / GROUP;
-    const uint32_t g_r = a.f / GROUP, g_s = a.f_shared ? a.f_shared / GROUP : g_r;
-    uint32_t ksplit = 1;
-    // few instances (small batches): split K so that every warp has a unit
-    if (T <= 2) {
-        if (g_r % 4 == 0 && g_s % 4 == 0 && g_r >= 16) ksplit = 4;
-        else if (g_r % 2 == 0 && g_s % 2 == 0 && g_r >= 4) ksplit = 2;
-    }
-    const uint32_t smem = p2_smem(gmax, T);
-    auto k = phase2_kernel<BITS, GROUP, META>;
-    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return e;
-    k<<<a.d / 16, kP2Warps * 32, smem, st>>>(a, T, ksplit, gmax, y, hidden);
     return cudaGetLastError();
 }
 
@@ -517,20 +648,23 @@ static cudaError_t launch_p2_t(cudaStream_t st, const ExpertArgs& a, uint32_t T,
         return cudaErrorInvalidValue;                                                     \
     } while (0)
 
-cudaError_t launch_phase1(const shrike_moe* m, cudaStream_t st, const ExpertArgs& a, uint32_t max_inst) {
-    SHRIKE_DISPATCH(launch_p1_t, st, a, max_inst);
+#ifdef SHRIKE_DEBUG_KNOB
+extern "C" void shrike_debug_knob(uint32_t v) { cudaMemcpyToSymbol(g_debug_knob, &v, 4); }
+#endif
+
+cudaError_t launch_phase1(const shrike_moe* m, cudaStream_t st, const ExpertArgs& a, uint32_t max_inst,
+                          bool pdl) {
+    SHRIKE_DISPATCH(launch_p1_t, st, a, max_inst, pdl);
 }
 
 cudaError_t launch_phase2(const shrike_moe* m, cudaStream_t st, const ExpertArgs& a, uint32_t T,
-                          void* y, void* hidden) {
-    SHRIKE_DISPATCH(launch_p2_t, st, a, T, y, hidden);
+                          uint32_t max_inst, void* y, void* hidden, bool pdl) {
+    SHRIKE_DISPATCH(launch_p2_t, st, a, T, max_inst, y, hidden, pdl);
 }
 
-}  // namespace shrike
-
-namespace shrike {
 cudaError_t launch_phase2_partials(const shrike_moe* m, cudaStream_t st, const ExpertArgs& a,
                                    uint32_t max_inst, float* partials, float* partial_shared) {
     SHRIKE_DISPATCH(launch_p2p_t, st, a, max_inst, partials, partial_shared);
 }
+
 }  // namespace shrike

@@ -13,6 +13,7 @@ struct Instance {
     uint32_t slot;   // pool cell (routed)
     uint32_t first;  // routed: index into the sorted pair list; shared: first token
     uint32_t count;  // 1..8
+    uint32_t pair[8];  // routed: row*top_k + rank of each of the `count` rows; shared: the row
 };
 
 // PoolBases (moe.metal:297-300) by value as a kernel argument.
@@ -53,22 +54,26 @@ struct ExpertArgs {
     const uint32_t* n_inst;
     const uint32_t* sorted;       // sorted pair ids (token*top_k + rank)
     const uint16_t* xh;           // fp16 operand copy of x, [tokens x d]
+    const float* xsum;            // per-group sums of xh, [tokens x d/group]
     uint16_t* acts;               // fp16 operand copy of the routed activations [pairs x f]
     uint16_t* acts_shared;        // [tokens x f_shared]
     const float* route_w;         // [tokens x top_k]
     const float* shared_gate;     // [tokens] or NULL
     uint32_t* status;
+    uint64_t* trace;              // diagnostics: per-block timestamps of phase 1, or NULL
 };
 
 struct Workspace {
     float* logits = nullptr;        // [max_tokens x num_experts]
     uint16_t* xh = nullptr;
+    float* xsum = nullptr;
     uint16_t* acts = nullptr;
     uint16_t* acts_shared = nullptr;
     uint32_t* sorted = nullptr;     // [max_tokens x top_k]
     Instance* inst = nullptr;
     uint32_t* n_inst = nullptr;
     uint32_t* status = nullptr;     // device status word
+    uint32_t* done_counter = nullptr; // blocks finished, fused route kernel
     uint32_t* block_hist = nullptr; // prefill grouping scratch
     uint32_t* expert_offsets = nullptr;
     uint32_t* expert_counts = nullptr;
@@ -98,6 +103,7 @@ struct shrike_moe {
     uint64_t* residency = nullptr;
     uint32_t residency_layers = 0;
     int sm_count = 148;
+    uint64_t* trace = nullptr;
 };
 
 namespace shrike {
@@ -108,6 +114,10 @@ size_t act_bytes(uint32_t dt);
 cudaError_t launch_router(const shrike_moe* m, cudaStream_t st, const shrike_router_operands& ops,
                           const void* hidden, uint32_t T, uint32_t stride, uint32_t* ids,
                           float* weights, float* shared_gate);
+cudaError_t launch_route_fused(const shrike_moe* m, cudaStream_t st, const shrike_router_operands& ops,
+                               const void* hidden, uint32_t T, uint32_t stride, const uint64_t* table,
+                               uint32_t pool_cells, const uint32_t* io_status, uint32_t* ids, float* weights,
+                               float* shared_gate, uint32_t* slots, uint32_t* counts, bool pdl);
 cudaError_t launch_classify(const shrike_moe* m, cudaStream_t st, const uint32_t* ids,
                             const uint64_t* table, uint32_t T, uint32_t* slots, uint32_t* counts,
                             uint32_t* miss_pos, uint32_t* miss_exp);
@@ -120,9 +130,9 @@ cudaError_t launch_group_pairs(const shrike_moe* m, cudaStream_t st, const uint3
                                uint32_t* offsets, uint32_t* counts);
 // decode.cu
 cudaError_t launch_phase1(const shrike_moe* m, cudaStream_t st, const ExpertArgs& a,
-                          uint32_t max_inst);
+                          uint32_t max_inst, bool pdl);
 cudaError_t launch_phase2(const shrike_moe* m, cudaStream_t st, const ExpertArgs& a, uint32_t T,
-                          void* y, void* hidden);
+                          uint32_t max_inst, void* y, void* hidden, bool pdl);
 // synth.cu
 cudaError_t launch_synth_fill(const shrike_moe* m, cudaStream_t st, const PoolView& pool,
                               uint32_t first_cell, uint32_t count, uint64_t seed, uint32_t layer,

@@ -8,11 +8,11 @@
 // (PrefillMoEGrouping.swift:269-370) as a three-step counting sort by expert
 // id that keeps (token, rank) order inside an expert, in place of the host
 // sort the reference runs between two GPU syncs (RealForwardRunner.swift:4305).
-#include "internal.h"
+#include "plan.cuh"
 
 namespace shrike {
 
-constexpr uint32_t kPlanThreads = 512;  // >= SHRIKE_MAX_DECODE_TOKENS * SHRIKE_MAX_TOP_K
+constexpr uint32_t kPlanThreads = 512;
 
 __device__ __forceinline__ uint32_t block_exclusive_scan(uint32_t v, uint32_t* warp_sums, uint32_t& total) {
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -41,10 +41,9 @@ decode_plan_kernel(const uint32_t* __restrict__ slots, uint32_t T, uint32_t top_
                    const uint32_t* __restrict__ io_status, uint32_t with_shared, uint32_t pool_cells,
                    Instance* __restrict__ inst, uint32_t* __restrict__ n_inst,
                    uint32_t* __restrict__ sorted, const void* __restrict__ x, uint32_t act_dtype,
-                   uint32_t d, uint32_t int4, uint16_t* __restrict__ xh, uint32_t* status) {
-    __shared__ uint32_t key[kPlanThreads];
-    __shared__ uint32_t order[kPlanThreads];
-    __shared__ uint32_t warp_sums[kPlanThreads / 32];
+                   uint32_t d, uint32_t int4, uint32_t group, uint16_t* __restrict__ xh,
+                   float* __restrict__ xsum, uint32_t* status) {
+    __shared__ PlanSmem sm;
     const uint32_t tid = threadIdx.x;
     const uint32_t n_pairs = T * top_k;
 
@@ -55,61 +54,22 @@ decode_plan_kernel(const uint32_t* __restrict__ slots, uint32_t T, uint32_t top_
         const uint32_t s = *io_status;
         ready = s == 1u || s == 3u;
     }
-    uint32_t s = SHRIKE_SLOT_MISS;
-    if (tid < n_pairs && ready) {
-        s = slots[tid];
+    for (uint32_t p = tid; p < n_pairs; p += kPlanThreads) {
+        uint32_t s = ready ? slots[p] : SHRIKE_SLOT_MISS;
         if (s != SHRIKE_SLOT_MISS && s >= pool_cells) {
             report_status(status, kStatusBadIndex);
             s = SHRIKE_SLOT_MISS;
         }
+        sm.key[p] = s;
     }
-    key[tid] = s;
     __syncthreads();
-    const bool valid = s != SHRIKE_SLOT_MISS;
-    uint32_t rank = 0;
-    if (valid) {
-        for (uint32_t j = 0; j < n_pairs; ++j) {
-            const uint32_t o = key[j];
-            rank += (o < s || (o == s && j < tid)) ? 1u : 0u;  // misses are 0xffffffff: never smaller
-        }
-        order[rank] = tid;
-    }
-    const uint32_t n_valid = __syncthreads_count(valid);
+    plan_body(sm, n_pairs, T, with_shared, inst, n_inst, sorted);
 
-    // instance starts: every 8th row of a run of equal slots
-    bool start = false;
-    uint32_t my_slot = 0;
-    if (tid < n_valid) {
-        my_slot = key[order[tid]];
-        uint32_t q = 0;
-        while (q < tid && key[order[tid - q - 1]] == my_slot) ++q;
-        start = (q & 7u) == 0;
-    }
-    uint32_t n_routed;
-    const uint32_t idx = block_exclusive_scan(start ? 1u : 0u, warp_sums, n_routed);
-    if (start) {
-        uint32_t count = 1;
-        while (count < 8 && tid + count < n_valid && key[order[tid + count]] == my_slot) ++count;
-        Instance in;
-        in.kind = 0; in.slot = my_slot; in.first = tid; in.count = count;
-        inst[idx] = in;
-    }
-    if (tid < n_valid) sorted[tid] = order[tid];
-    const uint32_t n_shared = with_shared ? (T + 7) / 8 : 0;
-    if (tid < n_shared) {
-        Instance in;
-        in.kind = 1; in.slot = 0; in.first = tid * 8; in.count = min(8u, T - tid * 8);
-        inst[n_routed + tid] = in;
-    }
-    if (tid == 0) *n_inst = n_routed + n_shared;
-
-    // fp16 operand copy of the activation rows
-    const uint32_t total = T * d;
-    for (uint32_t i = tid; i < total; i += kPlanThreads) {
-        const uint32_t row = i / d, e = i - row * d;
-        xh[(size_t)row * d + perm_index(e, int4 != 0)] =
-            __half_as_ushort(__float2half_rn(load_act(x, i, act_dtype)));
-    }
+    // fp16 operand copy of the activation rows and their per-group sums
+    const uint32_t items = T * (d / 8);
+    const size_t row_bytes = (size_t)d * (act_dtype == SHRIKE_DTYPE_FP32 ? 4 : 2);
+    for (uint32_t i0 = 0; i0 < items; i0 += kPlanThreads)
+        xprep_item(x, row_bytes, d, group, act_dtype, int4 != 0, i0 + tid, i0 + tid < items, xh, xsum);
 }
 
 cudaError_t launch_decode_plan(const shrike_moe* m, cudaStream_t st, const uint32_t* slots,
@@ -118,7 +78,7 @@ cudaError_t launch_decode_plan(const shrike_moe* m, cudaStream_t st, const uint3
     decode_plan_kernel<<<1, kPlanThreads, 0, st>>>(
         slots, T, m->cfg.top_k, io_status, with_shared ? 1u : 0u, pool_cells,
         m->ws.inst, m->ws.n_inst, m->ws.sorted, x, m->cfg.act_dtype, m->cfg.d,
-        m->cfg.weight_bits == 4 ? 1u : 0u, m->ws.xh, m->ws.status);
+        m->cfg.weight_bits == 4 ? 1u : 0u, m->cfg.group_size, m->ws.xh, m->ws.xsum, m->ws.status);
     return cudaGetLastError();
 }
 

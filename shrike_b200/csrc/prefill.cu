@@ -12,7 +12,8 @@ namespace shrike {
 __global__ void __launch_bounds__(256)
 prefill_instances_kernel(const uint32_t* __restrict__ offsets, const uint32_t* __restrict__ counts,
                          const uint32_t* __restrict__ slot_of_expert, uint32_t ne, uint32_t T,
-                         uint32_t with_shared, uint32_t pool_cells, Instance* __restrict__ inst,
+                         uint32_t with_shared, uint32_t pool_cells,
+                         const uint32_t* __restrict__ sorted, Instance* __restrict__ inst,
                          uint32_t* __restrict__ n_inst, uint32_t* status) {
     __shared__ uint32_t warp_sums[8];
     const uint32_t e = threadIdx.x;
@@ -45,26 +46,28 @@ prefill_instances_kernel(const uint32_t* __restrict__ offsets, const uint32_t* _
     for (uint32_t j = 0; j < n; ++j) {
         Instance in;
         in.kind = 0; in.slot = slot; in.first = offsets[e] + 8 * j; in.count = min(8u, c - 8 * j);
+        for (uint32_t q = 0; q < 8; ++q) in.pair[q] = sorted[in.first + (q < in.count ? q : 0)];
         inst[base + j] = in;
     }
     const uint32_t n_shared = with_shared ? (T + 7) / 8 : 0;
     for (uint32_t j = threadIdx.x; j < n_shared; j += blockDim.x) {
         Instance in;
         in.kind = 1; in.slot = 0; in.first = 8 * j; in.count = min(8u, T - 8 * j);
+        for (uint32_t q = 0; q < 8; ++q) in.pair[q] = 8 * j + (q < in.count ? q : 0);
         inst[total + j] = in;
     }
     if (threadIdx.x == 0) *n_inst = total + n_shared;
 }
 
-// x -> fp16 operand layout, all rows.
+// x -> fp16 operand layout and per-group sums, all rows.
 __global__ void __launch_bounds__(256)
-prefill_xprep_kernel(const void* __restrict__ x, uint32_t total, uint32_t d, uint32_t act_dtype,
-                     uint32_t int4, uint16_t* __restrict__ xh) {
-    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
-        const uint32_t row = i / d, e = i - row * d;
-        xh[(size_t)row * d + perm_index(e, int4 != 0)] =
-            __half_as_ushort(__float2half_rn(load_act(x, i, act_dtype)));
-    }
+prefill_xprep_kernel(const void* __restrict__ x, uint32_t T, uint32_t d, uint32_t group, uint32_t act_dtype,
+                     uint32_t int4, uint16_t* __restrict__ xh, float* __restrict__ xsum) {
+    const uint32_t items = T * (d / 8);
+    const size_t row_bytes = (size_t)d * (act_dtype == SHRIKE_DTYPE_FP32 ? 4 : 2);
+    for (uint32_t i0 = blockIdx.x * blockDim.x; i0 < items; i0 += gridDim.x * blockDim.x)
+        xprep_item(x, row_bytes, d, group, act_dtype, int4 != 0, i0 + threadIdx.x, i0 + threadIdx.x < items, xh,
+                   xsum);
 }
 
 // slot_of_expert[e] = the cell every pair of expert e resolved to.
@@ -119,11 +122,11 @@ cudaError_t launch_prefill_plan(const shrike_moe* m, cudaStream_t st, const uint
     e = launch_group_pairs(m, st, ids, nullptr, T, nullptr, ws.expert_offsets, ws.expert_counts);
     if (e != cudaSuccess) return e;
     prefill_instances_kernel<<<1, 256, 0, st>>>(ws.expert_offsets, ws.expert_counts, ws.slot_of_expert,
-                                                c.num_experts, T, with_shared ? 1u : 0u, pool_cells, ws.inst,
+                                                c.num_experts, T, with_shared ? 1u : 0u, pool_cells, ws.sorted, ws.inst,
                                                 ws.n_inst, ws.status);
-    const uint32_t total = T * c.d;
-    prefill_xprep_kernel<<<min(2048u, (total + 255) / 256), 256, 0, st>>>(x, total, c.d, c.act_dtype,
-                                                                         c.weight_bits == 4 ? 1u : 0u, ws.xh);
+    const uint32_t items = T * (c.d / 8);
+    prefill_xprep_kernel<<<min(2048u, (items + 255) / 256), 256, 0, st>>>(
+        x, T, c.d, c.group_size, c.act_dtype, c.weight_bits == 4 ? 1u : 0u, ws.xh, ws.xsum);
     return cudaGetLastError();
 }
 

@@ -12,7 +12,7 @@
 // float4 chunks l, l+32, ... ; affine rows: lane l takes elements 64g+2l,
 // 64g+2l+1 of every group g, as the shader does. exp() is a fixed sequence of
 // fp32 operations (exp_det) instead of the library routine for the same reason.
-#include "internal.h"
+#include "plan.cuh"
 
 namespace shrike {
 
@@ -75,58 +75,41 @@ __device__ __forceinline__ void load_act4(const void* row, uint32_t c, uint32_t 
 constexpr int kRouterMaxChunks = 23;  // d <= 2944 (the reference stages at most 2880, moe.metal:11)
 constexpr int kRouterWarps = 4;       // rows per block, as router_gemv_r4
 
-// grid (ceil((ne + has_gate)/4), token blocks); fp32 rows kept in registers and
-// reused for every token of the block.
-__global__ void __launch_bounds__(kRouterWarps * 32)
-router_logits_f32_kernel(const float* __restrict__ w, const float* __restrict__ gate_row,
-                         const uint16_t* __restrict__ eff_scale, const void* __restrict__ hidden,
-                         uint32_t T, uint32_t stride, uint32_t dt, uint32_t ne, uint32_t d,
-                         uint32_t tokens_per_block, float* __restrict__ logits,
-                         float* __restrict__ gate_out) {
-    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t e = blockIdx.x * kRouterWarps + warp;
-    const bool is_gate = gate_row != nullptr && e == ne;
-    if (e >= ne && !is_gate) return;
-    const float4* row = (const float4*)(is_gate ? gate_row : w + (size_t)e * d);
-    const uint32_t chunks = d / 4;
-    float4 wr[kRouterMaxChunks];
-#pragma unroll
-    for (int i = 0; i < kRouterMaxChunks; ++i) {
-        const uint32_t c = lane + 32 * i;
-        if (c < chunks) wr[i] = __ldg(row + c);
-    }
-    const uint32_t t0 = blockIdx.y * tokens_per_block;
-    const uint32_t t1 = min(T, t0 + tokens_per_block);
-    const size_t esz = dt == SHRIKE_DTYPE_FP32 ? 4 : 2;
-    for (uint32_t tk = t0; tk < t1; ++tk) {
-        const void* xrow = (const uint8_t*)hidden + (size_t)tk * stride * esz;
-        float acc = 0.f;
-#pragma unroll
-        for (int i = 0; i < kRouterMaxChunks; ++i) {
-            const uint32_t c = lane + 32 * i;
-            if (c < chunks) {
-                float x[4];
-                load_act4(xrow, c, dt, x);
-                if (eff_scale && !is_gate) {
-                    const uint2 s = __ldg((const uint2*)eff_scale + c);
-                    x[0] = __fmul_rn(x[0], __uint_as_float(s.x << 16));
-                    x[1] = __fmul_rn(x[1], __uint_as_float(s.x & 0xffff0000u));
-                    x[2] = __fmul_rn(x[2], __uint_as_float(s.y << 16));
-                    x[3] = __fmul_rn(x[3], __uint_as_float(s.y & 0xffff0000u));
-                }
-                acc = __fmaf_rn(wr[i].x, x[0], acc);
-                acc = __fmaf_rn(wr[i].y, x[1], acc);
-                acc = __fmaf_rn(wr[i].z, x[2], acc);
-                acc = __fmaf_rn(wr[i].w, x[3], acc);
-            }
-        }
-        acc = butterfly_sum(acc);
-        if (lane == 0) {
-            if (is_gate) gate_out[tk] = sigmoid_det(acc);
-            else logits[(size_t)tk * ne + e] = acc;
-        }
-    }
-}
+struct RouterArgs {
+    const void* w;                 // fp32 rows, or packed affine rows
+    const uint16_t* scales;        // affine only
+    const uint16_t* biases;        // affine only
+    uint32_t bits;                 // 0 = fp32
+    const float* gate_row;         // shared expert scalar gate row or NULL
+    const uint16_t* eff_scale;
+    const uint16_t* logit_bias;
+    const uint16_t* per_expert_scale;
+    const void* hidden;
+    uint32_t T, stride, dt, ne, d, top_k;
+    uint32_t sigmoid_scores;
+    float scaling;
+    uint32_t round_f16;
+    float* logits;
+    uint32_t* ids;
+    float* weights;
+    float* gate_out;
+    uint32_t tokens_per_block;
+    // fused decode tail (route_fused_kernel only)
+    const uint64_t* table;
+    uint32_t pool_cells;
+    const uint32_t* io_status;
+    uint32_t with_shared, int4, group;
+    uint32_t* slots;
+    uint32_t* counts;
+    Instance* inst;
+    uint32_t* n_inst;
+    uint32_t* sorted;
+    uint16_t* xh;
+    float* xsum;
+    uint32_t* done_counter;
+    uint32_t* status;
+    uint64_t* trace;               // diagnostics: 8 timestamps per block, or NULL
+};
 
 __device__ __forceinline__ uint32_t affine_value(const uint8_t* packed, uint32_t element, uint32_t bits) {
     const uint32_t bit = element * bits, byte = bit >> 3, shift = bit & 7u;
@@ -135,72 +118,119 @@ __device__ __forceinline__ uint32_t affine_value(const uint8_t* packed, uint32_t
     return (word >> shift) & ((1u << bits) - 1u);
 }
 
-// Affine int8/int4 rows, group 64, bf16 scales/biases: router_gemv_body.
-__global__ void __launch_bounds__(kRouterWarps * 32)
-router_logits_affine_kernel(const uint8_t* __restrict__ w, const uint16_t* __restrict__ scales,
-                            const uint16_t* __restrict__ biases, uint32_t bits,
-                            const float* __restrict__ gate_row,
-                            const uint16_t* __restrict__ eff_scale, const void* __restrict__ hidden,
-                            uint32_t T, uint32_t stride, uint32_t dt, uint32_t ne, uint32_t d,
-                            uint32_t tokens_per_block, float* __restrict__ logits,
-                            float* __restrict__ gate_out) {
+// N chunks per lane; PRED: the row may be shorter than 32*N chunks.
+template <int N, bool PRED>
+__device__ __forceinline__ void load_row_f32(const float* row, uint32_t chunks, uint32_t lane, float4 (&wr)[N]) {
+#pragma unroll
+    for (int i = 0; i < N; ++i) {
+        const uint32_t c = lane + 32 * i;
+        if (!PRED || c < chunks) wr[i] = __ldg((const float4*)row + c);
+    }
+}
+
+// One lane's share of an fp32 row against one activation row: float4 chunks
+// lane, lane+32, ... in order, four fused multiply-adds each.
+template <int N, bool PRED>
+__device__ __forceinline__ float lane_dot_f32(const float4 (&wr)[N], uint32_t chunks, uint32_t lane,
+                                              const void* xrow, uint32_t dt, const uint16_t* eff_scale) {
+    float acc = 0.f;
+#pragma unroll
+    for (int i = 0; i < N; ++i) {
+        const uint32_t c = lane + 32 * i;
+        if (!PRED || c < chunks) {
+            float x[4];
+            load_act4(xrow, c, dt, x);
+            if (eff_scale) {
+                const uint2 s = __ldg((const uint2*)eff_scale + c);
+                x[0] = __fmul_rn(x[0], __uint_as_float(s.x << 16));
+                x[1] = __fmul_rn(x[1], __uint_as_float(s.x & 0xffff0000u));
+                x[2] = __fmul_rn(x[2], __uint_as_float(s.y << 16));
+                x[3] = __fmul_rn(x[3], __uint_as_float(s.y & 0xffff0000u));
+            }
+            acc = __fmaf_rn(wr[i].x, x[0], acc);
+            acc = __fmaf_rn(wr[i].y, x[1], acc);
+            acc = __fmaf_rn(wr[i].z, x[2], acc);
+            acc = __fmaf_rn(wr[i].w, x[3], acc);
+        }
+    }
+    return acc;
+}
+
+// router_gemv_body (moe.metal:324-364): lane l takes elements 64g+2l, 64g+2l+1.
+__device__ __forceinline__ float lane_dot_affine(const uint8_t* row, const uint16_t* s_row,
+                                                 const uint16_t* b_row, uint32_t bits, uint32_t groups,
+                                                 uint32_t lane, const void* xrow, uint32_t dt,
+                                                 const uint16_t* eff_scale) {
+    float acc = 0.f;
+    for (uint32_t gi = 0; gi < groups; ++gi) {
+        const float s = bf16_bits_to_f32(s_row[gi]);
+        const float b = bf16_bits_to_f32(b_row[gi]);
+        const uint32_t idx = gi * 64 + lane * 2;
+        const float q0 = (float)affine_value(row, idx, bits);
+        const float q1 = (float)affine_value(row, idx + 1, bits);
+        float x0 = load_act(xrow, idx, dt), x1 = load_act(xrow, idx + 1, dt);
+        if (eff_scale) {
+            x0 = __fmul_rn(x0, bf16_bits_to_f32(eff_scale[idx]));
+            x1 = __fmul_rn(x1, bf16_bits_to_f32(eff_scale[idx + 1]));
+        }
+        acc = __fmaf_rn(s, __fadd_rn(__fmul_rn(q0, x0), __fmul_rn(q1, x1)), acc);
+        acc = __fmaf_rn(b, __fadd_rn(x0, x1), acc);
+    }
+    return acc;
+}
+
+// Logits (and the shared expert's scalar gate as row `ne`) of this warp's row
+// for the block's tokens. `pre` runs between the weight-row prefetch and the
+// first read of the activations.
+template <int N, bool PRED, typename Pre>
+__device__ __forceinline__ void logits_rows(const RouterArgs& a, Pre pre) {
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t e = blockIdx.x * kRouterWarps + warp;
-    const bool is_gate = gate_row != nullptr && e == ne;
-    if (e >= ne && !is_gate) return;
-    const uint32_t groups = d / 64;
-    const uint32_t t0 = blockIdx.y * tokens_per_block;
-    const uint32_t t1 = min(T, t0 + tokens_per_block);
-    const size_t esz = dt == SHRIKE_DTYPE_FP32 ? 4 : 2;
+    const bool is_gate = a.gate_row != nullptr && e == a.ne;
+    const bool active = e < a.ne || is_gate;
+    const bool f32row = a.bits == 0 || is_gate;
+    const uint32_t chunks = a.d / 4, groups = a.d / 64;
+    float4 wr[N];
+    if (active && f32row)
+        load_row_f32<N, PRED>(is_gate ? a.gate_row : (const float*)a.w + (size_t)e * a.d, chunks, lane, wr);
+    pre();
+    if (!active) return;
+    const uint32_t t0 = blockIdx.y * a.tokens_per_block;
+    const uint32_t t1 = min(a.T, t0 + a.tokens_per_block);
+    const size_t esz = a.dt == SHRIKE_DTYPE_FP32 ? 4 : 2;
     for (uint32_t tk = t0; tk < t1; ++tk) {
-        const void* xrow = (const uint8_t*)hidden + (size_t)tk * stride * esz;
-        float acc = 0.f;
-        if (is_gate) {
-            // the scalar gate row is fp32: lane-strided float4 chunks as above
-            for (uint32_t c = lane; c < d / 4; c += 32) {
-                float x[4];
-                load_act4(xrow, c, dt, x);
-                const float4 g4 = __ldg((const float4*)gate_row + c);
-                acc = __fmaf_rn(g4.x, x[0], acc); acc = __fmaf_rn(g4.y, x[1], acc);
-                acc = __fmaf_rn(g4.z, x[2], acc); acc = __fmaf_rn(g4.w, x[3], acc);
-            }
+        const void* xrow = (const uint8_t*)a.hidden + (size_t)tk * a.stride * esz;
+        float acc;
+        if (f32row) {
+            acc = lane_dot_f32<N, PRED>(wr, chunks, lane, xrow, a.dt, is_gate ? nullptr : a.eff_scale);
         } else {
-            const uint8_t* row = w + (size_t)e * (d * bits / 8);
-            for (uint32_t gi = 0; gi < groups; ++gi) {
-                const float s = bf16_bits_to_f32(scales[e * groups + gi]);
-                const float b = bf16_bits_to_f32(biases[e * groups + gi]);
-                const uint32_t idx = gi * 64 + lane * 2;
-                const float q0 = (float)affine_value(row, idx, bits);
-                const float q1 = (float)affine_value(row, idx + 1, bits);
-                float x0 = load_act(xrow, idx, dt), x1 = load_act(xrow, idx + 1, dt);
-                if (eff_scale) {
-                    x0 = __fmul_rn(x0, bf16_bits_to_f32(eff_scale[idx]));
-                    x1 = __fmul_rn(x1, bf16_bits_to_f32(eff_scale[idx + 1]));
-                }
-                acc = __fmaf_rn(s, __fadd_rn(__fmul_rn(q0, x0), __fmul_rn(q1, x1)), acc);
-                acc = __fmaf_rn(b, __fadd_rn(x0, x1), acc);
-            }
+            acc = lane_dot_affine((const uint8_t*)a.w + (size_t)e * (a.d * a.bits / 8), a.scales + (size_t)e * groups,
+                                  a.biases + (size_t)e * groups, a.bits, groups, lane, xrow, a.dt, a.eff_scale);
         }
         acc = butterfly_sum(acc);
         if (lane == 0) {
-            if (is_gate) gate_out[tk] = sigmoid_det(acc);
-            else logits[(size_t)tk * ne + e] = acc;
+            if (is_gate) a.gate_out[tk] = sigmoid_det(acc);
+            else a.logits[(size_t)tk * a.ne + e] = acc;
         }
     }
 }
 
-// One warp per row. The (score desc, expert asc) order is total, so K rounds
-// of a warp arg-max give exactly the list the reference's insertion scan
-// builds (moe.metal:436-456).
-__global__ void __launch_bounds__(128)
-router_select_kernel(const float* __restrict__ logits, const uint16_t* __restrict__ logit_bias,
-                     const uint16_t* __restrict__ per_expert_scale, uint32_t T, uint32_t ne,
-                     uint32_t top_k, uint32_t sigmoid_scores, float scaling, uint32_t round_f16,
-                     uint32_t* __restrict__ out_ids, float* __restrict__ out_w) {
-    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t row = blockIdx.x * 4 + warp;
-    if (row >= T) return;
-    const float* lg = logits + (size_t)row * ne;
+// The common hidden sizes get straight-line code without bounds checks.
+template <typename Pre>
+__device__ __forceinline__ void logits_body(const RouterArgs& a, Pre pre) {
+    if (a.d == 2048) logits_rows<16, false>(a, pre);
+    else if (a.d == 2304) logits_rows<18, false>(a, pre);
+    else logits_rows<kRouterMaxChunks, true>(a, pre);
+}
+
+// Top-k of one row by one warp. The (score desc, expert asc) order is total,
+// so K rounds of a warp arg-max give exactly the list the reference's
+// insertion scan builds (moe.metal:436-456). Lane r returns the r-th pick.
+// CG: read the logits past L1 (they were written by other blocks of this launch).
+template <bool CG>
+__device__ __forceinline__ void select_row(const float* lg, const RouterArgs& a, uint32_t lane,
+                                           uint32_t& out_id, float& out_w) {
+    const uint32_t ne = a.ne, top_k = a.top_k;
     float sc[8];
     uint32_t taken = 0;
 #pragma unroll
@@ -208,57 +238,204 @@ router_select_kernel(const float* __restrict__ logits, const uint16_t* __restric
         const uint32_t e = lane + 32 * i;
         float s = -INFINITY;
         if (e < ne) {
-            const float raw = lg[e];
-            const float b = logit_bias ? bf16_bits_to_f32(logit_bias[e]) : 0.0f;
-            s = __fadd_rn(sigmoid_scores ? sigmoid_det(raw) : raw, b);
+            const float raw = CG ? __ldcg(lg + e) : lg[e];
+            const float b = a.logit_bias ? bf16_bits_to_f32(a.logit_bias[e]) : 0.0f;
+            s = __fadd_rn(__fadd_rn(a.sigmoid_scores ? sigmoid_det(raw) : raw, b), 0.0f);  // -0 -> +0
         } else {
             taken |= 1u << i;
         }
         sc[i] = s;
     }
-    float my_score = 0.f;   // lane r keeps the r-th selection
+    // order-preserving integer keys: one warp-wide max and one warp-wide min per pick
+    uint32_t key[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const uint32_t b = __float_as_uint(sc[i]);
+        key[i] = (taken & (1u << i)) ? 0u : ((b & 0x80000000u) ? ~b : (b | 0x80000000u));
+    }
+    float my_score = 0.f;
     uint32_t my_id = 0;
     for (uint32_t r = 0; r < top_k; ++r) {
-        float best = -INFINITY;
-        uint32_t best_e = 0xffffffffu;
+        uint32_t bestk = 0;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const uint32_t e = lane + 32 * i;
-            if (!(taken & (1u << i)) && (best_e == 0xffffffffu || sc[i] > best)) {
-                best = sc[i];
-                best_e = e;   // ascending e within a lane: ties keep the lower id
-            }
-        }
+        for (int i = 0; i < 8; ++i) bestk = max(bestk, key[i]);
+        const uint32_t wmax = __reduce_max_sync(0xffffffffu, bestk);
+        uint32_t cand = 0xffffffffu;
 #pragma unroll
-        for (int m = 16; m >= 1; m >>= 1) {
-            const float os = __shfl_xor_sync(0xffffffffu, best, m);
-            const uint32_t oe = __shfl_xor_sync(0xffffffffu, best_e, m);
-            if (oe != 0xffffffffu && (best_e == 0xffffffffu || os > best || (os == best && oe < best_e))) {
-                best = os;
-                best_e = oe;
-            }
+        for (int i = 7; i >= 0; --i) cand = (key[i] == wmax && wmax != 0u) ? lane + 32u * i : cand;
+        const uint32_t win = __reduce_min_sync(0xffffffffu, cand);  // ties: the lower expert id
+        if (win != 0xffffffffu && (win & 31u) == lane) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) key[i] = (win >> 5) == (uint32_t)i ? 0u : key[i];
         }
-        if (best_e != 0xffffffffu && (best_e & 31u) == lane) taken |= 1u << (best_e >> 5);
-        if (lane == r) { my_score = best; my_id = best_e == 0xffffffffu ? 0u : best_e; }
+        if (lane == r) {
+            my_score = __uint_as_float((wmax & 0x80000000u) ? (wmax & 0x7fffffffu) : ~wmax);
+            my_id = win == 0xffffffffu ? 0u : win;
+        }
     }
     // weights (moe.metal:458-490), sums in rank order
     float val;
-    if (sigmoid_scores) val = lane < top_k ? sigmoid_det(lg[my_id]) : 0.f;
-    else {
+    if (a.sigmoid_scores) {
+        val = lane < top_k ? sigmoid_det(CG ? __ldcg(lg + my_id) : lg[my_id]) : 0.f;
+    } else {
         const float mx = __shfl_sync(0xffffffffu, my_score, 0);
         val = lane < top_k ? exp_det(__fsub_rn(my_score, mx)) : 0.f;
     }
     float sum = 0.f;
     for (uint32_t r = 0; r < top_k; ++r) sum = __fadd_rn(sum, __shfl_sync(0xffffffffu, val, r));
-    if (lane < top_k) {
+    float w;
+    if (a.sigmoid_scores) w = __fmul_rn(val, __fdiv_rn(a.scaling, __fadd_rn(sum, 1e-20f)));
+    else w = __fdiv_rn(val, sum);
+    const float pes = a.per_expert_scale ? bf16_bits_to_f32(a.per_expert_scale[my_id]) : 1.0f;
+    w = __fmul_rn(w, pes);
+    if (a.round_f16) w = __half2float(__float2half_rn(w));
+    out_id = my_id;
+    out_w = w;
+}
+
+// grid (ceil((ne + has_gate)/4), token blocks)
+__global__ void __launch_bounds__(kRouterWarps * 32) router_logits_kernel(const RouterArgs a) {
+    logits_body(a, [] {});
+}
+
+__global__ void __launch_bounds__(128) router_select_kernel(const RouterArgs a) {
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t row = blockIdx.x * 4 + warp;
+    if (row >= a.T) return;
+    uint32_t id;
+    float w;
+    select_row<false>(a.logits + (size_t)row * a.ne, a, lane, id, w);
+    if (lane < a.top_k) {
+        a.ids[(size_t)row * a.top_k + lane] = id;
+        a.weights[(size_t)row * a.top_k + lane] = w;
+    }
+}
+
+// Decode (T <= 64) in one launch: logits by all blocks; the block that
+// finishes last then selects, looks the experts up in the residency table and
+// builds the work lists -- no wait on another block anywhere. Every block also
+// converts its slice of the activation rows to the fp16 operand layout.
+// grid (ceil((ne + has_gate)/4), 1).
+__global__ void __launch_bounds__(kRouterWarps * 32) route_fused_kernel(const RouterArgs a) {
+    __shared__ PlanSmem sm;
+    __shared__ uint32_t ids_sm[kPlanMaxPairs];
+    __shared__ uint32_t s_last, s_miss;
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    uint64_t ts[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if (a.trace) ts[0] = globaltimer_ns();
+
+    // the weight rows do not depend on the previous kernel: fetch them first
+    logits_body(a, [] {
+        pdl_wait();
+        pdl_launch_dependents();
+    });
+    if (a.trace) ts[1] = globaltimer_ns();
+
+    // every block converts its share of the activation rows (blocks of 8 elements)
+    {
+        const uint32_t items = a.T * (a.d / 8);
+        const size_t esz = a.dt == SHRIKE_DTYPE_FP32 ? 4 : 2;
+        for (uint32_t i0 = blockIdx.x * blockDim.x; i0 < items; i0 += gridDim.x * blockDim.x)
+            xprep_item(a.hidden, (size_t)a.stride * esz, a.d, a.group, a.dt, a.int4 != 0, i0 + tid, i0 + tid < items,
+                       a.xh, a.xsum);
+    }
+
+    if (a.trace) ts[2] = globaltimer_ns();
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        const uint32_t ticket = atomicAdd(a.done_counter, 1u);
+        s_last = ticket == gridDim.x - 1 ? 1u : 0u;
+        if (s_last) *a.done_counter = 0;
+        s_miss = 0;
+    }
+    __syncthreads();
+    if (a.trace) ts[3] = globaltimer_ns();
+    if (!s_last) {
+        if (a.trace && tid == 0) for (int i = 0; i < 8; ++i) a.trace[8 * blockIdx.x + i] = ts[i];
+        return;
+    }
+    __threadfence();
+
+    for (uint32_t row = warp; row < a.T; row += kRouterWarps) {
+        uint32_t id;
         float w;
-        if (sigmoid_scores) w = __fmul_rn(val, __fdiv_rn(scaling, __fadd_rn(sum, 1e-20f)));
-        else w = __fdiv_rn(val, sum);
-        const float pes = per_expert_scale ? bf16_bits_to_f32(per_expert_scale[my_id]) : 1.0f;
-        w = __fmul_rn(w, pes);
-        if (round_f16) w = __half2float(__float2half_rn(w));
-        out_ids[(size_t)row * top_k + lane] = my_id;
-        out_w[(size_t)row * top_k + lane] = w;
+        select_row<true>(a.logits + (size_t)row * a.ne, a, lane, id, w);
+        if (lane < a.top_k) {
+            a.ids[(size_t)row * a.top_k + lane] = id;
+            a.weights[(size_t)row * a.top_k + lane] = w;
+            ids_sm[row * a.top_k + lane] = id;
+        }
+    }
+    __syncthreads();
+    if (a.trace) ts[4] = globaltimer_ns();
+    bool ready = true;
+    if (a.io_status) {
+        const uint32_t s = *a.io_status;
+        ready = s == 1u || s == 3u;
+    }
+    const uint32_t n_pairs = a.T * a.top_k;
+    uint32_t misses = 0;
+    for (uint32_t p = tid; p < n_pairs; p += blockDim.x) {
+        const uint32_t e = min(ids_sm[p], a.ne - 1u);
+        const uint64_t word = a.table[e];
+        uint32_t slot = (uint32_t)(word & 0xffffffffu);
+        const bool hit = (uint32_t)(word >> 32) == 2u && slot != SHRIKE_SLOT_MISS;
+        if (!hit) { slot = SHRIKE_SLOT_MISS; ++misses; }
+        if (a.slots) a.slots[p] = slot;
+        if (slot != SHRIKE_SLOT_MISS && slot >= a.pool_cells) {
+            report_status(a.status, kStatusBadIndex);
+            slot = SHRIKE_SLOT_MISS;
+        }
+        sm.key[p] = ready ? slot : SHRIKE_SLOT_MISS;
+    }
+    if (misses) atomicAdd(&s_miss, misses);
+    __syncthreads();
+    if (tid == 0 && a.counts) {
+        a.counts[0] = n_pairs - s_miss;
+        a.counts[1] = s_miss;
+    }
+    if (a.trace) ts[5] = globaltimer_ns();
+    // One row: every pair is its own instance; order them by cell as plan_body
+    // would, with eight shuffles instead of the block-wide sort.
+    bool fast = false;
+    if (a.T == 1) {
+        const uint32_t my = lane < n_pairs ? sm.key[lane] : SHRIKE_SLOT_MISS;
+        uint32_t rank = 0;
+        bool dup = false;
+        for (uint32_t j = 0; j < n_pairs; ++j) {
+            const uint32_t o = __shfl_sync(0xffffffffu, my, j);
+            if (my != SHRIKE_SLOT_MISS && o != SHRIKE_SLOT_MISS) {
+                rank += (o < my || (o == my && j < lane)) ? 1u : 0u;
+                dup |= (o == my && j != lane);
+            }
+        }
+        fast = !__any_sync(0xffffffffu, dup);  // same answer in every warp
+        if (fast && warp == 0) {
+            const uint32_t n_routed = __popc(__ballot_sync(0xffffffffu, my != SHRIKE_SLOT_MISS));
+            if (my != SHRIKE_SLOT_MISS) {
+                Instance in;
+                in.kind = 0; in.slot = my; in.first = rank; in.count = 1;
+                for (int q = 0; q < 8; ++q) in.pair[q] = lane;
+                a.inst[rank] = in;
+                a.sorted[rank] = lane;
+            }
+            if (lane == 0) {
+                if (a.with_shared) {
+                    Instance in;
+                    in.kind = 1; in.slot = 0; in.first = 0; in.count = 1;
+                    for (int q = 0; q < 8; ++q) in.pair[q] = 0;
+                    a.inst[n_routed] = in;
+                }
+                *a.n_inst = n_routed + (a.with_shared ? 1u : 0u);
+            }
+        }
+    }
+    if (!fast) plan_body(sm, n_pairs, a.T, a.with_shared, a.inst, a.n_inst, a.sorted);
+    if (a.trace && tid == 0) {
+        ts[6] = globaltimer_ns();
+        ts[7] = 1;
+        for (int i = 0; i < 8; ++i) a.trace[8 * blockIdx.x + i] = ts[i];
     }
 }
 
@@ -299,32 +476,59 @@ __global__ void classify_kernel(const uint32_t* __restrict__ ids, const uint64_t
     }
 }
 
+static RouterArgs make_router_args(const shrike_moe* m, const shrike_router_operands& ops, const void* hidden,
+                                   uint32_t T, uint32_t stride, uint32_t* ids, float* weights,
+                                   float* shared_gate) {
+    const shrike_moe_config& c = m->cfg;
+    RouterArgs a = {};
+    a.w = ops.weights; a.scales = ops.scales; a.biases = ops.biases; a.bits = c.router_weight_bits;
+    a.gate_row = (ops.shared_gate && shared_gate) ? ops.shared_gate : nullptr;
+    a.eff_scale = ops.effective_scale; a.logit_bias = ops.logit_bias; a.per_expert_scale = ops.per_expert_scale;
+    a.hidden = hidden; a.T = T; a.stride = stride; a.dt = c.act_dtype; a.ne = c.num_experts; a.d = c.d;
+    a.top_k = c.top_k; a.sigmoid_scores = c.router_kind == SHRIKE_ROUTER_SIGMOID; a.scaling = c.routed_scaling;
+    a.round_f16 = c.round_route_weights_f16; a.logits = m->ws.logits; a.ids = ids; a.weights = weights;
+    a.gate_out = shared_gate; a.tokens_per_block = T;
+    return a;
+}
+
 cudaError_t launch_router(const shrike_moe* m, cudaStream_t st, const shrike_router_operands& ops,
                           const void* hidden, uint32_t T, uint32_t stride, uint32_t* ids,
                           float* weights, float* shared_gate) {
-    const shrike_moe_config& c = m->cfg;
-    const bool gate = ops.shared_gate != nullptr && shared_gate != nullptr;
-    const uint32_t rows = c.num_experts + (gate ? 1u : 0u);
+    RouterArgs a = make_router_args(m, ops, hidden, T, stride, ids, weights, shared_gate);
+    const uint32_t rows = a.ne + (a.gate_row ? 1u : 0u);
     uint32_t tpb = 1;
     if (T > 64) tpb = 32;
     else if (T > 8) tpb = 4;
+    a.tokens_per_block = tpb;
     const dim3 grid((rows + kRouterWarps - 1) / kRouterWarps, (T + tpb - 1) / tpb);
-    if (c.router_weight_bits == 0) {
-        router_logits_f32_kernel<<<grid, kRouterWarps * 32, 0, st>>>(
-            (const float*)ops.weights, gate ? ops.shared_gate : nullptr, ops.effective_scale, hidden, T,
-            stride, c.act_dtype, c.num_experts, c.d, tpb, m->ws.logits, shared_gate);
-    } else {
-        router_logits_affine_kernel<<<grid, kRouterWarps * 32, 0, st>>>(
-            (const uint8_t*)ops.weights, ops.scales, ops.biases, c.router_weight_bits,
-            gate ? ops.shared_gate : nullptr, ops.effective_scale, hidden, T, stride, c.act_dtype,
-            c.num_experts, c.d, tpb, m->ws.logits, shared_gate);
-    }
+    router_logits_kernel<<<grid, kRouterWarps * 32, 0, st>>>(a);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
-    router_select_kernel<<<(T + 3) / 4, 128, 0, st>>>(
-        m->ws.logits, ops.logit_bias, ops.per_expert_scale, T, c.num_experts, c.top_k,
-        c.router_kind == SHRIKE_ROUTER_SIGMOID, c.routed_scaling, c.round_route_weights_f16, ids, weights);
+    router_select_kernel<<<(T + 3) / 4, 128, 0, st>>>(a);
     return cudaGetLastError();
+}
+
+cudaError_t launch_route_fused(const shrike_moe* m, cudaStream_t st, const shrike_router_operands& ops,
+                               const void* hidden, uint32_t T, uint32_t stride, const uint64_t* table,
+                               uint32_t pool_cells, const uint32_t* io_status, uint32_t* ids, float* weights,
+                               float* shared_gate, uint32_t* slots, uint32_t* counts, bool pdl) {
+    RouterArgs a = make_router_args(m, ops, hidden, T, stride, ids, weights, shared_gate);
+    a.table = table; a.pool_cells = pool_cells; a.io_status = io_status;
+    a.with_shared = m->cfg.has_shared; a.int4 = m->cfg.weight_bits == 4; a.group = m->cfg.group_size;
+    a.xsum = m->ws.xsum;
+    a.slots = slots; a.counts = counts; a.inst = m->ws.inst; a.n_inst = m->ws.n_inst; a.sorted = m->ws.sorted;
+    a.xh = m->ws.xh; a.done_counter = m->ws.done_counter; a.status = m->ws.status; a.trace = m->trace;
+    const uint32_t rows = a.ne + (a.gate_row ? 1u : 0u);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((rows + kRouterWarps - 1) / kRouterWarps);
+    cfg.blockDim = dim3(kRouterWarps * 32);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = pdl ? attr : nullptr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, route_fused_kernel, a);
 }
 
 cudaError_t launch_classify(const shrike_moe* m, cudaStream_t st, const uint32_t* ids,

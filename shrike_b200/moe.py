@@ -213,6 +213,34 @@ class MoE:
             self._h, _stream(), pool._h, C.byref(routed_offsets), _ptr(routing_weights),
             C.byref(shared) if shared is not None else None, _ptr(shared_gate), query_count, _ptr(y), _ptr(hidden)))
 
+    def encode_route_decode(self, operands: RouterOperands, layer: int, pool: "ExpertCellArena",
+                            hidden: torch.Tensor, out_indices: torch.Tensor, out_weights: torch.Tensor,
+                            out_shared_gate: Optional[torch.Tensor] = None,
+                            out_resolved_slots: Optional[torch.Tensor] = None,
+                            out_counts: Optional[torch.Tensor] = None, io_status: Optional[torch.Tensor] = None,
+                            query_count: Optional[int] = None, hidden_stride_elements: Optional[int] = None) -> None:
+        """Router + residency classification + decode work lists in one launch."""
+        q = hidden.shape[0] if query_count is None else query_count
+        stride = hidden.stride(0) if hidden_stride_elements is None else hidden_stride_elements
+        ops = operands.to_c()
+        self._check(self._lib.shrike_encode_route_decode(
+            self._h, _stream(), C.byref(ops), self.residency_row(layer), pool._h, hidden.data_ptr(), q, stride,
+            _ptr(io_status), _ptr(out_indices), _ptr(out_weights), _ptr(out_shared_gate),
+            _ptr(out_resolved_slots), _ptr(out_counts)))
+
+    def encode_decode_layer(self, pool: "ExpertCellArena", routed_offsets: capi.ExpertOffsets, layer: int,
+                            router: RouterOperands, x: torch.Tensor, y: torch.Tensor,
+                            hidden: Optional[torch.Tensor] = None, shared: Optional[capi.SharedExpert] = None,
+                            out_indices: Optional[torch.Tensor] = None, out_weights: Optional[torch.Tensor] = None,
+                            io_status: Optional[torch.Tensor] = None, query_count: Optional[int] = None) -> None:
+        """One decode layer (route -> phase 1 -> phase 2) as three dependent launches."""
+        q = x.shape[0] if query_count is None else query_count
+        ops = router.to_c()
+        self._check(self._lib.shrike_encode_decode_layer(
+            self._h, _stream(), pool._h, C.byref(routed_offsets), self.residency_row(layer), C.byref(ops),
+            C.byref(shared) if shared is not None else None, _ptr(x), q, _ptr(io_status), _ptr(out_indices),
+            _ptr(out_weights), _ptr(y), _ptr(hidden)))
+
     def encode_prefill(self, pool: "ExpertCellArena", routed_offsets: capi.ExpertOffsets,
                        topk_indices: torch.Tensor, resolved_slots: torch.Tensor, routing_weights: torch.Tensor,
                        x: torch.Tensor, y: torch.Tensor, hidden: Optional[torch.Tensor] = None,

@@ -114,11 +114,23 @@ class Layer:
         return slots, counts
 
     def forward(self, x: np.ndarray, prefill: bool | None = None, hidden: np.ndarray | None = None,
-                io_status: int | None = None):
-        """router -> classification -> decode/prefill. Returns (y fp32, ids, weights, hidden_out)."""
+                io_status: int | None = None, fused: bool = False):
+        """router -> classification -> decode/prefill. Returns (y fp32, ids, weights, hidden_out).
+        fused=True takes the one-call decode layer (three dependent launches) instead."""
         cfg = self.cfg
         x_dev = to_act_tensor(x, cfg.act_dtype, self.device)
         T = x_dev.shape[0]
+        if fused:
+            ids = torch.empty((T, cfg.top_k), dtype=torch.int32, device=self.device)
+            w = torch.empty((T, cfg.top_k), dtype=torch.float32, device=self.device)
+            y = torch.empty_like(x_dev)
+            h = None if hidden is None else to_act_tensor(hidden, cfg.act_dtype, self.device)
+            st = None if io_status is None else torch.tensor([io_status], dtype=torch.int32, device=self.device)
+            self.moe.encode_decode_layer(self.pool, self.offsets, self.layer, self.router_ops, x_dev, y, h,
+                                         self.shared, ids, w, st)
+            self.moe.status()
+            return (y.float().cpu().numpy(), ids.cpu().numpy().astype(np.uint32), w.cpu().numpy(),
+                    None if h is None else h.float().cpu().numpy())
         ids, w, gate = self.route(x_dev)
         slots, _ = self.classify(ids)
         y = torch.empty_like(x_dev)

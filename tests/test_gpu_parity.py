@@ -234,6 +234,48 @@ def test_device_fill_is_the_host_function(cuda_device):
         layer.close()
 
 
+@pytest.mark.parametrize("T", [1, 3, 8, 17, 64])
+@pytest.mark.parametrize("kw", [dict(), dict(weight_bits=8, router_weight_bits=8, router_kind=capi.ROUTER_SIGMOID,
+                                             routed_scaling=2.446, shared_gated=False),
+                                dict(has_shared=False, shared_gated=False, expert_bias=True,
+                                     activation=capi.ACT_CLAMPED_SWIGLU, group_size=32, top_k=2)])
+def test_fused_decode_layer_equals_the_separate_calls(cuda_device, T, kw):
+    """One-call decode layer (fused route kernel + dependent launches) against the five separate calls:
+    ids, weights and outputs bit for bit; and against the oracle."""
+    layer = Layer(small_config(d=256, **kw))
+    x = inputs(T, 256, seed=T + 40)
+    h0 = inputs(T, 256, seed=T + 41)
+    a = layer.forward(x, hidden=h0)
+    b = layer.forward(x, hidden=h0, fused=True)
+    assert (a[1] == b[1]).all() and (a[2] == b[2]).all()
+    assert (a[0] == b[0]).all() and (a[3] == b[3]).all()
+    check_layer(layer, x, fused=True)
+    # repeated calls reuse the workspace and the completion counter
+    c = layer.forward(x, hidden=h0, fused=True)
+    assert (c[0] == b[0]).all()
+    layer.close()
+
+
+def test_fused_route_reports_slots_counts_and_status(cuda_device):
+    cfg = small_config()
+    layer = Layer(cfg)
+    layer.moe.residency_set(0, 3, 0, 1)
+    x = inputs(9, 128, seed=50)
+    x_dev = to_act_tensor(x, cfg.act_dtype, layer.device)
+    ids, w, gate = layer.route(x_dev)
+    slots, counts = layer.classify(ids)
+    ids2, w2, gate2, slots2 = torch.empty_like(ids), torch.empty_like(w), torch.empty_like(gate), torch.empty_like(slots)
+    counts2 = torch.zeros(2, dtype=torch.int32, device=layer.device)
+    layer.moe.encode_route_decode(layer.router_ops, 0, layer.pool, x_dev, ids2, w2, gate2, slots2, counts2)
+    layer.moe.status()
+    assert (ids == ids2).all() and (w == w2).all() and (gate == gate2).all()
+    assert (slots == slots2).all() and (counts == counts2).all() and int(counts2[1]) > 0
+    # a batch that is not ready leaves only the shared term
+    y, ids3, w3, _ = layer.forward(x, io_status=capi.IO_FAILED, fused=True)
+    assert rel_l2(y, layer.oracle_forward(x, ids3, np.zeros_like(w3))) <= TOL
+    layer.close()
+
+
 @pytest.mark.parametrize("T", [65, 100, 257])
 def test_prefill_small(cuda_device, T):
     layer = Layer(small_config(max_tokens=512))

@@ -31,7 +31,8 @@ def test_qwen_layer_decode(cuda_device, T):
     layer = Layer(cfg, seed=101, device_fill=True)
     assert layer.block_bytes == 1_769_472
     err, gap = run(layer, inputs(T, cfg.d, seed=T))
-    print(f"qwen T={T}: rel L2 {err:.2e}, min top-k gap {gap:.2e}")
+    err2, _ = run(layer, inputs(T, cfg.d, seed=T), fused=True)
+    print(f"qwen T={T}: rel L2 {err:.2e} (fused {err2:.2e}), min top-k gap {gap:.2e}")
     layer.close()
 
 
@@ -49,6 +50,7 @@ def test_gpt_oss_layer(cuda_device, group, T):
     layer = Layer(cfg, seed=103, device_fill=True)
     assert layer.block_bytes == (15_569_280 if group == 32 else 14_014_080)
     err, gap = run(layer, inputs(T, cfg.d, seed=group + T))
+    run(layer, inputs(T, cfg.d, seed=group + T), fused=True)
     print(f"gpt-oss g{group} T={T}: rel L2 {err:.2e}, min top-k gap {gap:.2e}")
     layer.close()
 
@@ -60,6 +62,7 @@ def test_kimi_layer_decode_and_prefill(cuda_device):
     layer = Layer(cfg, seed=104, device_fill=True, logit_bias=rng.uniform(-0.1, 0.1, 256).astype(np.float32))
     assert layer.block_bytes == 7_520_256
     run(layer, inputs(16, cfg.d, seed=1))
+    run(layer, inputs(16, cfg.d, seed=1), fused=True)
     run(layer, inputs(96, cfg.d, seed=2), prefill=True)
     layer.close()
 
