@@ -35,8 +35,8 @@ METRIC = "MoE-FFN tokens/s and HBM GB/s vs 8 TB/s peak at 1/2/4/8 B200"
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--tokens", type=int, default=1, help="decode batch: 1, 4 or 16")
     ap.add_argument("--layers", type=int, default=LAYERS)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
@@ -321,6 +321,10 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     units = [u + 1 for u in distinct]             # + the shared expert
     mean_units = sum(units) / L
     peak, peak_src = measured_peaks()
+    # dram__bytes_read + dram__bytes_write of one phase-1 launch from the ncu capture summarised in
+    # profiles/phase1_kernel_qwen_batch1.md: 10,654,848 B for 9 experts, i.e. 1.0036 x the algorithmic bytes;
+    # traffic grows with the experts a launch touches, so it is scaled by the units of this run.
+    traffic = mean_units * 10_654_848 / 9.0
     p1_gbs = mean_units * gate_up_bytes / (ms_p1 * 1e-3) / 1e9
     p2_gbs = mean_units * down_bytes / (ms_p2 * 1e-3) / 1e9
     layer_gbs = mean_units * wl.block_bytes / (ms / L * 1e-3) / 1e9
@@ -342,7 +346,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             },
             "hbm_gbs_per_layer": layer_gbs,
             "roofline": {"bound": "hbm", "kernel": "phase1_kernel<4,64,bf16>", "achieved": p1_gbs, "peak": peak,
-                         "unit": "GB/s", "frac": p1_gbs / peak, "peak_source": peak_src, "traffic": None,
+                         "unit": "GB/s", "frac": p1_gbs / peak, "peak_source": peak_src, "traffic": traffic,
                          "algorithmic_bytes_per_launch": mean_units * gate_up_bytes, "us_per_launch": ms_p1 * 1e3,
                          "phase2": {"achieved": p2_gbs, "frac": p2_gbs / peak, "us_per_launch": ms_p2 * 1e3,
                                     "algorithmic_bytes_per_launch": mean_units * down_bytes},

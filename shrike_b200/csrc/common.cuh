@@ -122,7 +122,7 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
 // spinning forever if the copy never lands.
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
     const uint32_t addr = smem_u32(bar);
-    for (uint32_t it = 0; it < (1u << 22); ++it) {
+    for (uint32_t it = 0; it < (1u << 20); ++it) {
         uint32_t ok;
         asm volatile(
             "{\n\t.reg .pred p;\n\t"
@@ -130,8 +130,19 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
             "selp.u32 %0, 1, 0, p;\n\t}"
             : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
         if (ok) return true;
+        if (it > 4) __nanosleep(64);  // a waiting warp should not eat issue slots
     }
     return false;
+}
+
+// ---- cp.async (16-byte global -> shared copies issued by every lane) ---------
+__device__ __forceinline__ void cp_async_16(uint32_t smem_addr, const void* gptr) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr), "l"(gptr) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
 __device__ __forceinline__ uint64_t globaltimer_ns() {

@@ -24,9 +24,6 @@
 
 namespace shrike {
 
-#ifdef SHRIKE_DEBUG_KNOB
-__device__ uint32_t g_debug_knob = 0;
-#endif
 
 template <int BITS, int GROUP>
 struct QT {
@@ -84,16 +81,6 @@ __device__ __forceinline__ void group_mma(const uint32_t (&raw)[NMAT][2][QT<BITS
                                           const uint32_t (&b)[QT<BITS, GROUP>::kBRegs],
                                           float (&c)[NMAT][4], float (&xs)[4]) {
     constexpr uint32_t kOnes = 0x3C003C00u;
-#ifdef SHRIKE_DEBUG_KNOB
-    if (g_debug_knob & 2) {  // no dequant, no MMA: keep the loads alive
-#pragma unroll
-        for (int mat = 0; mat < NMAT; ++mat)
-#pragma unroll
-            for (int w = 0; w < QT<BITS, GROUP>::kWords; ++w)
-                c[mat][0] += __uint_as_float((raw[mat][0][w] ^ raw[mat][1][w] ^ b[w]) & 0x3fffffffu);
-        return;
-    }
-#endif
 #pragma unroll
     for (int m = 0; m < QT<BITS, GROUP>::kMmas; ++m) {
         const uint32_t b0 = b[2 * m], b1 = b[2 * m + 1];
@@ -103,9 +90,6 @@ __device__ __forceinline__ void group_mma(const uint32_t (&raw)[NMAT][2][QT<BITS
             uint32_t lo0, hi0, lo1, hi1;
             unpack_step<BITS>(raw[mat][0], m, lo0, hi0);
             unpack_step<BITS>(raw[mat][1], m, lo1, hi1);
-#ifdef SHRIKE_DEBUG_KNOB
-            if (g_debug_knob & 1) { c[mat][0] += __uint_as_float((lo0 ^ lo1 ^ hi0 ^ hi1 ^ b0 ^ b1) & 0x3fffffffu); continue; }
-#endif
             mma_16816(c[mat], lo0, lo1, hi0, hi1, b0, b1);
         }
     }
@@ -332,8 +316,8 @@ __global__ void __launch_bounds__(kP1Warps * 32) phase1_kernel(const ExpertArgs 
     const uint32_t p1 = pick(in.pair, 2 * t + 1 < in.count ? 2 * t + 1 : 0);
     const float* xs0 = a.xsum + (size_t)(shared ? p0 : p0 / a.top_k) * G;
     const float* xs1 = a.xsum + (size_t)(shared ? p1 : p1 / a.top_k) * G;
-    tile_accumulate<BITS, GROUP, META, 2, false>(wrow, s_sm, b_sm, xrow, G, warp, G, kP1Warps, g, t, bar, 0,
-                                                 a.status, tot, true, raw, xs0, xs1);
+    tile_accumulate<BITS, GROUP, META, 2, true>(wrow, s_sm, b_sm, xrow, G, warp, G, kP1Warps, g, t, bar, 0,
+                                                a.status, tot, true, raw, xs0, xs1);
 
     const uint64_t t_acc = a.trace ? globaltimer_ns() : 0;
     // split-K reduction across the warps, fixed order
@@ -648,9 +632,6 @@ static cudaError_t launch_p2p_t(cudaStream_t st, const ExpertArgs& a, uint32_t m
         return cudaErrorInvalidValue;                                                     \
     } while (0)
 
-#ifdef SHRIKE_DEBUG_KNOB
-extern "C" void shrike_debug_knob(uint32_t v) { cudaMemcpyToSymbol(g_debug_knob, &v, 4); }
-#endif
 
 cudaError_t launch_phase1(const shrike_moe* m, cudaStream_t st, const ExpertArgs& a, uint32_t max_inst,
                           bool pdl) {
