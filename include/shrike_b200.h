@@ -31,6 +31,7 @@ extern "C" {
 #define SHRIKE_MAX_EXPERTS 256u      /* MoE.swift:263 */
 #define SHRIKE_MAX_POOL_CHUNKS 8u    /* PoolBases.base[8], moe.metal:297-300 */
 #define SHRIKE_MAX_DECODE_TOKENS 64u /* largest query_count of the decode entry points */
+#define SHRIKE_STATIC_ROUTER_MAX_ROWS 64u /* rows the allocation-free router accepts per call */
 #define SHRIKE_SLOT_MISS 0xffffffffu /* resolved_slots sentinel, moe.metal:146 */
 
 enum { SHRIKE_DTYPE_BF16 = 0, SHRIKE_DTYPE_FP16 = 1, SHRIKE_DTYPE_FP32 = 2 };
@@ -275,6 +276,34 @@ int shrike_encode_group_pairs(shrike_moe* moe, void* stream, const uint32_t* top
                               const float* routing_weights, uint32_t query_count,
                               uint32_t* sorted_pairs, uint32_t* per_expert_offsets,
                               uint32_t* per_expert_counts);
+
+/* The router for callers that cannot allocate. No counterpart in the reference.
+ * Creating a handle sizes a workspace with cudaMalloc; a host that has already
+ * given all free HBM to its expert pool, that fixes its memory plan before the
+ * first token, or that must not take cudaMalloc's device-wide synchronisation
+ * inside its decode loop cannot do that. This call needs no handle: it takes
+ * the configuration by pointer (d, num_experts, top_k, act_dtype, router_kind,
+ * routed_scaling, router_weight_bits and round_route_weights_f16 are read) and
+ * keeps its one piece of scratch, the logits, in a 64 KiB device array built
+ * into the library (resident on every GPU that loads it, until exit). It calls
+ * no cudaMalloc, cudaFree or other allocating routine. Same outputs as
+ * shrike_encode_router, bit for bit.
+ *   - Limits: query_count <= SHRIKE_STATIC_ROUTER_MAX_ROWS and num_experts <=
+ *     SHRIKE_MAX_EXPERTS; anything larger is refused with SHRIKE_ERANGE.
+ *   - The device to run on must be current. The first call on a device looks up
+ *     the array's device address (cudaGetSymbolAddress); make that first call
+ *     before any stream capture begins.
+ *   - Every call on a device shares the one array, which keeps the previous
+ *     call's logits (each call overwrites the rows it uses before reading them,
+ *     so nothing needs clearing). Two calls whose kernels overlap on the GPU --
+ *     different streams without an ordering between them -- race on it.
+ *   - Errors come back as the return code and, when error_text is given, as
+ *     text in that buffer (there is no handle to hold a message). */
+int shrike_encode_router_static(const shrike_moe_config* config, void* stream,
+                                const shrike_router_operands* operands, const void* hidden,
+                                uint32_t query_count, uint32_t hidden_stride_elements,
+                                uint32_t* out_indices, float* out_weights, float* out_shared_gate,
+                                char* error_text, size_t error_text_bytes);
 
 /* End-to-end convenience for hosts that keep activations in host memory:
  * copies x_host in, runs router -> classification -> decode/prefill for one

@@ -16,6 +16,7 @@ ROUTER_SOFTMAX, ROUTER_SIGMOID = 0, 1
 IO_PENDING, IO_READY, IO_FAILED = 0, 1, 2
 SLOT_MISS = 0xFFFFFFFF
 MAX_DECODE_TOKENS = 64
+STATIC_ROUTER_MAX_ROWS = 64
 
 OK, EINVAL, ENOMEM, ERANGE, EIO, ETIMEDOUT = 0, 22, 12, 34, 5, 110
 
@@ -71,6 +72,8 @@ SIGNATURES = {
     "shrike_residency_set": (_INT, [_P, _U32, _U32, _U32, _U32, _P]),
     "shrike_residency_set_layer_identity": (_INT, [_P, _U32, _U32, _P]),
     "shrike_encode_router": (_INT, [_P, _P, C.POINTER(RouterOperands), _P, _U32, _U32, _P, _P, _P]),
+    "shrike_encode_router_static": (_INT, [C.POINTER(MoEConfig), _P, C.POINTER(RouterOperands), _P, _U32, _U32, _P, _P,
+                                           _P, C.c_char_p, C.c_size_t]),
     "shrike_encode_residency_classification": (_INT, [_P, _P, _P, _P, _U32, _P, _P, _P, _P]),
     "shrike_encode_decode_plan": (_INT, [_P, _P, _P, _P, _P, _U32, _P]),
     "shrike_encode_phase1": (_INT, [_P, _P, _P, C.POINTER(ExpertOffsets), C.POINTER(SharedExpert), _U32]),

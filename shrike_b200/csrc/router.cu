@@ -540,3 +540,109 @@ cudaError_t launch_classify(const shrike_moe* m, cudaStream_t st, const uint32_t
 }
 
 }  // namespace shrike
+
+// ---- router entry point that allocates nothing --------------------------------
+//
+// Some hosts cannot let this library call cudaMalloc at all: a decode loop that
+// has handed every free byte of HBM to the expert pool, a process whose memory
+// plan is fixed before the first token, or a latency-critical thread that must
+// not take cudaMalloc's device-wide synchronisation. shrike_moe_create sizes a
+// workspace with cudaMalloc, so those hosts cannot own a handle. This entry
+// point runs the router (logits + top-k + weights, and the shared expert's
+// scalar gate) without one: its only scratch, the logits of up to
+// SHRIKE_STATIC_ROUTER_MAX_ROWS rows by SHRIKE_MAX_EXPERTS experts, lives in
+// the file-scope device array below (64 KiB on every GPU that loads the
+// library, until the process exits).
+#include <mutex>
+
+namespace shrike {
+
+static __device__ __align__(256) float g_static_router_logits[SHRIKE_STATIC_ROUTER_MAX_ROWS * SHRIKE_MAX_EXPERTS];
+
+// Device address of the array, per device ordinal. The array's name is only a
+// host-side stand-in in host code; the address the kernels need comes from
+// cudaGetSymbolAddress, asked once per device with that device current.
+static float* g_static_logits_ptr[64] = {};
+static std::mutex g_static_logits_mutex;
+
+static cudaError_t static_logits_for_current_device(float** out) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    std::lock_guard<std::mutex> lock(g_static_logits_mutex);
+    if (!g_static_logits_ptr[dev]) {
+        float* p = nullptr;
+        e = cudaGetSymbolAddress((void**)&p, g_static_router_logits);
+        if (e != cudaSuccess) return e;
+        g_static_logits_ptr[dev] = p;
+    }
+    *out = g_static_logits_ptr[dev];
+    return cudaSuccess;
+}
+
+static int static_router_fail(char* text, size_t bytes, int code, const char* msg) {
+    if (text && bytes) {
+        size_t i = 0;
+        for (; msg[i] && i + 1 < bytes; ++i) text[i] = msg[i];
+        text[i] = 0;
+    }
+    return code;
+}
+
+}  // namespace shrike
+
+extern "C" int shrike_encode_router_static(const shrike_moe_config* config, void* stream,
+                                           const shrike_router_operands* ops, const void* hidden,
+                                           uint32_t query_count, uint32_t hidden_stride_elements,
+                                           uint32_t* out_indices, float* out_weights, float* out_shared_gate,
+                                           char* error_text, size_t error_text_bytes) {
+    using namespace shrike;
+    auto bad = [&](int code, const char* msg) { return static_router_fail(error_text, error_text_bytes, code, msg); };
+    if (!config) return bad(SHRIKE_EINVAL, "static router: config is null");
+    if (query_count == 0) return SHRIKE_OK;
+    const shrike_moe_config& c = *config;
+    if (query_count > SHRIKE_STATIC_ROUTER_MAX_ROWS)
+        return bad(SHRIKE_ERANGE, "static router: query_count exceeds SHRIKE_STATIC_ROUTER_MAX_ROWS (64); "
+                                  "the built-in scratch holds 64 rows of logits");
+    if (c.num_experts == 0 || c.num_experts > SHRIKE_MAX_EXPERTS)
+        return bad(SHRIKE_ERANGE, "static router: num_experts must be 1..256 (the built-in scratch is 64 x 256 floats)");
+    if (c.top_k == 0 || c.top_k > SHRIKE_MAX_TOP_K || c.top_k > c.num_experts)
+        return bad(SHRIKE_EINVAL, "static router: top_k must be 1..8 and at most num_experts");
+    if (c.d == 0 || c.d % 64 != 0 || c.d > 2944) return bad(SHRIKE_EINVAL, "static router: d must be a multiple of 64, at most 2944");
+    if (c.act_dtype > SHRIKE_DTYPE_FP32 || c.router_kind > SHRIKE_ROUTER_SIGMOID ||
+        (c.router_weight_bits != 0 && c.router_weight_bits != 4 && c.router_weight_bits != 8))
+        return bad(SHRIKE_EINVAL, "static router: unknown act_dtype, router_kind or router_weight_bits");
+    if (!ops || !ops->weights || !hidden || !out_indices || !out_weights)
+        return bad(SHRIKE_EINVAL, "static router: null operand");
+    if (c.router_weight_bits != 0 && (!ops->scales || !ops->biases))
+        return bad(SHRIKE_EINVAL, "static router: affine weights need scales and biases");
+    if (hidden_stride_elements < c.d || hidden_stride_elements % 4 != 0)
+        return bad(SHRIKE_EINVAL, "static router: hidden stride must be >= d and a multiple of 4 elements");
+    float* logits = nullptr;
+    cudaError_t e = static_logits_for_current_device(&logits);
+    if (e != cudaSuccess) return bad(SHRIKE_EIO, cudaGetErrorString(e));
+
+    RouterArgs a = {};
+    a.w = ops->weights; a.scales = ops->scales; a.biases = ops->biases; a.bits = c.router_weight_bits;
+    a.gate_row = (ops->shared_gate && out_shared_gate) ? ops->shared_gate : nullptr;
+    a.eff_scale = ops->effective_scale; a.logit_bias = ops->logit_bias; a.per_expert_scale = ops->per_expert_scale;
+    a.hidden = hidden; a.T = query_count; a.stride = hidden_stride_elements; a.dt = c.act_dtype;
+    a.ne = c.num_experts; a.d = c.d; a.top_k = c.top_k;
+    a.sigmoid_scores = c.router_kind == SHRIKE_ROUTER_SIGMOID; a.scaling = c.routed_scaling;
+    a.round_f16 = c.round_route_weights_f16; a.logits = logits; a.ids = out_indices; a.weights = out_weights;
+    a.gate_out = out_shared_gate;
+    const uint32_t rows = a.ne + (a.gate_row ? 1u : 0u);
+    const uint32_t tpb = query_count > 8 ? 4 : 1;
+    a.tokens_per_block = tpb;
+    cudaStream_t st = (cudaStream_t)stream;
+    router_logits_kernel<<<dim3((rows + kRouterWarps - 1) / kRouterWarps, (query_count + tpb - 1) / tpb),
+                           kRouterWarps * 32, 0, st>>>(a);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return bad(SHRIKE_EIO, cudaGetErrorString(e));
+    router_select_kernel<<<(query_count + 3) / 4, 128, 0, st>>>(a);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return bad(SHRIKE_EIO, cudaGetErrorString(e));
+    return SHRIKE_OK;
+}
+

@@ -278,6 +278,29 @@ class MoE:
             weights_host.data_ptr() if weights_host is not None else None))
 
 
+def encode_router_static(config: MoEConfig, operands: RouterOperands, hidden: torch.Tensor,
+                         out_indices: torch.Tensor, out_weights: torch.Tensor,
+                         out_shared_gate: Optional[torch.Tensor] = None, query_count: Optional[int] = None,
+                         hidden_stride_elements: Optional[int] = None) -> None:
+    """The router without a handle and without any allocation (`shrike_encode_router_static`).
+
+    For hosts that cannot call cudaMalloc once their expert pool owns the device's memory or inside
+    their decode loop: the logits scratch is a 64 KiB array built into the library, so at most 64 rows
+    and 256 experts per call. Calls that overlap on the GPU share that array and race; make the first
+    call on a device outside stream capture.
+    """
+    lib = capi.load()
+    q = hidden.shape[0] if query_count is None else query_count
+    stride = hidden.stride(0) if hidden_stride_elements is None else hidden_stride_elements
+    cfg = config.to_c()
+    ops = operands.to_c()
+    text = C.create_string_buffer(256)
+    rc = lib.shrike_encode_router_static(C.byref(cfg), _stream(), C.byref(ops), hidden.data_ptr(), q, stride,
+                                         _ptr(out_indices), _ptr(out_weights), _ptr(out_shared_gate), text, 256)
+    if rc:
+        raise ShrikeError(rc, text.value.decode())
+
+
 class ExpertCellArena:
     """`ExpertCellArena` (ExpertCellArena.swift:16-132): cells of whole expert blocks in HBM."""
 
