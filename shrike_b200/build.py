@@ -69,5 +69,26 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     return LIB
 
 
+HARNESS = OUT_DIR / "harness"
+
+
+def build_harness(force: bool = False) -> Path:
+    """Compiles the C++ host harness (shrike_b200/host) against the library with g++."""
+    src = ROOT / "host" / "harness.cpp"
+    hdr = ROOT / "host" / "shrike_moe.hpp"
+    build()
+    if not force and HARNESS.exists() and HARNESS.stat().st_mtime >= max(src.stat().st_mtime, hdr.stat().st_mtime,
+                                                                         LIB.stat().st_mtime):
+        return HARNESS
+    cuda = Path(_nvcc()).resolve().parent.parent if _nvcc() != "nvcc" else Path("/usr/local/cuda")
+    cmd = ["g++", "-std=c++17", "-O2", str(src), "-o", str(HARNESS), f"-I{cuda / 'include'}",
+           f"-L{OUT_DIR}", "-lshrike_b200", f"-L{cuda / 'lib64'}", "-lcudart",
+           f"-Wl,-rpath,{OUT_DIR}", f"-Wl,-rpath,{cuda / 'lib64'}"]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"g++ failed on harness.cpp:\n{res.stdout}\n{res.stderr}")
+    return HARNESS
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
