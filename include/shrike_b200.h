@@ -277,6 +277,32 @@ int shrike_encode_group_pairs(shrike_moe* moe, void* stream, const uint32_t* top
                               uint32_t* sorted_pairs, uint32_t* per_expert_offsets,
                               uint32_t* per_expert_counts);
 
+/* ---- expert parallelism (no counterpart in the reference, which runs on one
+ * device): rank r owns experts [r*experts_per_rank, (r+1)*experts_per_rank).
+ * The three calls bracket the host's two all-to-all exchanges (NCCL).
+ *
+ * dispatch: packs, per destination rank g, the rows that have an expert on g --
+ * one copy per (row, rank), in row order -- into send_x[g][0..count_g) with the
+ * expert ids local to g (0xffffffff for the row's other experts) and the route
+ * weights. Buffers are [world x capacity_rows x ...] so that the exchange is a
+ * fixed-size all-to-all; capacity_rows >= query_count always suffices.
+ * row_of[row*world + g] = the row's index at g, or -1. */
+int shrike_ep_encode_dispatch(shrike_moe* moe, void* stream, const void* x, const uint32_t* topk_indices,
+                              const float* routing_weights, uint32_t query_count, uint32_t world,
+                              uint32_t experts_per_rank, uint32_t capacity_rows, void* send_x,
+                              uint32_t* send_ids, float* send_weights, uint32_t* send_counts,
+                              int32_t* row_of);
+/* On the receiving rank (`moe` is the handle of its local experts): received
+ * local ids -> pool cells through the residency table; invalid ids miss. */
+int shrike_ep_encode_local_slots(shrike_moe* moe, void* stream, const uint32_t* recv_ids,
+                                 const uint64_t* residency_table_row, uint32_t rows,
+                                 uint32_t* resolved_slots);
+/* Back on the home rank: y = y_home (the shared-expert term, may be NULL) + the
+ * partial rows returned by every rank, in rank order; hidden += y. */
+int shrike_ep_encode_combine(shrike_moe* moe, void* stream, const void* recv_y, const int32_t* row_of,
+                             const void* y_home, uint32_t query_count, uint32_t world,
+                             uint32_t capacity_rows, void* y, void* hidden);
+
 /* The router for callers that cannot allocate. No counterpart in the reference.
  * Creating a handle sizes a workspace with cudaMalloc; a host that has already
  * given all free HBM to its expert pool, that fixes its memory plan before the

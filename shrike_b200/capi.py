@@ -88,6 +88,9 @@ SIGNATURES = {
     "shrike_encode_moe_prefill": (_INT, [_P, _P, _P, C.POINTER(ExpertOffsets), _P, _P, _P, _P, _U32,
                                          C.POINTER(SharedExpert), _P, _P, _P]),
     "shrike_encode_group_pairs": (_INT, [_P, _P, _P, _P, _U32, _P, _P, _P]),
+    "shrike_ep_encode_dispatch": (_INT, [_P, _P, _P, _P, _P, _U32, _U32, _U32, _U32, _P, _P, _P, _P, _P]),
+    "shrike_ep_encode_local_slots": (_INT, [_P, _P, _P, _P, _U32, _P]),
+    "shrike_ep_encode_combine": (_INT, [_P, _P, _P, _P, _P, _U32, _U32, _U32, _P, _P]),
     "shrike_moe_layer_forward_host": (_INT, [_P, _P, _P, C.POINTER(ExpertOffsets), _P,
                                              C.POINTER(RouterOperands), C.POINTER(SharedExpert),
                                              _P, _U32, _P, _P, _P]),

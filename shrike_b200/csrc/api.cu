@@ -562,6 +562,49 @@ int shrike_encode_group_pairs(shrike_moe* m, void* stream, const uint32_t* topk_
     return SHRIKE_OK;
 }
 
+// ---- expert parallelism ---------------------------------------------------------
+
+int shrike_ep_encode_dispatch(shrike_moe* m, void* stream, const void* x, const uint32_t* topk_indices,
+                              const float* routing_weights, uint32_t query_count, uint32_t world,
+                              uint32_t experts_per_rank, uint32_t capacity_rows, void* send_x, uint32_t* send_ids,
+                              float* send_weights, uint32_t* send_counts, int32_t* row_of) {
+    if (!m) return SHRIKE_EINVAL;
+    if (!x || !topk_indices || !routing_weights || !send_x || !send_ids || !send_weights || !send_counts || !row_of)
+        return fail(m, SHRIKE_EINVAL, "ep dispatch: null operand");
+    if (world == 0 || world > 64 || experts_per_rank == 0 || (uint64_t)world * experts_per_rank < m->cfg.num_experts)
+        return fail(m, SHRIKE_EINVAL, "ep dispatch: world x experts_per_rank must cover num_experts");
+    if (query_count > m->cfg.max_tokens) return fail(m, SHRIKE_ERANGE, "query_count exceeds max_tokens");
+    if (capacity_rows < query_count)
+        return fail(m, SHRIKE_ERANGE, "ep dispatch: capacity_rows must be at least query_count (a row goes to a rank at most once)");
+    if (query_count == 0) {
+        CU(cudaMemsetAsync(send_counts, 0, world * 4, (cudaStream_t)stream));
+        return SHRIKE_OK;
+    }
+    CU(launch_ep_dispatch(m, (cudaStream_t)stream, x, topk_indices, routing_weights, query_count, world,
+                          experts_per_rank, capacity_rows, send_x, send_ids, send_weights, send_counts, row_of));
+    return SHRIKE_OK;
+}
+
+int shrike_ep_encode_local_slots(shrike_moe* m, void* stream, const uint32_t* recv_ids,
+                                 const uint64_t* residency_table_row, uint32_t rows, uint32_t* resolved_slots) {
+    if (!m) return SHRIKE_EINVAL;
+    if (!recv_ids || !residency_table_row || !resolved_slots) return fail(m, SHRIKE_EINVAL, "ep local slots: null operand");
+    if (rows == 0) return SHRIKE_OK;
+    CU(launch_ep_local_slots(m, (cudaStream_t)stream, recv_ids, residency_table_row, rows, resolved_slots));
+    return SHRIKE_OK;
+}
+
+int shrike_ep_encode_combine(shrike_moe* m, void* stream, const void* recv_y, const int32_t* row_of,
+                             const void* y_home, uint32_t query_count, uint32_t world, uint32_t capacity_rows,
+                             void* y, void* hidden) {
+    if (!m) return SHRIKE_EINVAL;
+    if (!recv_y || !row_of || !y) return fail(m, SHRIKE_EINVAL, "ep combine: null operand");
+    if (query_count == 0) return SHRIKE_OK;
+    CU(launch_ep_combine(m, (cudaStream_t)stream, recv_y, row_of, y_home, query_count, world, capacity_rows, y,
+                         hidden));
+    return SHRIKE_OK;
+}
+
 int shrike_moe_layer_forward_host(shrike_moe* m, void* stream, const shrike_pool* pool,
                                   const shrike_expert_offsets* routed_offsets,
                                   const uint64_t* residency_table_row, const shrike_router_operands* router,

@@ -151,3 +151,15 @@ cudaError_t launch_prefill_combine(const shrike_moe* m, cudaStream_t st, const f
                                    const float* shared_gate, const uint32_t* slots, uint32_t T, void* y,
                                    void* hidden);
 }  // namespace shrike
+
+namespace shrike {
+// ep.cu
+cudaError_t launch_ep_dispatch(const shrike_moe* m, cudaStream_t st, const void* x, const uint32_t* ids,
+                               const float* weights, uint32_t T, uint32_t world, uint32_t experts_per_rank,
+                               uint32_t cap, void* send_x, uint32_t* send_ids, float* send_w,
+                               uint32_t* send_counts, int32_t* row_of);
+cudaError_t launch_ep_local_slots(const shrike_moe* m, cudaStream_t st, const uint32_t* recv_ids,
+                                  const uint64_t* table, uint32_t rows, uint32_t* slots);
+cudaError_t launch_ep_combine(const shrike_moe* m, cudaStream_t st, const void* recv_y, const int32_t* row_of,
+                              const void* y_home, uint32_t T, uint32_t world, uint32_t cap, void* y, void* hidden);
+}  // namespace shrike

@@ -1,0 +1,116 @@
+"""Expert-parallel MoE layer: one process per GPU, routed experts sharded over the ranks.
+
+Rank r owns experts [r*NE/G, (r+1)*NE/G). Rows are sharded by home rank; the router and the shared
+expert are replicated and run on the home rank. Per layer: route -> dispatch (pack) -> all-to-all ->
+local experts -> all-to-all -> combine. The exchanges are fixed-capacity `all_to_all_single` calls over
+the process group (NCCL on GPUs: NVLink/NVSwitch), so no sizes are negotiated and nothing syncs with the
+host inside a layer. torch.distributed is plumbing; packing, expert compute and combine are this
+library's kernels.
+"""
+from __future__ import annotations
+
+import dataclasses
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from . import capi
+from .moe import ExpertCellArena, MoE, MoEConfig, RouterOperands, _ptr, _stream, expert_offsets, round_up
+
+
+def shard_range(num_experts: int, world: int, rank: int) -> tuple[int, int]:
+    """Experts [lo, hi) owned by `rank` (equal shards; num_experts must divide evenly)."""
+    if num_experts % world:
+        raise ValueError("num_experts must be a multiple of the world size")
+    per = num_experts // world
+    return rank * per, (rank + 1) * per
+
+
+class ExpertParallelLayer:
+    """One MoE layer under expert parallelism on this rank's GPU."""
+
+    def __init__(self, config: MoEConfig, rank: int, world: int, device: int, rows_per_rank: int,
+                 group: Optional[dist.ProcessGroup] = None):
+        self.cfg = config
+        self.rank, self.world, self.group = rank, world, group
+        self.rows = rows_per_rank
+        self.cap = rows_per_rank  # a row goes to a rank at most once
+        self.lo, self.hi = shard_range(config.num_experts, world, rank)
+        self.epr = self.hi - self.lo
+        self.dev = torch.device("cuda", device)
+        # home handle: router over all experts + the shared expert on this rank's rows
+        self.home = MoE(dataclasses.replace(config, max_tokens=max(rows_per_rank, 1)), device)
+        # routed handle: this rank's experts on every row it may receive
+        recv_rows = world * self.cap
+        self.routed = MoE(dataclasses.replace(config, num_experts=self.epr, has_shared=False, shared_gated=False,
+                                              shared_f=0, max_tokens=max(recv_rows, 65)), device)
+        self.offsets, self.block_bytes = expert_offsets(config)
+        self.pool = ExpertCellArena(self.routed, self.epr, round_up(self.block_bytes, 256))
+        self.routed.create_residency(1)
+        self.routed.residency_set_layer_identity(0, 0)
+        self.shared: Optional[capi.SharedExpert] = None
+        k, d = config.top_k, config.d
+        act = config.torch_act_dtype
+        T, G, cap = rows_per_rank, world, self.cap
+        z = lambda *shape, dtype: torch.zeros(shape, dtype=dtype, device=self.dev)
+        self.ids, self.w = z(T, k, dtype=torch.int32), z(T, k, dtype=torch.float32)
+        self.gate = z(T, dtype=torch.float32) if config.shared_gated else None
+        self.miss_slots = torch.full((T, k), -1, dtype=torch.int32, device=self.dev)
+        self.send_x, self.recv_x = z(G, cap, d, dtype=act), z(G, cap, d, dtype=act)
+        self.send_ids, self.recv_ids = z(G, cap, k, dtype=torch.int32), z(G, cap, k, dtype=torch.int32)
+        self.send_w, self.recv_w = z(G, cap, k, dtype=torch.float32), z(G, cap, k, dtype=torch.float32)
+        self.send_counts = z(G, dtype=torch.int32)
+        self.row_of = z(T, G, dtype=torch.int32)
+        self.slots = z(G * cap, k, dtype=torch.int32)
+        self.y_part, self.y_back = z(G * cap, d, dtype=act), z(G, cap, d, dtype=act)
+        self.y_home = z(T, d, dtype=act) if config.has_shared else None
+
+    def close(self):
+        self.pool.close()
+        self.routed.close()
+        self.home.close()
+
+    def set_shared(self, shared: capi.SharedExpert) -> None:
+        self.shared = shared
+
+    def _all_to_all(self, out: torch.Tensor, inp: torch.Tensor) -> None:
+        if self.world == 1:
+            out.copy_(inp)
+        else:
+            dist.all_to_all_single(out.view(-1), inp.view(-1), group=self.group)
+
+    def forward(self, router: RouterOperands, x: torch.Tensor, y: torch.Tensor,
+                hidden: Optional[torch.Tensor] = None) -> None:
+        """x, y: this rank's rows [rows_per_rank, d] in the activation dtype."""
+        cfg, T, G, cap = self.cfg, self.rows, self.world, self.cap
+        lib, st = self.home._lib, _stream()
+        self.home.encode_router(router, x, self.ids, self.w, self.gate)
+        self.home._check(lib.shrike_ep_encode_dispatch(
+            self.home._h, st, _ptr(x), _ptr(self.ids), _ptr(self.w), T, G, self.epr, cap, _ptr(self.send_x),
+            _ptr(self.send_ids), _ptr(self.send_w), _ptr(self.send_counts), _ptr(self.row_of)))
+        self._all_to_all(self.recv_x, self.send_x)
+        self._all_to_all(self.recv_ids, self.send_ids)
+        self._all_to_all(self.recv_w, self.send_w)
+        # the shared expert of the home rows does not depend on the exchange
+        if cfg.has_shared:
+            if T <= capi.MAX_DECODE_TOKENS:
+                self.home.encode_decode(self.pool, self.offsets, self.miss_slots, self.w, x, self.y_home, None,
+                                        self.shared, self.gate)
+            else:
+                self.home.encode_prefill(self.pool, self.offsets, self.ids, self.miss_slots, self.w, x, self.y_home,
+                                         None, self.shared, self.gate)
+        rows = G * cap
+        self.routed._check(lib.shrike_ep_encode_local_slots(
+            self.routed._h, st, _ptr(self.recv_ids), self.routed.residency_row(0), rows, _ptr(self.slots)))
+        rx = self.recv_x.view(rows, cfg.d)
+        rw = self.recv_w.view(rows, cfg.top_k)
+        rid = self.recv_ids.view(rows, cfg.top_k)
+        if rows <= capi.MAX_DECODE_TOKENS:
+            self.routed.encode_decode(self.pool, self.offsets, self.slots, rw, rx, self.y_part)
+        else:
+            self.routed.encode_prefill(self.pool, self.offsets, rid, self.slots, rw, rx, self.y_part)
+        self._all_to_all(self.y_back, self.y_part.view(G, cap, cfg.d))
+        self.home._check(lib.shrike_ep_encode_combine(
+            self.home._h, st, _ptr(self.y_back), _ptr(self.row_of), _ptr(self.y_home), T, G, cap, _ptr(y),
+            _ptr(hidden)))
