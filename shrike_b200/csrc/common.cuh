@@ -157,6 +157,22 @@ __device__ __forceinline__ void pdl_launch_dependents() {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 
+// moe_hidden_activation / moe_glu, moe.metal:233-238, 280-288.
+__device__ __forceinline__ float glu(float gate, float up, uint32_t activation) {
+    if (activation == SHRIKE_ACT_CLAMPED_SWIGLU) {
+        const float gc = fminf(gate, 7.0f);
+        const float uc = fmaxf(-7.0f, fminf(up, 7.0f));
+        return (gc / (1.0f + expf(-1.702f * gc))) * (uc + 1.0f);
+    }
+    if (activation == SHRIKE_ACT_GELU_TANH) {
+        const float x3 = gate * gate * gate;
+        float inner = 0.7978845608028654f * (gate + 0.044715f * x3);
+        inner = fmaxf(-20.0f, fminf(inner, 20.0f));
+        return (0.5f * gate * (1.0f + tanhf(inner))) * up;
+    }
+    return (gate / (1.0f + expf(-gate))) * up;
+}
+
 // ---- layout of the fp16 operand copies ------------------------------------
 // The B operand of the skinny MMA tiles is a copy of the activation row in fp16
 // whose aligned blocks of 8 elements are stored in the order the nibble

@@ -79,6 +79,8 @@ struct Workspace {
     uint32_t* expert_counts = nullptr;
     uint32_t* slot_of_expert = nullptr;
     float* partials = nullptr;      // prefill: per-pair down outputs
+    void* chunk_inst = nullptr;     // prefill: instances of up to 128 rows (tensor-core path)
+    uint32_t* n_chunk_inst = nullptr;
     // forward_host staging
     void* x_dev = nullptr; void* y_dev = nullptr;
     uint32_t* ids_dev = nullptr; float* w_dev = nullptr; float* gate_dev = nullptr;
@@ -162,4 +164,12 @@ cudaError_t launch_ep_local_slots(const shrike_moe* m, cudaStream_t st, const ui
                                   const uint64_t* table, uint32_t rows, uint32_t* slots);
 cudaError_t launch_ep_combine(const shrike_moe* m, cudaStream_t st, const void* recv_y, const int32_t* row_of,
                               const void* y_home, uint32_t T, uint32_t world, uint32_t cap, void* y, void* hidden);
+}  // namespace shrike
+
+namespace shrike {
+// umma_gemm.cu
+uint32_t umma_max_chunk_instances(const shrike_moe_config& c, uint32_t T);
+size_t umma_chunk_instance_bytes();
+cudaError_t launch_umma_prefill(const shrike_moe* m, cudaStream_t st, const ExpertArgs& a, uint32_t T,
+                                uint32_t pool_cells, float* partials, float* partial_shared);
 }  // namespace shrike
