@@ -94,6 +94,7 @@ struct RouterArgs {
     float* weights;
     float* gate_out;
     uint32_t tokens_per_block;
+    uint32_t row_base;             // first row of this launch (the tiled prefill router leaves only the gate row)
     // fused decode tail (route_fused_kernel only)
     const uint64_t* table;
     uint32_t pool_cells;
@@ -185,7 +186,7 @@ __device__ __forceinline__ float lane_dot_affine(const uint8_t* row, const uint1
 template <int N, bool PRED, typename Pre>
 __device__ __forceinline__ void logits_rows(const RouterArgs& a, Pre pre) {
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t e = blockIdx.x * kRouterWarps + warp;
+    const uint32_t e = a.row_base + blockIdx.x * kRouterWarps + warp;
     const bool is_gate = a.gate_row != nullptr && e == a.ne;
     const bool active = e < a.ne || is_gate;
     const bool f32row = a.bits == 0 || is_gate;
@@ -296,6 +297,173 @@ __device__ __forceinline__ void select_row(const float* lg, const RouterArgs& a,
 // grid (ceil((ne + has_gate)/4), token blocks)
 __global__ void __launch_bounds__(kRouterWarps * 32) router_logits_kernel(const RouterArgs a) {
     logits_body(a, [] {});
+}
+
+// ---- prefill router: register-tiled logits ---------------------------------------
+//
+// Hundreds of rows against the same fp32 router matrix: the warp-per-row kernel
+// above re-reads every activation row once per expert row and stalls on those
+// loads. Here a block owns 32 expert rows x 32 tokens, stages both operands in
+// shared memory (activations converted to fp32 once per block), and a warp
+// accumulates an 8 x 16 register tile. Lane l still owns the float4 chunks
+// l, l+32, ... of every row and walks them in order with one fused multiply-add
+// per element, and the 32 lane sums still meet in the xor 16..1 butterfly, so
+// each logit is the same sequence of roundings as in the warp-per-row kernel.
+// Chunks past the end of a row are staged as zeros: adding +0 changes nothing.
+constexpr int kTileRows = 32, kTileTokens = 32, kTileStage = 256;   // 256 elements of K per stage
+constexpr int kTileWarpRows = 8, kTileWarpTokens = 16;
+constexpr size_t kTileSmemBytes = 2 * (size_t)(kTileRows + kTileTokens) * kTileStage * sizeof(float);
+
+__device__ __forceinline__ void cp_async_16_zfill(uint32_t smem_addr, const void* gptr, bool valid) {
+    const uint32_t n = valid ? 16u : 0u;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_addr), "l"(gptr), "r"(n) : "memory");
+}
+
+__global__ void __launch_bounds__(256, 1) router_logits_tiled_kernel(const RouterArgs a) {
+    extern __shared__ __align__(16) float tile_smem[];
+    float* const w_s = tile_smem;                                           // [2][32][256]
+    float* const x_s = tile_smem + 2 * kTileRows * kTileStage;              // [2][32][256]
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t e0 = blockIdx.x * kTileRows, t0 = blockIdx.y * kTileTokens;
+    const uint32_t chunks = a.d / 4;
+    const uint32_t stages = (a.d + kTileStage - 1) / kTileStage;
+    const size_t esz = a.dt == SHRIKE_DTYPE_FP32 ? 4 : 2;
+
+    // staging roles: thread -> (row, 8 chunks of 4 floats) of each operand tile
+    const uint32_t srow = tid >> 3, sc0 = (tid & 7) * 8;                    // 32 rows x 8 threads x 8 chunks
+    const uint32_t wrow = min(e0 + srow, a.ne - 1), xtok = min(t0 + srow, a.T - 1);
+    const float* const wsrc = (const float*)a.w + (size_t)wrow * a.d;
+    const uint8_t* const xsrc = (const uint8_t*)a.hidden + (size_t)xtok * a.stride * esz;
+
+    uint4 xr[8];   // the next stage's activations: 32 elements (16-bit) or 2 x 16 (fp32)
+    auto fetch_w = [&](uint32_t s, uint32_t buf) {
+        const uint32_t dst = (uint32_t)__cvta_generic_to_shared(w_s + ((size_t)buf * kTileRows + srow) * kTileStage);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const uint32_t c = s * (kTileStage / 4) + sc0 + j;
+            cp_async_16_zfill(dst + (sc0 + j) * 16, wsrc + (size_t)min(c, chunks - 1) * 4, c < chunks);
+        }
+        cp_async_commit();
+    };
+    auto fetch_x = [&](uint32_t s) {
+        if (a.dt == SHRIKE_DTYPE_FP32) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const uint32_t c = s * (kTileStage / 4) + sc0 + j;
+                xr[j] = c < chunks ? __ldg((const uint4*)xsrc + c) : make_uint4(0, 0, 0, 0);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const uint32_t c = s * (kTileStage / 4) + sc0 + 2 * j;       // two chunks per 16 bytes
+                xr[j] = c < chunks ? __ldg((const uint4*)xsrc + c / 2) : make_uint4(0, 0, 0, 0);
+            }
+        }
+    };
+    auto store_x = [&](uint32_t s, uint32_t buf) {
+        float4* const dst = (float4*)(x_s + ((size_t)buf * kTileTokens + srow) * kTileStage) + sc0;
+        const uint2* const es = a.eff_scale ? (const uint2*)a.eff_scale + s * (kTileStage / 4) + sc0 : nullptr;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            float4 v;
+            if (a.dt == SHRIKE_DTYPE_FP32) {
+                v = make_float4(__uint_as_float(xr[j].x), __uint_as_float(xr[j].y), __uint_as_float(xr[j].z),
+                                __uint_as_float(xr[j].w));
+            } else {
+                const uint32_t lo = (j & 1) ? xr[j / 2].z : xr[j / 2].x, hi = (j & 1) ? xr[j / 2].w : xr[j / 2].y;
+                if (a.dt == SHRIKE_DTYPE_FP16)
+                    v = make_float4(f16_bits_to_f32(lo & 0xffff), f16_bits_to_f32(lo >> 16), f16_bits_to_f32(hi & 0xffff),
+                                    f16_bits_to_f32(hi >> 16));
+                else
+                    v = make_float4(__uint_as_float(lo << 16), __uint_as_float(lo & 0xffff0000u),
+                                    __uint_as_float(hi << 16), __uint_as_float(hi & 0xffff0000u));
+            }
+            if (es && s * (kTileStage / 4) + sc0 + j < chunks) {
+                const uint2 q = __ldg(es + j);
+                v.x = __fmul_rn(v.x, __uint_as_float(q.x << 16));
+                v.y = __fmul_rn(v.y, __uint_as_float(q.x & 0xffff0000u));
+                v.z = __fmul_rn(v.z, __uint_as_float(q.y << 16));
+                v.w = __fmul_rn(v.w, __uint_as_float(q.y & 0xffff0000u));
+            }
+            dst[j] = v;
+        }
+    };
+
+    float acc[kTileWarpRows][kTileWarpTokens];
+#pragma unroll
+    for (int r = 0; r < kTileWarpRows; ++r)
+#pragma unroll
+        for (int t = 0; t < kTileWarpTokens; ++t) acc[r][t] = 0.f;
+
+    fetch_w(0, 0);
+    fetch_x(0);
+    store_x(0, 0);
+    cp_async_wait<0>();
+    __syncthreads();
+
+    const uint32_t rg = warp & 3, tg = warp >> 2;
+    for (uint32_t s = 0; s < stages; ++s) {
+        const uint32_t buf = s & 1;
+        const bool more = s + 1 < stages;
+        if (more) {
+            fetch_w(s + 1, buf ^ 1);
+            fetch_x(s + 1);
+        }
+        const float4* const wb = (const float4*)(w_s + ((size_t)buf * kTileRows + rg * kTileWarpRows) * kTileStage);
+        const float4* const xb = (const float4*)(x_s + ((size_t)buf * kTileTokens + tg * kTileWarpTokens) * kTileStage);
+#pragma unroll
+        for (int ii = 0; ii < kTileStage / 128; ++ii) {
+            float4 wv[kTileWarpRows];
+#pragma unroll
+            for (int r = 0; r < kTileWarpRows; ++r) wv[r] = wb[r * (kTileStage / 4) + ii * 32 + lane];
+#pragma unroll
+            for (int t = 0; t < kTileWarpTokens; ++t) {
+                const float4 xv = xb[t * (kTileStage / 4) + ii * 32 + lane];
+#pragma unroll
+                for (int r = 0; r < kTileWarpRows; ++r) {
+                    float v = acc[r][t];
+                    v = __fmaf_rn(wv[r].x, xv.x, v);
+                    v = __fmaf_rn(wv[r].y, xv.y, v);
+                    v = __fmaf_rn(wv[r].z, xv.z, v);
+                    v = __fmaf_rn(wv[r].w, xv.w, v);
+                    acc[r][t] = v;
+                }
+            }
+        }
+        if (more) {
+            store_x(s + 1, buf ^ 1);
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+    }
+
+    // butterfly, then lane 2t + (r / 4) stores the four logits (r & ~3 .. +3) of token t
+    float4 out = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int t = 0; t < kTileWarpTokens; ++t)
+#pragma unroll
+        for (int r = 0; r < kTileWarpRows; ++r) {
+            const float v = butterfly_sum(acc[r][t]);
+            if (lane == (uint32_t)(2 * t + r / 4)) {
+                if ((r & 3) == 0) out.x = v;
+                else if ((r & 3) == 1) out.y = v;
+                else if ((r & 3) == 2) out.z = v;
+                else out.w = v;
+            }
+        }
+    const uint32_t tok = t0 + tg * kTileWarpTokens + (lane >> 1);
+    const uint32_t e = e0 + rg * kTileWarpRows + (lane & 1) * 4;
+    if (tok < a.T) {
+        float* const dst = a.logits + (size_t)tok * a.ne + e;
+        if (e + 4 <= a.ne && (a.ne & 3u) == 0) {
+            *(float4*)dst = out;
+        } else {
+            if (e + 0 < a.ne) dst[0] = out.x;
+            if (e + 1 < a.ne) dst[1] = out.y;
+            if (e + 2 < a.ne) dst[2] = out.z;
+            if (e + 3 < a.ne) dst[3] = out.w;
+        }
+    }
 }
 
 __global__ void __launch_bounds__(128) router_select_kernel(const RouterArgs a) {
@@ -496,14 +664,41 @@ cudaError_t launch_router(const shrike_moe* m, cudaStream_t st, const shrike_rou
                           float* weights, float* shared_gate) {
     RouterArgs a = make_router_args(m, ops, hidden, T, stride, ids, weights, shared_gate);
     const uint32_t rows = a.ne + (a.gate_row ? 1u : 0u);
-    uint32_t tpb = 1;
-    if (T > 64) tpb = 32;
-    else if (T > 8) tpb = 4;
-    a.tokens_per_block = tpb;
-    const dim3 grid((rows + kRouterWarps - 1) / kRouterWarps, (T + tpb - 1) / tpb);
-    router_logits_kernel<<<grid, kRouterWarps * 32, 0, st>>>(a);
-    cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess) return e;
+    cudaError_t e;
+    if (T > 256 && a.bits == 0 && a.d % 8 == 0 && stride % 8 == 0 && ((uintptr_t)hidden & 15u) == 0 &&
+        ((uintptr_t)a.w & 15u) == 0) {
+        // tiled logits for the expert rows; the warp-per-row kernel keeps the gate row
+        static bool attr_set[64] = {};
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (dev < 64 && !attr_set[dev]) {
+            e = cudaFuncSetAttribute(router_logits_tiled_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)kTileSmemBytes);
+            if (e != cudaSuccess) return e;
+            attr_set[dev] = true;
+        }
+        const dim3 grid((a.ne + kTileRows - 1) / kTileRows, (T + kTileTokens - 1) / kTileTokens);
+        router_logits_tiled_kernel<<<grid, 256, kTileSmemBytes, st>>>(a);
+        e = cudaGetLastError();
+        if (e != cudaSuccess) return e;
+        if (a.gate_row) {
+            RouterArgs g = a;
+            g.row_base = a.ne;
+            g.tokens_per_block = 8;
+            router_logits_kernel<<<dim3(1, (T + 7) / 8), kRouterWarps * 32, 0, st>>>(g);
+            e = cudaGetLastError();
+            if (e != cudaSuccess) return e;
+        }
+    } else {
+        uint32_t tpb = 1;
+        if (T > 64) tpb = 32;
+        else if (T > 8) tpb = 4;
+        a.tokens_per_block = tpb;
+        const dim3 grid((rows + kRouterWarps - 1) / kRouterWarps, (T + tpb - 1) / tpb);
+        router_logits_kernel<<<grid, kRouterWarps * 32, 0, st>>>(a);
+        e = cudaGetLastError();
+        if (e != cudaSuccess) return e;
+    }
     router_select_kernel<<<(T + 3) / 4, 128, 0, st>>>(a);
     return cudaGetLastError();
 }

@@ -31,7 +31,7 @@
 
 namespace shrike {
 
-constexpr uint32_t kUmmaStages = 4;
+constexpr uint32_t kUmmaStages = 2;
 constexpr uint32_t kUmmaMaxN = 128;
 constexpr uint32_t kUmmaThreads = 160;
 constexpr uint32_t kTileBytes = 128 * 128;  // 128 rows x 64 fp16, one swizzle-128B K block

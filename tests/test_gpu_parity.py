@@ -9,7 +9,7 @@ import pytest
 import torch
 
 import oracle_lib as O
-from gpu_harness import Layer, inputs, rel_l2, small_config, to_act_tensor
+from gpu_harness import Layer, bf16_tensor, inputs, rel_l2, small_config, to_act_tensor
 from shrike_b200 import capi, fixtures as fx
 from shrike_b200.moe import ShrikeError
 
@@ -105,6 +105,46 @@ def test_router_ids_and_weights_exact(cuda_device, router_bits, sigmoid):
     assert (w.cpu().numpy() == w_ref).all()
     g_ref = 1 / (1 + np.exp(-(x.astype(np.float64) @ layer.gate_w.astype(np.float64))))
     assert np.abs(gate.cpu().numpy() - g_ref).max() < 1e-5
+    layer.close()
+
+
+@pytest.mark.parametrize("act_dtype", [capi.DTYPE_FP32, capi.DTYPE_BF16, capi.DTYPE_FP16])
+@pytest.mark.parametrize("d,ne,T", [(2048, 256, 300), (2304, 40, 257), (128, 16, 1000), (2880, 32, 290)])
+def test_prefill_router_tiled_logits_exact(cuda_device, act_dtype, d, ne, T):
+    """More than 256 rows take the register-tiled logits kernel: ragged row, expert and K tiles,
+    every activation type, and the same ids / weights / gate as the oracle, bit for bit."""
+    cfg = small_config(d=d, num_experts=ne, top_k=8, act_dtype=act_dtype, max_tokens=1024)
+    layer = Layer(cfg, router_sigma=0.05)
+    x = inputs(T, d, seed=31)
+    if act_dtype == capi.DTYPE_FP16:
+        x = x.astype(np.float16).astype(np.float32)
+    ids, w, gate = layer.route(to_act_tensor(x, act_dtype, layer.device))
+    ids_ref, w_ref, _ = layer.oracle_route(x)
+    assert (ids.cpu().numpy().astype(np.uint32) == ids_ref).all()
+    assert (w.cpu().numpy() == w_ref).all()
+    # the first rows through the warp-per-row kernel (fewer than 257 rows) must agree exactly
+    ids_s, w_s, gate_s = layer.route(to_act_tensor(x[:200], act_dtype, layer.device))
+    assert (ids_s == ids[:200]).all() and (w_s == w[:200]).all() and (gate_s == gate[:200]).all()
+    layer.close()
+
+
+def test_prefill_router_effective_scale_and_stride(cuda_device):
+    """Tiled and warp-per-row logits with the per-element activation scale and a row stride:
+    the same as routing the pre-scaled fp32 rows, packed."""
+    d, T = 256, 400
+    cfg = small_config(d=d, num_experts=32, top_k=4, act_dtype=capi.DTYPE_FP32, max_tokens=512, has_shared=False,
+                       shared_gated=False)
+    layer = Layer(cfg, router_sigma=0.05)
+    x = inputs(T, d, seed=33)
+    es = fx.round_bf16(np.random.default_rng(5).uniform(0.5, 1.5, d).astype(np.float32))
+    ids_ref, w_ref, _ = layer.oracle_route((x * es).astype(np.float32))
+    layer.router_ops.effective_scale = bf16_tensor(es, layer.device)
+    wide = np.full((T, d + 64), 3.0, dtype=np.float32)
+    wide[:, :d] = x
+    for rows in (T, 100):
+        ids, w, _ = layer.route(to_act_tensor(wide[:rows], cfg.act_dtype, layer.device), stride=d + 64)
+        assert (ids.cpu().numpy().astype(np.uint32) == ids_ref[:rows]).all()
+        assert (w.cpu().numpy() == w_ref[:rows]).all()
     layer.close()
 
 
