@@ -93,11 +93,12 @@ cudaError_t dev_alloc(P** p, size_t bytes) {
 }
 
 void free_workspace(Workspace& w) {
-    void* ptrs[] = {w.chunk_inst, w.n_chunk_inst, w.done_counter, w.xsum, w.logits, w.xh, w.acts, w.acts_shared, w.sorted, w.inst, w.n_inst, w.status, w.block_hist,
+    void* ptrs[] = {w.xs, w.chunk_inst, w.n_chunk_inst, w.done_counter, w.xsum, w.logits, w.xh, w.acts, w.acts_shared, w.sorted, w.inst, w.n_inst, w.status, w.block_hist,
                     w.expert_offsets, w.expert_counts, w.slot_of_expert, w.partials, w.x_dev, w.y_dev,
                     w.ids_dev, w.w_dev, w.gate_dev, w.slots_dev, w.counts_dev};
     for (void* p : ptrs)
         if (p) cudaFree(p);
+    free(w.tensor_maps);
     w = Workspace();
 }
 
@@ -196,7 +197,8 @@ int shrike_moe_create(const shrike_moe_config* config, int device, shrike_moe** 
     A(&w.slot_of_expert, c.num_experts * 4);
     A(&w.partials, T > SHRIKE_MAX_DECODE_TOKENS ? (T * K + (c.has_shared ? T : 0)) * c.d * 4 : 0);
     A(&w.chunk_inst, T > SHRIKE_MAX_DECODE_TOKENS ? umma_max_chunk_instances(c, c.max_tokens) * umma_chunk_instance_bytes() : 0);
-    A(&w.n_chunk_inst, 4);
+    A(&w.n_chunk_inst, 8);
+    A(&w.xs, T > SHRIKE_MAX_DECODE_TOKENS ? T * K * c.d * 2 : 0);
     A(&w.x_dev, T * c.d * ab);
     A(&w.y_dev, T * c.d * ab);
     A(&w.ids_dev, T * K * 4);
@@ -209,6 +211,19 @@ int shrike_moe_create(const shrike_moe_config* config, int device, shrike_moe** 
         delete m;
         cudaGetLastError();
         return fail(nullptr, SHRIKE_ENOMEM, "device allocation of the workspace failed");
+    }
+    if (T <= SHRIKE_MAX_DECODE_TOKENS) {   // decode-only handle: no prefill operands
+        cudaFree(w.xs);
+        w.xs = nullptr;
+    } else {
+        w.tensor_maps = aligned_alloc(64, umma_tensor_map_bytes());
+        const cudaError_t me = w.tensor_maps ? umma_prepare(m) : cudaErrorMemoryAllocation;
+        if (me != cudaSuccess) {
+            free_workspace(w);
+            delete m;
+            cudaGetLastError();
+            return fail(nullptr, SHRIKE_EIO, "TMA descriptors of the prefill operands: %s", cudaGetErrorString(me));
+        }
     }
     cudaMemset(w.status, 0, 4);
     cudaMemset(w.done_counter, 0, 4);
@@ -544,13 +559,14 @@ int shrike_encode_moe_prefill(shrike_moe* m, void* stream, const shrike_pool* po
     if (rc) return rc;
     cudaStream_t st = (cudaStream_t)stream;
     const uint32_t mi = max_instances(m->cfg, query_count);
-    CU(launch_prefill_plan(m, st, topk_indices, resolved_slots, x, query_count, m->cfg.has_shared != 0,
-                           pool->view.cells));
-    float* partial_shared = m->ws.partials + (size_t)m->cfg.max_tokens * m->cfg.top_k * m->cfg.d;
     // SHRIKE_PREFILL_PATH=mma keeps every expert on the 8-row warp-MMA tiles (the decode kernels);
     // the default runs the expert-grouped GEMM on the tcgen05 tensor cores.
     const char* path = getenv("SHRIKE_PREFILL_PATH");
-    if (path && strcmp(path, "mma") == 0) {
+    const bool warp_mma = path && strcmp(path, "mma") == 0;
+    CU(launch_prefill_plan(m, st, topk_indices, resolved_slots, x, query_count, m->cfg.has_shared != 0,
+                           pool->view.cells, warp_mma));
+    float* partial_shared = m->ws.partials + (size_t)m->cfg.max_tokens * m->cfg.top_k * m->cfg.d;
+    if (warp_mma) {
         CU(launch_phase1(m, st, a, mi, false));
         CU(launch_phase2_partials(m, st, a, mi, m->ws.partials, partial_shared));
     } else {

@@ -79,8 +79,10 @@ struct Workspace {
     uint32_t* expert_counts = nullptr;
     uint32_t* slot_of_expert = nullptr;
     float* partials = nullptr;      // prefill: per-pair down outputs
-    void* chunk_inst = nullptr;     // prefill: instances of up to 128 rows (tensor-core path)
-    uint32_t* n_chunk_inst = nullptr;
+    void* chunk_inst = nullptr;     // prefill: instances of up to 256 rows (tensor-core path)
+    uint32_t* n_chunk_inst = nullptr; // [0] instances, [1] sorted rows
+    uint16_t* xs = nullptr;         // prefill: fp16 activation rows in expert-sorted order [max_tokens x top_k x d]
+    void* tensor_maps = nullptr;    // host: the TMA descriptors of xs, acts, xh, acts_shared
     // forward_host staging
     void* x_dev = nullptr; void* y_dev = nullptr;
     uint32_t* ids_dev = nullptr; float* w_dev = nullptr; float* gate_dev = nullptr;
@@ -148,7 +150,7 @@ cudaError_t launch_phase2_partials(const shrike_moe* m, cudaStream_t st, const E
 // prefill.cu
 cudaError_t launch_prefill_plan(const shrike_moe* m, cudaStream_t st, const uint32_t* ids,
                                 const uint32_t* slots, const void* x, uint32_t T, bool with_shared,
-                                uint32_t pool_cells);
+                                uint32_t pool_cells, bool warp_mma_instances);
 cudaError_t launch_prefill_combine(const shrike_moe* m, cudaStream_t st, const float* route_w,
                                    const float* shared_gate, const uint32_t* slots, uint32_t T, void* y,
                                    void* hidden);
@@ -170,6 +172,8 @@ namespace shrike {
 // umma_gemm.cu
 uint32_t umma_max_chunk_instances(const shrike_moe_config& c, uint32_t T);
 size_t umma_chunk_instance_bytes();
+size_t umma_tensor_map_bytes();
+cudaError_t umma_prepare(shrike_moe* m);
 cudaError_t launch_umma_prefill(const shrike_moe* m, cudaStream_t st, const ExpertArgs& a, uint32_t T,
                                 uint32_t pool_cells, float* partials, float* partial_shared);
 }  // namespace shrike

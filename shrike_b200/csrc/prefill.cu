@@ -111,7 +111,7 @@ prefill_combine_kernel(const float* __restrict__ partials, const float* __restri
 
 cudaError_t launch_prefill_plan(const shrike_moe* m, cudaStream_t st, const uint32_t* ids,
                                 const uint32_t* slots, const void* x, uint32_t T, bool with_shared,
-                                uint32_t pool_cells) {
+                                uint32_t pool_cells, bool warp_mma_instances) {
     const shrike_moe_config& c = m->cfg;
     const Workspace& ws = m->ws;
     cudaError_t e = cudaMemsetAsync(ws.slot_of_expert, 0xff, c.num_experts * 4, st);
@@ -121,9 +121,10 @@ cudaError_t launch_prefill_plan(const shrike_moe* m, cudaStream_t st, const uint
                                                                          ws.slot_of_expert);
     e = launch_group_pairs(m, st, ids, nullptr, T, nullptr, ws.expert_offsets, ws.expert_counts);
     if (e != cudaSuccess) return e;
-    prefill_instances_kernel<<<1, 256, 0, st>>>(ws.expert_offsets, ws.expert_counts, ws.slot_of_expert,
-                                                c.num_experts, T, with_shared ? 1u : 0u, pool_cells, ws.sorted, ws.inst,
-                                                ws.n_inst, ws.status);
+    if (warp_mma_instances)   // the tensor-core path builds its own 256-row instances
+        prefill_instances_kernel<<<1, 256, 0, st>>>(ws.expert_offsets, ws.expert_counts, ws.slot_of_expert,
+                                                    c.num_experts, T, with_shared ? 1u : 0u, pool_cells, ws.sorted,
+                                                    ws.inst, ws.n_inst, ws.status);
     const uint32_t items = T * (c.d / 8);
     prefill_xprep_kernel<<<min(2048u, (items + 255) / 256), 256, 0, st>>>(
         x, T, c.d, c.group_size, c.act_dtype, c.weight_bits == 4 ? 1u : 0u, ws.xh, ws.xsum);

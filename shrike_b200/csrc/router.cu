@@ -684,8 +684,8 @@ cudaError_t launch_router(const shrike_moe* m, cudaStream_t st, const shrike_rou
         if (a.gate_row) {
             RouterArgs g = a;
             g.row_base = a.ne;
-            g.tokens_per_block = 8;
-            router_logits_kernel<<<dim3(1, (T + 7) / 8), kRouterWarps * 32, 0, st>>>(g);
+            g.tokens_per_block = 1;
+            router_logits_kernel<<<dim3(1, T), kRouterWarps * 32, 0, st>>>(g);
             e = cudaGetLastError();
             if (e != cudaSuccess) return e;
         }
