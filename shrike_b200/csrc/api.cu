@@ -559,10 +559,11 @@ int shrike_encode_moe_prefill(shrike_moe* m, void* stream, const shrike_pool* po
     if (rc) return rc;
     cudaStream_t st = (cudaStream_t)stream;
     const uint32_t mi = max_instances(m->cfg, query_count);
-    // SHRIKE_PREFILL_PATH=mma keeps every expert on the 8-row warp-MMA tiles (the decode kernels);
-    // the default runs the expert-grouped GEMM on the tcgen05 tensor cores.
+    // The default runs the expert-grouped GEMM on the tcgen05 tensor cores. Shapes whose scale rows are
+    // not whole 16-byte units (the TMA copies need that), and SHRIKE_PREFILL_PATH=mma, keep every expert
+    // on the 8-row warp-MMA tiles (the decode kernels).
     const char* path = getenv("SHRIKE_PREFILL_PATH");
-    const bool warp_mma = path && strcmp(path, "mma") == 0;
+    const bool warp_mma = (path && strcmp(path, "mma") == 0) || !umma_supported(m->cfg);
     CU(launch_prefill_plan(m, st, topk_indices, resolved_slots, x, query_count, m->cfg.has_shared != 0,
                            pool->view.cells, warp_mma));
     float* partial_shared = m->ws.partials + (size_t)m->cfg.max_tokens * m->cfg.top_k * m->cfg.d;

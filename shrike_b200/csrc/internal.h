@@ -174,6 +174,7 @@ uint32_t umma_max_chunk_instances(const shrike_moe_config& c, uint32_t T);
 size_t umma_chunk_instance_bytes();
 size_t umma_tensor_map_bytes();
 cudaError_t umma_prepare(shrike_moe* m);
+bool umma_supported(const shrike_moe_config& c);
 cudaError_t launch_umma_prefill(const shrike_moe* m, cudaStream_t st, const ExpertArgs& a, uint32_t T,
                                 uint32_t pool_cells, float* partials, float* partial_shared);
 }  // namespace shrike

@@ -10,18 +10,23 @@
 // reads each activation byte once per 256 weight rows and dequantises each
 // weight once per 256 activation rows.
 //
-//   warps 0-7  producers: each thread owns one weight row; per 64-wide K block
+//   warp 10    one thread streams the packed weights (64 bytes of every row
+//              per copy: a 3-D TMA box of 128 rows of one matrix of one pool
+//              cell, 64-byte swizzle) and the group scales / biases (16 bytes
+//              of every row per copy) into shared-memory rings. Whole-line TMA
+//              requests keep the packed experts streaming at HBM speed where
+//              per-thread 32-byte loads ran out of outstanding requests.
+//   warp 9     one thread copies the activation tiles: a 64 x 256 box of the
+//              expert-sorted fp16 rows per K block, 128-byte swizzle.
+//   warps 0-7  converters: each thread owns one weight row; per 64-wide K block
 //              it turns the packed nibbles/bytes into fp16 (q - Z) * scale +
 //              (bias + Z*scale) -- the reference's half(fma(q, scale, bias)),
 //              tensorops.metal:106 -- and writes them, 16 bytes at a time, into
-//              the K-major 128-byte-swizzled shared-memory tile the MMA reads.
-//              Thread 0 also starts the TMA copy of the K block's activation
-//              tile (a 64 x 256 box of the expert-sorted fp16 rows, landing in
-//              the same swizzled layout). After the K loop the same warps run
-//              the epilogue.
+//              the K-major 128-byte-swizzled tile the MMA reads. After the K
+//              loop the same warps run the epilogue.
 //   warp 8     one thread issues tcgen05.mma (M 128, N = rows, K 16, fp16 in,
 //              fp32 accumulate in TMEM) for both tiles and commits to the
-//              stage's mbarrier.
+//              mbarriers that free the converted tile and the activation tile.
 //
 // PHASE 0: tile 0 = 128 gate rows, tile 1 = the matching 128 up rows; epilogue
 //          GLU -> fp16 activations in operand layout, one row per sorted pair.
@@ -31,21 +36,40 @@
 // Every wait is bounded; a wait that gives up sets the status word and the
 // block falls through to the TMEM release.
 #include <cuda.h>
-
-#include <type_traits>
+#ifndef SHRIKE_EXP
+#define SHRIKE_EXP 0
+#endif
 
 #include "internal.h"
 
 namespace shrike {
 
-constexpr uint32_t kUmmaStages = 3;
 constexpr uint32_t kUmmaMaxN = 256;
-constexpr uint32_t kUmmaProducers = 256;
-constexpr uint32_t kUmmaThreads = kUmmaProducers + 32;
-constexpr uint32_t kTileBytes = 128 * 128;              // 128 rows x 64 fp16, one swizzle-128B K block
-constexpr uint32_t kBTileBytes = kUmmaMaxN * 128;       // 256 rows x 64 fp16
-constexpr uint32_t kStageBytes = 2 * kTileBytes + kBTileBytes;
-static_assert(kUmmaStages == 3, "the producers' register buffers double as the stage index");
+constexpr uint32_t kConverters = 256;
+constexpr uint32_t kUmmaThreads = kConverters + 96;    // + MMA warp, activation-copy warp, weight-copy warp
+constexpr uint32_t kAStages = 2, kBStages = 3, kPkSlots = 3;
+constexpr uint32_t kTileBytes = 128 * 128;             // 128 rows x 64 fp16, one swizzle-128B K block
+constexpr uint32_t kAStageBytes = 2 * kTileBytes;      // both weight tiles
+constexpr uint32_t kBTileBytes = kUmmaMaxN * 128;      // 256 rows x 64 fp16
+constexpr uint32_t kPkSlotBytes = 256 * 64;            // 64 packed bytes of 256 rows
+constexpr uint32_t kScHalfBytes = 256 * 16;            // 8 scales (or biases) of 256 rows
+constexpr uint32_t kOffA = kBStages * kBTileBytes;
+constexpr uint32_t kOffPk = kOffA + kAStages * kAStageBytes;
+constexpr uint32_t kOffSc = kOffPk + kPkSlots * kPkSlotBytes;
+constexpr uint32_t kOffBar = kOffSc + 2 * kScHalfBytes;
+constexpr uint32_t kNumBars = 2 * kAStages + 2 * kBStages + 2 * kPkSlots + 3;
+constexpr uint32_t kUmmaSmemBytes = kOffBar + kNumBars * 8 + kUmmaMaxN * 4 + 16 + 1024 /*alignment slack*/;
+
+struct WeightMaps {       // TMA descriptors of the two 128-row tiles of a block
+    CUtensorMap w[2];     // packed weights   [cells][rows][row bytes]
+    CUtensorMap s[2];     // group scales     [cells][rows][groups]
+    CUtensorMap b[2];     // group biases
+};
+struct UmmaMaps {
+    WeightMaps routed[SHRIKE_MAX_POOL_CHUNKS];
+    WeightMaps shared;
+    CUtensorMap act_routed, act_shared;
+};
 
 // ---- tcgen05 wrappers -------------------------------------------------------
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
@@ -131,29 +155,59 @@ __device__ __forceinline__ void tmem_ld16_issue(uint32_t taddr, uint32_t (&r)[16
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
-// 2-D tiled TMA load (no multicast): box origin (x = element column, y = row).
+// Tiled TMA loads (no multicast). x is the element column, then row, then cell.
 __device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const CUtensorMap* map, int32_t x, int32_t y,
                                             uint64_t* bar) {
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
         ::"r"(smem_dst), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
 }
+__device__ __forceinline__ void tma_load_3d(uint32_t smem_dst, const CUtensorMap* map, int32_t x, int32_t y, int32_t z,
+                                            uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+        ::"r"(smem_dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar)) : "memory");
+}
+
+// SiLU / clamped-SwiGLU gates with the fast exponential and reciprocal: the
+// epilogue runs one per output element, and the result is rounded to fp16.
+__device__ __forceinline__ float glu_epilogue(float gate, float up, uint32_t activation) {
+    if (activation == SHRIKE_ACT_CLAMPED_SWIGLU) {
+        const float gc = fminf(gate, 7.0f);
+        const float uc = fmaxf(-7.0f, fminf(up, 7.0f));
+        return __fdividef(gc, 1.0f + __expf(-1.702f * gc)) * (uc + 1.0f);
+    }
+    if (activation == SHRIKE_ACT_GELU_TANH) return glu(gate, up, activation);
+    return __fdividef(gate, 1.0f + __expf(-gate)) * up;
+}
+
+// 16-bit field `idx` (0..7) of four registers.
+__device__ __forceinline__ uint16_t pick16(const uint32_t (&v)[4], uint32_t idx) {
+    const uint32_t lo = (idx & 2u) ? v[1] : v[0], hi = (idx & 2u) ? v[3] : v[2];
+    const uint32_t w = (idx & 4u) ? hi : lo;
+    return (uint16_t)((idx & 1u) ? (w >> 16) : (w & 0xffffu));
+}
 
 struct ChunkInstance {  // up to 256 rows that share one expert block
     uint32_t kind, slot, first, count;
 };
 
-// grid (row tiles, max chunk instances); block 288.
+// grid (row tiles, max chunk instances); block 352.
 template <int BITS, int GROUP, int META, int PHASE>
 __global__ void __launch_bounds__(kUmmaThreads, 1)
 umma_expert_kernel(const ExpertArgs a, const ChunkInstance* __restrict__ inst, const uint32_t* __restrict__ n_inst,
                    float* __restrict__ partials, float* __restrict__ partial_shared,
-                   const __grid_constant__ CUtensorMap tm_routed, const __grid_constant__ CUtensorMap tm_shared) {
+                   const __grid_constant__ UmmaMaps maps) {
     constexpr uint32_t kRowBlockBytes = 64 * BITS / 8;  // packed bytes of one row per K block (32 or 64)
     constexpr uint32_t kWordsPerBlock = kRowBlockBytes / 4;
     constexpr uint32_t kGroupsPerBlock = 64 / GROUP;    // 1 (g64) or 2 (g32)
+    constexpr uint32_t kKbPerPk = 64 / kRowBlockBytes;  // K blocks per packed copy (2 or 1)
+    constexpr uint32_t kKbPerSc = 8 / kGroupsPerBlock;  // K blocks per scale copy (8 or 4)
     constexpr float kZero = BITS == 4 ? 8.0f : 128.0f;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
+#if SHRIKE_EXP == 9
+    const uint64_t t_entry = globaltimer_ns();
+#endif
     const uint32_t ii = blockIdx.y;
     if (ii >= *n_inst) return;
     const ChunkInstance in = inst[ii];
@@ -165,30 +219,34 @@ umma_expert_kernel(const ExpertArgs a, const ChunkInstance* __restrict__ inst, c
     if (r0 >= out_rows) return;
     const Offsets3& off = shared ? a.shared : a.routed;
     const uint8_t* base = shared ? a.shared_block : pool_cell_base(a.pool, in.slot);
-    const CUtensorMap* tmap = shared ? &tm_shared : &tm_routed;
-    const uint32_t G = kdim / GROUP;
     const uint32_t KB = kdim / 64;
-    const uint32_t row_bytes = kdim * BITS / 8;
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t N = (in.count + 15u) & ~15u;           // MMA N: rows padded to 16
     uint32_t ncols = 32;                                   // TMEM columns of one accumulator
     while (ncols < N) ncols <<= 1;
 
-    // shared memory (1024-byte aligned): stages x [A0 16 KB][A1 16 KB][B 32 KB] | barriers | row ids | tmem slot
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem = smem_raw + (smem_base - smem_u32(smem_raw));
-    uint64_t* full = (uint64_t*)(smem + kUmmaStages * kStageBytes);
-    uint64_t* empty = full + kUmmaStages;
-    uint64_t* accum = empty + kUmmaStages;
-    uint32_t* rowid = (uint32_t*)(accum + 1);   // output row of column n: pair id (routed) or row (shared)
+    uint64_t* bars = (uint64_t*)(smem + kOffBar);
+    uint64_t* a_full = bars;                       // converters -> MMA
+    uint64_t* a_empty = a_full + kAStages;         // MMA -> converters
+    uint64_t* b_full = a_empty + kAStages;         // activation copy -> MMA
+    uint64_t* b_empty = b_full + kBStages;         // MMA -> activation copy
+    uint64_t* pk_full = b_empty + kBStages;        // weight copy -> converters
+    uint64_t* pk_empty = pk_full + kPkSlots;       // converters -> weight copy
+    uint64_t* sc_full = pk_empty + kPkSlots;
+    uint64_t* sc_empty = sc_full + 1;
+    uint64_t* accum = sc_empty + 1;
+    uint32_t* rowid = (uint32_t*)(bars + kNumBars);   // output row of column n: pair id (routed) or row (shared)
     uint32_t* tmem_slot = rowid + kUmmaMaxN;
     __shared__ uint32_t s_failed;
 
     if (tid == 0) {
-        for (uint32_t s = 0; s < kUmmaStages; ++s) {
-            mbar_init(&full[s], kUmmaProducers + 1);   // every producer + the expect_tx arrival of the TMA copy
-            mbar_init(&empty[s], 1);
-        }
+        for (uint32_t s = 0; s < kAStages; ++s) { mbar_init(&a_full[s], kConverters); mbar_init(&a_empty[s], 1); }
+        for (uint32_t s = 0; s < kBStages; ++s) { mbar_init(&b_full[s], 1); mbar_init(&b_empty[s], 1); }
+        for (uint32_t s = 0; s < kPkSlots; ++s) { mbar_init(&pk_full[s], 1); mbar_init(&pk_empty[s], kConverters); }
+        mbar_init(sc_full, 1);
+        mbar_init(sc_empty, kConverters);
         mbar_init(accum, 1);
         fence_mbar_init();
         s_failed = 0;
@@ -204,63 +262,57 @@ umma_expert_kernel(const ExpertArgs a, const ChunkInstance* __restrict__ inst, c
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+#if SHRIKE_EXP == 9
+    uint64_t* const tr = a.trace ? a.trace + 8 * ((size_t)(PHASE * 4096 + blockIdx.y) * 8 + blockIdx.x) : nullptr;
+    if (tr && tid == 0) { tr[0] = t_entry; tr[1] = globaltimer_ns(); tr[7] = ((uint64_t)N << 32) | KB; }
+#endif
+    auto give_up = [&]() {
+        report_status(a.status, kStatusWaitTimeout);
+        s_failed = 1;
+    };
 
     if (warp < 8) {
-        // ---------------- producers ----------------
-        const uint32_t tile = tid >> 7, r = tid & 127;   // A tile and row inside it
-        uint32_t mrow;                                    // row of the weight matrix, which matrix
-        int mat;
-        if (PHASE == 0) { mat = (int)tile; mrow = r0 + r; } else { mat = 2; mrow = r0 + tid; }
-        const bool row_ok = mrow < out_rows;
-        const uint8_t* wrow = base + off.w[mat] + (size_t)(row_ok ? mrow : 0) * row_bytes;
-        const uint16_t* srow = (const uint16_t*)(base + off.s[mat]) + (size_t)(row_ok ? mrow : 0) * G;
-        const uint16_t* brow_meta = (const uint16_t*)(base + off.b[mat]) + (size_t)(row_ok ? mrow : 0) * G;
-
-        uint32_t pk[3][kWordsPerBlock];
-        uint16_t sraw[3][kGroupsPerBlock], braw[3][kGroupsPerBlock];
-        // three register buffers, indexed at compile time so that they stay in registers
-        auto fetch = [&](uint32_t kb, auto bufc) {
-            constexpr int buf = decltype(bufc)::value;
-            const uint4* p = (const uint4*)(wrow + (size_t)kb * kRowBlockBytes);
+        // ---------------- converters ----------------
+        const uint32_t tile = tid >> 7, r = tid & 127;   // weight tile and row inside it
+        const uint32_t pk_row = kOffPk + tile * (kPkSlotBytes / 2) + r * 64, pk_xor = (r >> 1) & 3;
+        uint32_t sreg[4] = {0, 0, 0, 0}, breg[4] = {0, 0, 0, 0};
+        for (uint32_t kb = 0; kb < KB; ++kb) {
+            if (*(volatile uint32_t*)&s_failed) break;
+            if (kb % kKbPerSc == 0) {
+                if (!mbar_wait_bounded(sc_full, (kb / kKbPerSc) & 1)) give_up();
+                const uint4 sv = *(const uint4*)(smem + kOffSc + tile * (kScHalfBytes / 2) + r * 16);
+                const uint4 bv = *(const uint4*)(smem + kOffSc + kScHalfBytes + tile * (kScHalfBytes / 2) + r * 16);
+                sreg[0] = sv.x; sreg[1] = sv.y; sreg[2] = sv.z; sreg[3] = sv.w;
+                breg[0] = bv.x; breg[1] = bv.y; breg[2] = bv.z; breg[3] = bv.w;
+            }
+            const uint32_t u = kb / kKbPerPk, slot = u % kPkSlots;
+            if (kb % kKbPerPk == 0 && !mbar_wait_bounded(&pk_full[slot], (u / kPkSlots) & 1)) give_up();
+            uint32_t pk[kWordsPerBlock];
 #pragma unroll
             for (uint32_t q = 0; q < kWordsPerBlock / 4; ++q) {
-                const uint4 v = ldg_stream_u128(p + q);
-                pk[buf][4 * q] = v.x; pk[buf][4 * q + 1] = v.y; pk[buf][4 * q + 2] = v.z; pk[buf][4 * q + 3] = v.w;
-            }
-#pragma unroll
-            for (uint32_t gq = 0; gq < kGroupsPerBlock; ++gq) {
-                sraw[buf][gq] = __ldg(srow + kb * kGroupsPerBlock + gq);
-                braw[buf][gq] = __ldg(brow_meta + kb * kGroupsPerBlock + gq);
-            }
-        };
-        auto step = [&](uint32_t kb, auto bufc) {
-            constexpr int buf = decltype(bufc)::value;     // also the pipeline stage: kb % 3
-            if (kb + 2 < KB) fetch(kb + 2, std::integral_constant<int, (buf + 2) % 3>{});
-            if (kb >= kUmmaStages && !mbar_wait_bounded(&empty[buf], ((kb / kUmmaStages) - 1) & 1)) {
-                report_status(a.status, kStatusWaitTimeout);
-                s_failed = 1;
-            }
-            uint8_t* a_tile = smem + buf * kStageBytes + tile * kTileBytes;
-            if (tid == 0) {
-                mbar_expect_tx(&full[buf], kBTileBytes);
-                tma_load_2d(smem_base + buf * kStageBytes + 2 * kTileBytes, tmap, (int32_t)(kb * 64), (int32_t)in.first,
-                            &full[buf]);
+                const uint32_t c = (kb % kKbPerPk) * (kRowBlockBytes / 16) + q;   // 16-byte chunk of the 64-byte row
+                const uint4 v = *(const uint4*)(smem + pk_row + slot * kPkSlotBytes + ((c ^ pk_xor) << 4));
+                pk[4 * q] = v.x; pk[4 * q + 1] = v.y; pk[4 * q + 2] = v.z; pk[4 * q + 3] = v.w;
             }
             uint32_t sz[kGroupsPerBlock][2];
 #pragma unroll
             for (uint32_t gq = 0; gq < kGroupsPerBlock; ++gq) {
-                const float s = meta_to_f32<META>(sraw[buf][gq]);
-                const float z = fmaf(kZero, s, meta_to_f32<META>(braw[buf][gq]));
-                sz[gq][0] = row_ok ? half2_dup(s) : 0u;
-                sz[gq][1] = row_ok ? half2_dup(z) : 0u;
+                const uint32_t gsel = (kb % kKbPerSc) * kGroupsPerBlock + gq;
+                const float sc = meta_to_f32<META>(pick16(sreg, gsel));
+                const float z = fmaf(kZero, sc, meta_to_f32<META>(pick16(breg, gsel)));
+                sz[gq][0] = half2_dup(sc);
+                sz[gq][1] = half2_dup(z);
             }
+            const uint32_t st = kb % kAStages;
+            if (kb >= kAStages && !mbar_wait_bounded(&a_empty[st], ((kb / kAStages) - 1) & 1)) give_up();
+            uint8_t* a_tile = smem + kOffA + st * kAStageBytes + tile * kTileBytes;
             // A row r: 8 chunks of 8 fp16; chunk c lives at chunk position c ^ (r & 7)
 #pragma unroll
             for (uint32_t w = 0; w < kWordsPerBlock; ++w) {
                 constexpr uint32_t kPerWord = BITS == 4 ? 8 : 4;           // weights per packed word
                 const uint32_t gq = (w * kPerWord) / GROUP;                // group of this word inside the K block
                 uint32_t o[4];
-                dequant_word<BITS>(pk[buf][w], sz[gq][0], sz[gq][1], o);
+                dequant_word<BITS>(pk[w], sz[gq][0], sz[gq][1], o);
                 if constexpr (BITS == 4) {
                     *(uint4*)(a_tile + r * 128 + ((w ^ (r & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
                 } else {
@@ -270,39 +322,75 @@ umma_expert_kernel(const ExpertArgs a, const ChunkInstance* __restrict__ inst, c
                 }
             }
             fence_async_smem();
-            mbar_arrive(&full[buf]);
-        };
-        fetch(0, std::integral_constant<int, 0>{});
-        if (KB > 1) fetch(1, std::integral_constant<int, 1>{});
-        for (uint32_t kb = 0; kb < KB; kb += 3) {
-            if (*(volatile uint32_t*)&s_failed) break;
-            step(kb, std::integral_constant<int, 0>{});
-            if (kb + 1 < KB) step(kb + 1, std::integral_constant<int, 1>{});
-            if (kb + 2 < KB) step(kb + 2, std::integral_constant<int, 2>{});
+            mbar_arrive(&a_full[st]);
+            // The ring slots are handed back only here: by now the values read from them have been
+            // consumed, so the reads are complete before the copy thread may overwrite the slot.
+            if ((kb + 1) % kKbPerPk == 0 || kb + 1 == KB) mbar_arrive(&pk_empty[slot]);
+            if (kb % kKbPerSc == 0) mbar_arrive(sc_empty);
+#if SHRIKE_EXP == 9
+            if (tr && tid == 0) { if (kb == 0) tr[2] = globaltimer_ns(); if (kb == KB / 2) tr[3] = globaltimer_ns(); if (kb == KB - 1) tr[4] = globaltimer_ns(); }
+#endif
         }
-    } else if (lane == 0) {
+    } else if (warp == 8 && lane == 0) {
         // ---------------- MMA issue ----------------
         const uint32_t idesc = umma_idesc(N);
         for (uint32_t kb = 0; kb < KB; ++kb) {
-            const uint32_t s = kb % kUmmaStages;
-            if (!mbar_wait_bounded(&full[s], (kb / kUmmaStages) & 1)) {
-                report_status(a.status, kStatusWaitTimeout);
-                s_failed = 1;
+            const uint32_t sa = kb % kAStages, sb = kb % kBStages;
+            if (!mbar_wait_bounded(&a_full[sa], (kb / kAStages) & 1) ||
+                !mbar_wait_bounded(&b_full[sb], (kb / kBStages) & 1)) {
+                give_up();
                 break;
             }
             tc_fence_after();
-            const uint32_t a_addr = smem_base + s * kStageBytes;
+            const uint32_t a_addr = smem_base + kOffA + sa * kAStageBytes;
             const uint64_t da0 = umma_smem_desc(a_addr), da1 = umma_smem_desc(a_addr + kTileBytes);
-            const uint64_t db = umma_smem_desc(a_addr + 2 * kTileBytes);
+            const uint64_t db = umma_smem_desc(smem_base + sb * kBTileBytes);
 #pragma unroll
             for (uint32_t k = 0; k < 4; ++k)  // 4 x K16 per 64-wide block: 32 bytes further along the row
                 umma_f16(tmem_base, da0 + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
 #pragma unroll
             for (uint32_t k = 0; k < 4; ++k)
                 umma_f16(tmem_base + ncols, da1 + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
-            umma_commit(&empty[s]);
+            umma_commit(&a_empty[sa]);
+            umma_commit(&b_empty[sb]);
         }
         umma_commit(accum);
+    } else if (warp == 9 && lane == 0) {
+        // ---------------- activation tiles ----------------
+        const CUtensorMap* tmap = shared ? &maps.act_shared : &maps.act_routed;
+        for (uint32_t kb = 0; kb < KB; ++kb) {
+            if (*(volatile uint32_t*)&s_failed) break;
+            const uint32_t sb = kb % kBStages;
+            if (kb >= kBStages && !mbar_wait_bounded(&b_empty[sb], ((kb / kBStages) - 1) & 1)) { give_up(); break; }
+            mbar_expect_tx(&b_full[sb], kBTileBytes);
+            tma_load_2d(smem_base + sb * kBTileBytes, tmap, (int32_t)(kb * 64), (int32_t)in.first, &b_full[sb]);
+        }
+    } else if (warp == 10 && lane == 0) {
+        // ---------------- packed weights, scales, biases ----------------
+        const WeightMaps* wm = shared ? &maps.shared : &maps.routed[in.slot / a.pool.cells_per_chunk];
+        const int32_t cell = shared ? 0 : (int32_t)(in.slot % a.pool.cells_per_chunk);
+        const int32_t y0 = (int32_t)r0, y1 = (int32_t)(PHASE == 0 ? r0 : r0 + 128);
+        for (uint32_t kb = 0; kb < KB; ++kb) {
+            if (*(volatile uint32_t*)&s_failed) break;
+            if (kb % kKbPerSc == 0) {
+                const uint32_t blk = kb / kKbPerSc;
+                if (blk > 0 && !mbar_wait_bounded(sc_empty, (blk - 1) & 1)) { give_up(); break; }
+                mbar_expect_tx(sc_full, 2 * kScHalfBytes);
+                const uint32_t dst = smem_base + kOffSc;
+                tma_load_3d(dst, &wm->s[0], (int32_t)(blk * 8), y0, cell, sc_full);
+                tma_load_3d(dst + kScHalfBytes / 2, &wm->s[1], (int32_t)(blk * 8), y1, cell, sc_full);
+                tma_load_3d(dst + kScHalfBytes, &wm->b[0], (int32_t)(blk * 8), y0, cell, sc_full);
+                tma_load_3d(dst + kScHalfBytes + kScHalfBytes / 2, &wm->b[1], (int32_t)(blk * 8), y1, cell, sc_full);
+            }
+            if (kb % kKbPerPk == 0) {
+                const uint32_t u = kb / kKbPerPk, slot = u % kPkSlots;
+                if (u >= kPkSlots && !mbar_wait_bounded(&pk_empty[slot], ((u / kPkSlots) - 1) & 1)) { give_up(); break; }
+                mbar_expect_tx(&pk_full[slot], kPkSlotBytes);
+                const uint32_t dst = smem_base + kOffPk + slot * kPkSlotBytes;
+                tma_load_3d(dst, &wm->w[0], (int32_t)(u * 64), y0, cell, &pk_full[slot]);
+                tma_load_3d(dst + kPkSlotBytes / 2, &wm->w[1], (int32_t)(u * 64), y1, cell, &pk_full[slot]);
+            }
+        }
     }
 
     // ---------------- epilogue (warp w: TMEM lanes 32*(w & 3) .. +31, every other 16-column group) ----------------
@@ -311,6 +399,9 @@ umma_expert_kernel(const ExpertArgs a, const ChunkInstance* __restrict__ inst, c
         if (!ok) report_status(a.status, kStatusWaitTimeout);
         if (*(volatile uint32_t*)&s_failed) ok = false;
         tc_fence_after();
+#if SHRIKE_EXP == 9
+        if (tr && tid == 0) tr[5] = globaltimer_ns();
+#endif
         const uint32_t q = warp & 3, h = warp >> 2;
         const uint32_t trow = q * 32 + lane;                       // row inside each 128-row tile
         const uint32_t taddr = tmem_base + ((q * 32) << 16);
@@ -330,7 +421,7 @@ umma_expert_kernel(const ExpertArgs a, const ChunkInstance* __restrict__ inst, c
                 tmem_ld_wait();
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
-                    const float v = glu(__uint_as_float(g[j]) + gab, __uint_as_float(u[j]) + uab, a.activation);
+                    const float v = glu_epilogue(__uint_as_float(g[j]) + gab, __uint_as_float(u[j]) + uab, a.activation);
                     if (ok && f_ok && c0 + j < in.count) dst[(size_t)(c0 + j) * F] = __half_as_ushort(__float2half_rn(v));
                 }
             }
@@ -359,7 +450,10 @@ umma_expert_kernel(const ExpertArgs a, const ChunkInstance* __restrict__ inst, c
             }
         }
     }
-    if (*(volatile uint32_t*)&s_failed && tid == 0) {
+#if SHRIKE_EXP == 9
+    if (tr && tid == 0) tr[6] = globaltimer_ns();
+#endif
+    if (*(volatile uint32_t*)&s_failed && lane == 0 && warp >= 9) {
         // a copy of this block may still be in flight: give it a bounded time to land
         for (int i = 0; i < 200; ++i) __nanosleep(1000);
     }
@@ -437,68 +531,102 @@ gather_sorted_rows_kernel(const uint16_t* __restrict__ xh, const uint32_t* __res
     for (uint32_t i = threadIdx.x; i < d / 8; i += blockDim.x) dst[i] = __ldg(src + i);
 }
 
-// ---- tensor maps of the activation operands ---------------------------------------
+// ---- tensor maps -------------------------------------------------------------------
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-static cudaError_t make_rows_map(EncodeTiledFn encode, CUtensorMap* map, const uint16_t* base, uint64_t cols,
-                                 uint64_t rows) {
-    const cuuint64_t dims[2] = {cols, rows};
-    const cuuint64_t strides[1] = {cols * 2};             // bytes between rows
-    const cuuint32_t box[2] = {64, kUmmaMaxN};            // 64 fp16 = one 128-byte swizzle row, 256 rows
-    const cuuint32_t elem[2] = {1, 1};
-    const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, (void*)base, dims, strides, box, elem,
-                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                              CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+static EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) != cudaSuccess ||
+            qres != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return (EncodeTiledFn)p;
+    }();
+    return fn;
 }
 
-// Called once per handle, after the workspace exists. Handles that only decode
-// (max_tokens <= 64) have no prefill buffers and no maps.
+// fp16 activation rows [rows][cols]: box = 64 columns (one 128-byte swizzle row) x 256 rows.
+static bool make_rows_map(CUtensorMap* map, const uint16_t* base, uint64_t cols, uint64_t rows) {
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {cols * 2};
+    const cuuint32_t box[2] = {64, kUmmaMaxN};
+    const cuuint32_t elem[2] = {1, 1};
+    return encode_tiled_fn()(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, (void*)base, dims, strides, box, elem,
+                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                             CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// One matrix of every cell of a pool chunk: [cells][rows][row_bytes] bytes (packed weights, 64-byte
+// boxes of 128 rows, 64-byte swizzle) or [cells][rows][groups] 16-bit (scales / biases, 8 per row).
+static bool make_matrix_map(CUtensorMap* map, const uint8_t* base, bool meta, uint64_t row_elems, uint64_t rows,
+                            uint64_t cells, uint64_t cell_stride) {
+    const uint64_t esz = meta ? 2 : 1;
+    const cuuint64_t dims[3] = {row_elems, rows, cells};
+    // a single cell (the shared expert's block) still needs a valid outer pitch
+    const cuuint64_t strides[2] = {row_elems * esz, cells > 1 ? cell_stride : row_elems * esz * rows};
+    const cuuint32_t box[3] = {meta ? 8u : 64u, 128, 1};
+    const cuuint32_t elem[3] = {1, 1, 1};
+    return encode_tiled_fn()(map, meta ? CU_TENSOR_MAP_DATA_TYPE_UINT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, (void*)base,
+                             dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                             meta ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_64B,
+                             CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// The two tiles of one phase: gate + up (phase 0) or down twice (phase 1).
+static bool make_weight_maps(WeightMaps* wm, const uint8_t* base, const Offsets3& off, int phase, uint32_t kdim,
+                             uint32_t rows, uint32_t bits, uint32_t group, uint64_t cells, uint64_t cell_stride) {
+    for (int t = 0; t < 2; ++t) {
+        const int mat = phase == 0 ? t : 2;
+        if (!make_matrix_map(&wm->w[t], base + off.w[mat], false, (uint64_t)kdim * bits / 8, rows, cells, cell_stride) ||
+            !make_matrix_map(&wm->s[t], base + off.s[mat], true, kdim / group, rows, cells, cell_stride) ||
+            !make_matrix_map(&wm->b[t], base + off.b[mat], true, kdim / group, rows, cells, cell_stride))
+            return false;
+    }
+    return true;
+}
+
+// The TMA path needs 16-byte row pitches everywhere: whole groups of 8 scales per row.
+bool umma_supported(const shrike_moe_config& c) {
+    const uint32_t g = c.group_size;
+    if (c.d % 64 || c.f % 64 || (c.d / g) % 8 || (c.f / g) % 8) return false;
+    if (c.has_shared && (c.shared_f % 64 || (c.shared_f / g) % 8)) return false;
+    return encode_tiled_fn() != nullptr;
+}
+
+// Called once per handle, after the workspace exists: the activation operands' maps.
 cudaError_t umma_prepare(shrike_moe* m) {
     const shrike_moe_config& c = m->cfg;
     Workspace& ws = m->ws;
-    if (!ws.xs) return cudaSuccess;
-    void* fn = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
-    if (e != cudaSuccess) return e;
-    if (!fn || qres != cudaDriverEntryPointSuccess) return cudaErrorNotSupported;
-    EncodeTiledFn encode = (EncodeTiledFn)fn;
-    CUtensorMap* maps = (CUtensorMap*)ws.tensor_maps;
+    if (!ws.xs || !umma_supported(c)) return cudaSuccess;
+    CUtensorMap* am = (CUtensorMap*)ws.tensor_maps;
     const uint64_t pairs = (uint64_t)c.max_tokens * c.top_k;
-    if ((e = make_rows_map(encode, &maps[0], ws.xs, c.d, pairs)) != cudaSuccess) return e;
-    if ((e = make_rows_map(encode, &maps[1], ws.acts, c.f, pairs)) != cudaSuccess) return e;
-    if (c.has_shared) {
-        if ((e = make_rows_map(encode, &maps[2], ws.xh, c.d, c.max_tokens)) != cudaSuccess) return e;
-        if ((e = make_rows_map(encode, &maps[3], ws.acts_shared, c.shared_f, c.max_tokens)) != cudaSuccess) return e;
-    } else {
-        maps[2] = maps[0];
-        maps[3] = maps[1];
-    }
-    return cudaSuccess;
+    bool ok = make_rows_map(&am[0], ws.xs, c.d, pairs) && make_rows_map(&am[1], ws.acts, c.f, pairs);
+    if (c.has_shared)
+        ok = ok && make_rows_map(&am[2], ws.xh, c.d, c.max_tokens) &&
+             make_rows_map(&am[3], ws.acts_shared, c.shared_f, c.max_tokens);
+    return ok ? cudaSuccess : cudaErrorInvalidValue;
 }
 
 template <int BITS, int GROUP, int META>
 static cudaError_t launch_umma_t(cudaStream_t st, const ExpertArgs& a, const ChunkInstance* inst,
                                  const uint32_t* n_inst, uint32_t max_inst, float* partials, float* partial_shared,
-                                 const CUtensorMap* maps) {
-    const uint32_t smem = kUmmaStages * kStageBytes + 1024 /*alignment slack*/ + (2 * kUmmaStages + 1) * 8 +
-                          kUmmaMaxN * 4 + 16;
+                                 const UmmaMaps& m0, const UmmaMaps& m1) {
     auto k0 = umma_expert_kernel<BITS, GROUP, META, 0>;
     auto k1 = umma_expert_kernel<BITS, GROUP, META, 1>;
-    cudaError_t e = cudaFuncSetAttribute(k0, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(k0, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kUmmaSmemBytes);
     if (e != cudaSuccess) return e;
-    e = cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    e = cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kUmmaSmemBytes);
     if (e != cudaSuccess) return e;
     const uint32_t fmax = a.f_shared > a.f ? a.f_shared : a.f;
-    k0<<<dim3((fmax + 127) / 128, max_inst), kUmmaThreads, smem, st>>>(a, inst, n_inst, partials, partial_shared,
-                                                                     maps[0], maps[2]);
+    k0<<<dim3((fmax + 127) / 128, max_inst), kUmmaThreads, kUmmaSmemBytes, st>>>(a, inst, n_inst, partials,
+                                                                               partial_shared, m0);
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;
-    k1<<<dim3((a.d + 255) / 256, max_inst), kUmmaThreads, smem, st>>>(a, inst, n_inst, partials, partial_shared,
-                                                                    maps[1], maps[3]);
+    k1<<<dim3((a.d + 255) / 256, max_inst), kUmmaThreads, kUmmaSmemBytes, st>>>(a, inst, n_inst, partials,
+                                                                              partial_shared, m1);
     return cudaGetLastError();
 }
 
@@ -518,6 +646,34 @@ cudaError_t launch_umma_prefill(const shrike_moe* m, cudaStream_t st, const Expe
                                 uint32_t pool_cells, float* partials, float* partial_shared) {
     const shrike_moe_config& c = m->cfg;
     const Workspace& ws = m->ws;
+    const CUtensorMap* am = (const CUtensorMap*)ws.tensor_maps;
+    if (!am || !umma_supported(c)) return cudaErrorNotSupported;
+    // descriptors of this call's pool and shared block (host work only)
+    UmmaMaps maps[2];
+    for (int phase = 0; phase < 2; ++phase) {
+        UmmaMaps& mp = maps[phase];
+        memset(&mp, 0, sizeof mp);
+        const uint32_t kdim = phase == 0 ? c.d : c.f, rows = phase == 0 ? c.f : c.d;
+        uint32_t left = a.pool.cells;
+        for (uint32_t ch = 0; ch < SHRIKE_MAX_POOL_CHUNKS && a.pool.base[ch] && left; ++ch) {
+            const uint32_t cells = left < a.pool.cells_per_chunk ? left : a.pool.cells_per_chunk;
+            if (!make_weight_maps(&mp.routed[ch], a.pool.base[ch], a.routed, phase, kdim, rows, c.weight_bits,
+                                  c.group_size, cells, a.pool.stride))
+                return cudaErrorInvalidValue;
+            left -= cells;
+        }
+        mp.act_routed = am[phase];
+        if (c.has_shared) {
+            const uint32_t kds = phase == 0 ? c.d : c.shared_f, rws = phase == 0 ? c.shared_f : c.d;
+            if (!make_weight_maps(&mp.shared, a.shared_block, a.shared, phase, kds, rws, c.weight_bits, c.group_size, 1,
+                                  16))
+                return cudaErrorInvalidValue;
+            mp.act_shared = am[2 + phase];
+        } else {
+            mp.shared = mp.routed[0];
+            mp.act_shared = mp.act_routed;
+        }
+    }
     ChunkInstance* inst = (ChunkInstance*)ws.chunk_inst;
     const uint32_t max_inst = umma_max_chunk_instances(c, T);
     chunk_instances_kernel<<<1, 256, 0, st>>>(ws.expert_offsets, ws.expert_counts, ws.slot_of_expert, c.num_experts, T,
@@ -527,11 +683,10 @@ cudaError_t launch_umma_prefill(const shrike_moe* m, cudaStream_t st, const Expe
     gather_sorted_rows_kernel<<<T * c.top_k, 128, 0, st>>>(ws.xh, ws.sorted, ws.n_chunk_inst, c.top_k, c.d, ws.xs);
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;
-    const CUtensorMap* maps = (const CUtensorMap*)ws.tensor_maps;
-    if (!maps) return cudaErrorInvalidValue;
     const uint32_t bits = c.weight_bits, grp = c.group_size;
     const bool f16 = c.meta_dtype == SHRIKE_DTYPE_FP16;
-#define SHRIKE_UMMA(B, G, M) return launch_umma_t<B, G, M>(st, a, inst, ws.n_chunk_inst, max_inst, partials, partial_shared, maps)
+#define SHRIKE_UMMA(B, G, M) \
+    return launch_umma_t<B, G, M>(st, a, inst, ws.n_chunk_inst, max_inst, partials, partial_shared, maps[0], maps[1])
     if (bits == 4 && grp == 64 && !f16) SHRIKE_UMMA(4, 64, SHRIKE_DTYPE_BF16);
     if (bits == 4 && grp == 64 && f16) SHRIKE_UMMA(4, 64, SHRIKE_DTYPE_FP16);
     if (bits == 4 && grp == 32 && !f16) SHRIKE_UMMA(4, 32, SHRIKE_DTYPE_BF16);

@@ -335,21 +335,38 @@ def test_prefill_equals_decode_on_the_same_rows(cuda_device):
     layer.close()
 
 
-def test_prefill_tensor_core_path_equals_the_warp_mma_path(cuda_device, monkeypatch):
-    """The tcgen05 grouped GEMM against the same rows on the 8-row warp-MMA tiles."""
-    for kw in (dict(), dict(weight_bits=8), dict(group_size=32, expert_bias=True, activation=capi.ACT_CLAMPED_SWIGLU,
-                                                 has_shared=False, shared_gated=False),
-               dict(d=320, f=192, shared_f=64)):
-        layer = Layer(small_config(max_tokens=512, **kw))
-        x = inputs(150, layer.cfg.d, seed=31)
-        monkeypatch.setenv("SHRIKE_PREFILL_PATH", "mma")
-        a = layer.forward(x, prefill=True)[0]
-        monkeypatch.setenv("SHRIKE_PREFILL_PATH", "umma")
-        b = layer.forward(x, prefill=True)[0]
-        monkeypatch.delenv("SHRIKE_PREFILL_PATH")
-        assert rel_l2(b, a) <= TOL, kw
-        assert rel_l2(b, layer.oracle_forward(x)) <= TOL, kw
-        layer.close()
+TENSOR_CORE_SHAPES = [
+    dict(d=512, f=512, shared_f=512),
+    dict(d=512, f=512, shared_f=512, weight_bits=8),
+    dict(d=512, f=1024, shared_f=512, meta_dtype=capi.DTYPE_FP16, act_dtype=capi.DTYPE_BF16),
+    dict(d=256, f=256, group_size=32, expert_bias=True, activation=capi.ACT_CLAMPED_SWIGLU, has_shared=False,
+         shared_gated=False),
+    dict(d=256, f=512, shared_f=256, group_size=32, weight_bits=8, activation=capi.ACT_GELU_TANH),
+]
+
+
+@pytest.mark.parametrize("kw", TENSOR_CORE_SHAPES, ids=lambda kw: "-".join(f"{k}{v}" for k, v in kw.items()))
+def test_prefill_tensor_core_path_equals_the_warp_mma_path(cuda_device, monkeypatch, kw):
+    """The tcgen05 grouped GEMM (shapes whose scale rows are whole 16-byte units) against the same rows
+    on the 8-row warp-MMA tiles, and both against the oracle."""
+    layer = Layer(small_config(max_tokens=512, **kw), chunks=2)
+    x = inputs(150, layer.cfg.d, seed=31)
+    tol = 4e-3 if layer.cfg.act_dtype == capi.DTYPE_BF16 else TOL
+    monkeypatch.setenv("SHRIKE_PREFILL_PATH", "mma")
+    a = layer.forward(x, prefill=True)[0]
+    monkeypatch.delenv("SHRIKE_PREFILL_PATH")
+    b = layer.forward(x, prefill=True)[0]
+    assert rel_l2(b, a) <= tol
+    assert rel_l2(b, layer.oracle_forward(x)) <= tol
+    layer.close()
+
+
+def test_prefill_tensor_core_experts_with_more_than_one_block_of_rows(cuda_device):
+    """Four experts, 600 rows, top-2: every expert gets about 300 rows, more than one 256-row block."""
+    cfg = small_config(d=512, f=512, shared_f=512, num_experts=4, top_k=2, max_tokens=640)
+    layer = Layer(cfg, router_sigma=0.05)
+    check_layer(layer, inputs(600, 512, seed=37), prefill=True)
+    layer.close()
 
 
 def test_prefill_skewed_routing_and_misses(cuda_device):
