@@ -10,21 +10,21 @@
 // reads each activation byte once per 256 weight rows and dequantises each
 // weight once per 256 activation rows.
 //
-//   warp 10    one thread streams the packed weights (64 bytes of every row
+//   warp 18    one thread streams the packed weights (64 bytes of every row
 //              per copy: a 3-D TMA box of 128 rows of one matrix of one pool
 //              cell, 64-byte swizzle) and the group scales / biases (16 bytes
 //              of every row per copy) into shared-memory rings. Whole-line TMA
 //              requests keep the packed experts streaming at HBM speed where
 //              per-thread 32-byte loads ran out of outstanding requests.
-//   warp 9     one thread copies the activation tiles: a 64 x 256 box of the
+//   warp 17    one thread copies the activation tiles: a 64 x 256 box of the
 //              expert-sorted fp16 rows per K block, 128-byte swizzle.
-//   warps 0-7  converters: each thread owns one weight row; per 64-wide K block
-//              it turns the packed nibbles/bytes into fp16 (q - Z) * scale +
+//   warps 0-15 converters: two threads per weight row; per 64-wide K block
+//              they turn the packed nibbles/bytes into fp16 (q - Z) * scale +
 //              (bias + Z*scale) -- the reference's half(fma(q, scale, bias)),
 //              tensorops.metal:106 -- and writes them, 16 bytes at a time, into
 //              the K-major 128-byte-swizzled tile the MMA reads. After the K
 //              loop the same warps run the epilogue.
-//   warp 8     one thread issues tcgen05.mma (M 128, N = rows, K 16, fp16 in,
+//   warp 16    one thread issues tcgen05.mma (M 128, N = rows, K 16, fp16 in,
 //              fp32 accumulate in TMEM) for both tiles and commits to the
 //              mbarriers that free the converted tile and the activation tile.
 //
@@ -36,16 +36,16 @@
 // Every wait is bounded; a wait that gives up sets the status word and the
 // block falls through to the TMEM release.
 #include <cuda.h>
-#ifndef SHRIKE_EXP
-#define SHRIKE_EXP 0
-#endif
+// -DSHRIKE_UMMA_TRACE: every block records entry / set-up / accumulators-ready / exit timestamps
+// in the handle's trace buffer (shrike_debug_set_trace); off in the shipped library.
 
 #include "internal.h"
 
 namespace shrike {
 
 constexpr uint32_t kUmmaMaxN = 256;
-constexpr uint32_t kConverters = 256;
+constexpr uint32_t kConverters = 512;                  // two threads per weight row
+constexpr uint32_t kConvWarps = kConverters / 32;
 constexpr uint32_t kUmmaThreads = kConverters + 96;    // + MMA warp, activation-copy warp, weight-copy warp
 constexpr uint32_t kAStages = 2, kBStages = 3, kPkSlots = 3;
 constexpr uint32_t kTileBytes = 128 * 128;             // 128 rows x 64 fp16, one swizzle-128B K block
@@ -68,7 +68,7 @@ struct WeightMaps {       // TMA descriptors of the two 128-row tiles of a block
 struct UmmaMaps {
     WeightMaps routed[SHRIKE_MAX_POOL_CHUNKS];
     WeightMaps shared;
-    CUtensorMap act_routed, act_shared;
+    CUtensorMap act_routed[4], act_shared[4];   // boxes of 32, 64, 128 and 256 activation rows
 };
 
 // ---- tcgen05 wrappers -------------------------------------------------------
@@ -181,6 +181,23 @@ __device__ __forceinline__ float glu_epilogue(float gate, float up, uint32_t act
     return __fdividef(gate, 1.0f + __expf(-gate)) * up;
 }
 
+// Bounded wait for the pipeline barriers: these are on the critical path of every K block, so the
+// first polls do not sleep.
+__device__ __forceinline__ bool pipe_wait(uint64_t* bar, uint32_t parity) {
+    const uint32_t addr = smem_u32(bar);
+    for (uint32_t it = 0; it < (1u << 21); ++it) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
+        if (ok) return true;
+        if (it > 256) __nanosleep(32);
+    }
+    return false;
+}
+
 // 16-bit field `idx` (0..7) of four registers.
 __device__ __forceinline__ uint16_t pick16(const uint32_t (&v)[4], uint32_t idx) {
     const uint32_t lo = (idx & 2u) ? v[1] : v[0], hi = (idx & 2u) ? v[3] : v[2];
@@ -192,7 +209,7 @@ struct ChunkInstance {  // up to 256 rows that share one expert block
     uint32_t kind, slot, first, count;
 };
 
-// grid (row tiles, max chunk instances); block 352.
+// grid (row tiles, max chunk instances); block 608.
 template <int BITS, int GROUP, int META, int PHASE>
 __global__ void __launch_bounds__(kUmmaThreads, 1)
 umma_expert_kernel(const ExpertArgs a, const ChunkInstance* __restrict__ inst, const uint32_t* __restrict__ n_inst,
@@ -205,7 +222,7 @@ umma_expert_kernel(const ExpertArgs a, const ChunkInstance* __restrict__ inst, c
     constexpr uint32_t kKbPerSc = 8 / kGroupsPerBlock;  // K blocks per scale copy (8 or 4)
     constexpr float kZero = BITS == 4 ? 8.0f : 128.0f;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
-#if SHRIKE_EXP == 9
+#ifdef SHRIKE_UMMA_TRACE
     const uint64_t t_entry = globaltimer_ns();
 #endif
     const uint32_t ii = blockIdx.y;
@@ -242,11 +259,11 @@ umma_expert_kernel(const ExpertArgs a, const ChunkInstance* __restrict__ inst, c
     __shared__ uint32_t s_failed;
 
     if (tid == 0) {
-        for (uint32_t s = 0; s < kAStages; ++s) { mbar_init(&a_full[s], kConverters); mbar_init(&a_empty[s], 1); }
+        for (uint32_t s = 0; s < kAStages; ++s) { mbar_init(&a_full[s], kConvWarps); mbar_init(&a_empty[s], 1); }
         for (uint32_t s = 0; s < kBStages; ++s) { mbar_init(&b_full[s], 1); mbar_init(&b_empty[s], 1); }
-        for (uint32_t s = 0; s < kPkSlots; ++s) { mbar_init(&pk_full[s], 1); mbar_init(&pk_empty[s], kConverters); }
+        for (uint32_t s = 0; s < kPkSlots; ++s) { mbar_init(&pk_full[s], 1); mbar_init(&pk_empty[s], kConvWarps); }
         mbar_init(sc_full, 1);
-        mbar_init(sc_empty, kConverters);
+        mbar_init(sc_empty, kConvWarps);
         mbar_init(accum, 1);
         fence_mbar_init();
         s_failed = 0;
@@ -257,12 +274,12 @@ umma_expert_kernel(const ExpertArgs a, const ChunkInstance* __restrict__ inst, c
             rowid[n] = shared ? in.first + src : a.sorted[in.first + src];
         }
     }
-    if (warp == 8) tmem_alloc(smem_u32(tmem_slot), 2 * ncols);
+    if (warp == kConvWarps) tmem_alloc(smem_u32(tmem_slot), 2 * ncols);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-#if SHRIKE_EXP == 9
+#ifdef SHRIKE_UMMA_TRACE
     uint64_t* const tr = a.trace ? a.trace + 8 * ((size_t)(PHASE * 4096 + blockIdx.y) * 8 + blockIdx.x) : nullptr;
     if (tr && tid == 0) { tr[0] = t_entry; tr[1] = globaltimer_ns(); tr[7] = ((uint64_t)N << 32) | KB; }
 #endif
@@ -271,73 +288,72 @@ umma_expert_kernel(const ExpertArgs a, const ChunkInstance* __restrict__ inst, c
         s_failed = 1;
     };
 
-    if (warp < 8) {
+    if (warp < kConvWarps) {
         // ---------------- converters ----------------
-        const uint32_t tile = tid >> 7, r = tid & 127;   // weight tile and row inside it
+        // Two threads per weight row: thread `half` converts 32 of the K block's 64 weights.
+        const uint32_t tile = tid >> 8, r = (tid >> 1) & 127, half = tid & 1;
+        constexpr uint32_t kWordsPerThread = kWordsPerBlock / 2;   // 4 (int4) or 8 (int8)
         const uint32_t pk_row = kOffPk + tile * (kPkSlotBytes / 2) + r * 64, pk_xor = (r >> 1) & 3;
         uint32_t sreg[4] = {0, 0, 0, 0}, breg[4] = {0, 0, 0, 0};
         for (uint32_t kb = 0; kb < KB; ++kb) {
             if (*(volatile uint32_t*)&s_failed) break;
             if (kb % kKbPerSc == 0) {
-                if (!mbar_wait_bounded(sc_full, (kb / kKbPerSc) & 1)) give_up();
+                if (!pipe_wait(sc_full, (kb / kKbPerSc) & 1)) give_up();
                 const uint4 sv = *(const uint4*)(smem + kOffSc + tile * (kScHalfBytes / 2) + r * 16);
                 const uint4 bv = *(const uint4*)(smem + kOffSc + kScHalfBytes + tile * (kScHalfBytes / 2) + r * 16);
                 sreg[0] = sv.x; sreg[1] = sv.y; sreg[2] = sv.z; sreg[3] = sv.w;
                 breg[0] = bv.x; breg[1] = bv.y; breg[2] = bv.z; breg[3] = bv.w;
             }
             const uint32_t u = kb / kKbPerPk, slot = u % kPkSlots;
-            if (kb % kKbPerPk == 0 && !mbar_wait_bounded(&pk_full[slot], (u / kPkSlots) & 1)) give_up();
-            uint32_t pk[kWordsPerBlock];
+            if (kb % kKbPerPk == 0 && !pipe_wait(&pk_full[slot], (u / kPkSlots) & 1)) give_up();
+            uint32_t pk[kWordsPerThread];
 #pragma unroll
-            for (uint32_t q = 0; q < kWordsPerBlock / 4; ++q) {
-                const uint32_t c = (kb % kKbPerPk) * (kRowBlockBytes / 16) + q;   // 16-byte chunk of the 64-byte row
+            for (uint32_t q = 0; q < kWordsPerThread / 4; ++q) {
+                // 16-byte chunk of the 64-byte row: this K block's share, then this thread's half of it
+                const uint32_t c = (kb % kKbPerPk) * (kRowBlockBytes / 16) + half * (kWordsPerThread / 4) + q;
                 const uint4 v = *(const uint4*)(smem + pk_row + slot * kPkSlotBytes + ((c ^ pk_xor) << 4));
                 pk[4 * q] = v.x; pk[4 * q + 1] = v.y; pk[4 * q + 2] = v.z; pk[4 * q + 3] = v.w;
             }
-            uint32_t sz[kGroupsPerBlock][2];
-#pragma unroll
-            for (uint32_t gq = 0; gq < kGroupsPerBlock; ++gq) {
-                const uint32_t gsel = (kb % kKbPerSc) * kGroupsPerBlock + gq;
-                const float sc = meta_to_f32<META>(pick16(sreg, gsel));
-                const float z = fmaf(kZero, sc, meta_to_f32<META>(pick16(breg, gsel)));
-                sz[gq][0] = half2_dup(sc);
-                sz[gq][1] = half2_dup(z);
-            }
+            // a thread's half of a 64-wide block lies inside one group of 32 or 64
+            const uint32_t gsel = (kb % kKbPerSc) * kGroupsPerBlock + (GROUP == 64 ? 0u : half);
+            const float sc = meta_to_f32<META>(pick16(sreg, gsel));
+            const float zf = fmaf(kZero, sc, meta_to_f32<META>(pick16(breg, gsel)));
+            const uint32_t s2 = half2_dup(sc), z2 = half2_dup(zf);
             const uint32_t st = kb % kAStages;
-            if (kb >= kAStages && !mbar_wait_bounded(&a_empty[st], ((kb / kAStages) - 1) & 1)) give_up();
-            uint8_t* a_tile = smem + kOffA + st * kAStageBytes + tile * kTileBytes;
+            if (kb >= kAStages && !pipe_wait(&a_empty[st], ((kb / kAStages) - 1) & 1)) give_up();
+            uint8_t* a_row = smem + kOffA + st * kAStageBytes + tile * kTileBytes + r * 128;
             // A row r: 8 chunks of 8 fp16; chunk c lives at chunk position c ^ (r & 7)
 #pragma unroll
-            for (uint32_t w = 0; w < kWordsPerBlock; ++w) {
+            for (uint32_t i = 0; i < kWordsPerThread; ++i) {
                 constexpr uint32_t kPerWord = BITS == 4 ? 8 : 4;           // weights per packed word
-                const uint32_t gq = (w * kPerWord) / GROUP;                // group of this word inside the K block
+                const uint32_t w = half * kWordsPerThread + i;             // word of the K block
                 uint32_t o[4];
-                dequant_word<BITS>(pk[w], sz[gq][0], sz[gq][1], o);
+                dequant_word<BITS>(pk[i], s2, z2, o);
                 if constexpr (BITS == 4) {
-                    *(uint4*)(a_tile + r * 128 + ((w ^ (r & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+                    *(uint4*)(a_row + ((w ^ (r & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
                 } else {
                     // two words make one 16-byte chunk
-                    uint2* dst = (uint2*)(a_tile + r * 128 + (((w >> 1) ^ (r & 7)) << 4)) + (w & 1);
+                    uint2* dst = (uint2*)(a_row + (((w >> 1) ^ (r & 7)) << 4)) + (w & 1);
                     *dst = make_uint2(o[0], o[1]);
                 }
             }
             fence_async_smem();
-            mbar_arrive(&a_full[st]);
-            // The ring slots are handed back only here: by now the values read from them have been
-            // consumed, so the reads are complete before the copy thread may overwrite the slot.
-            if ((kb + 1) % kKbPerPk == 0 || kb + 1 == KB) mbar_arrive(&pk_empty[slot]);
-            if (kb % kKbPerSc == 0) mbar_arrive(sc_empty);
-#if SHRIKE_EXP == 9
-            if (tr && tid == 0) { if (kb == 0) tr[2] = globaltimer_ns(); if (kb == KB / 2) tr[3] = globaltimer_ns(); if (kb == KB - 1) tr[4] = globaltimer_ns(); }
-#endif
+            __syncwarp();
+            if (lane == 0) {
+                // one arrival per warp: 512 arrivals on one barrier word would serialise every K block
+                mbar_arrive(&a_full[st]);
+                // The ring slots are handed back only here: by now the values read from them have been
+                // consumed, so the reads are complete before the copy thread may overwrite the slot.
+                if ((kb + 1) % kKbPerPk == 0 || kb + 1 == KB) mbar_arrive(&pk_empty[slot]);
+                if (kb % kKbPerSc == 0) mbar_arrive(sc_empty);
+            }
         }
-    } else if (warp == 8 && lane == 0) {
+    } else if (warp == kConvWarps && lane == 0) {
         // ---------------- MMA issue ----------------
         const uint32_t idesc = umma_idesc(N);
         for (uint32_t kb = 0; kb < KB; ++kb) {
             const uint32_t sa = kb % kAStages, sb = kb % kBStages;
-            if (!mbar_wait_bounded(&a_full[sa], (kb / kAStages) & 1) ||
-                !mbar_wait_bounded(&b_full[sb], (kb / kBStages) & 1)) {
+            if (!pipe_wait(&a_full[sa], (kb / kAStages) & 1) || !pipe_wait(&b_full[sb], (kb / kBStages) & 1)) {
                 give_up();
                 break;
             }
@@ -355,17 +371,20 @@ umma_expert_kernel(const ExpertArgs a, const ChunkInstance* __restrict__ inst, c
             umma_commit(&b_empty[sb]);
         }
         umma_commit(accum);
-    } else if (warp == 9 && lane == 0) {
+    } else if (warp == kConvWarps + 1 && lane == 0) {
         // ---------------- activation tiles ----------------
-        const CUtensorMap* tmap = shared ? &maps.act_shared : &maps.act_routed;
+        // the smallest box that holds the instance's rows: a short instance does not pay for 256 rows
+        const uint32_t bi = N <= 32 ? 0u : N <= 64 ? 1u : N <= 128 ? 2u : 3u;
+        const CUtensorMap* tmap = shared ? &maps.act_shared[bi] : &maps.act_routed[bi];
+        const uint32_t b_bytes = (32u << bi) * 128u;
         for (uint32_t kb = 0; kb < KB; ++kb) {
             if (*(volatile uint32_t*)&s_failed) break;
             const uint32_t sb = kb % kBStages;
-            if (kb >= kBStages && !mbar_wait_bounded(&b_empty[sb], ((kb / kBStages) - 1) & 1)) { give_up(); break; }
-            mbar_expect_tx(&b_full[sb], kBTileBytes);
+            if (kb >= kBStages && !pipe_wait(&b_empty[sb], ((kb / kBStages) - 1) & 1)) { give_up(); break; }
+            mbar_expect_tx(&b_full[sb], b_bytes);
             tma_load_2d(smem_base + sb * kBTileBytes, tmap, (int32_t)(kb * 64), (int32_t)in.first, &b_full[sb]);
         }
-    } else if (warp == 10 && lane == 0) {
+    } else if (warp == kConvWarps + 2 && lane == 0) {
         // ---------------- packed weights, scales, biases ----------------
         const WeightMaps* wm = shared ? &maps.shared : &maps.routed[in.slot / a.pool.cells_per_chunk];
         const int32_t cell = shared ? 0 : (int32_t)(in.slot % a.pool.cells_per_chunk);
@@ -374,7 +393,7 @@ umma_expert_kernel(const ExpertArgs a, const ChunkInstance* __restrict__ inst, c
             if (*(volatile uint32_t*)&s_failed) break;
             if (kb % kKbPerSc == 0) {
                 const uint32_t blk = kb / kKbPerSc;
-                if (blk > 0 && !mbar_wait_bounded(sc_empty, (blk - 1) & 1)) { give_up(); break; }
+                if (blk > 0 && !pipe_wait(sc_empty, (blk - 1) & 1)) { give_up(); break; }
                 mbar_expect_tx(sc_full, 2 * kScHalfBytes);
                 const uint32_t dst = smem_base + kOffSc;
                 tma_load_3d(dst, &wm->s[0], (int32_t)(blk * 8), y0, cell, sc_full);
@@ -384,7 +403,7 @@ umma_expert_kernel(const ExpertArgs a, const ChunkInstance* __restrict__ inst, c
             }
             if (kb % kKbPerPk == 0) {
                 const uint32_t u = kb / kKbPerPk, slot = u % kPkSlots;
-                if (u >= kPkSlots && !mbar_wait_bounded(&pk_empty[slot], ((u / kPkSlots) - 1) & 1)) { give_up(); break; }
+                if (u >= kPkSlots && !pipe_wait(&pk_empty[slot], ((u / kPkSlots) - 1) & 1)) { give_up(); break; }
                 mbar_expect_tx(&pk_full[slot], kPkSlotBytes);
                 const uint32_t dst = smem_base + kOffPk + slot * kPkSlotBytes;
                 tma_load_3d(dst, &wm->w[0], (int32_t)(u * 64), y0, cell, &pk_full[slot]);
@@ -393,36 +412,40 @@ umma_expert_kernel(const ExpertArgs a, const ChunkInstance* __restrict__ inst, c
         }
     }
 
-    // ---------------- epilogue (warp w: TMEM lanes 32*(w & 3) .. +31, every other 16-column group) ----------------
-    if (warp < 8) {
-        bool ok = mbar_wait_bounded(accum, 0);
+    // ---------------- epilogue (warp w: TMEM lanes 32*(w & 3) .. +31, every fourth 16-column group) ----------------
+    if (warp < kConvWarps) {
+        bool ok = pipe_wait(accum, 0);
         if (!ok) report_status(a.status, kStatusWaitTimeout);
         if (*(volatile uint32_t*)&s_failed) ok = false;
         tc_fence_after();
-#if SHRIKE_EXP == 9
+#ifdef SHRIKE_UMMA_TRACE
         if (tr && tid == 0) tr[5] = globaltimer_ns();
 #endif
         const uint32_t q = warp & 3, h = warp >> 2;
         const uint32_t trow = q * 32 + lane;                       // row inside each 128-row tile
         const uint32_t taddr = tmem_base + ((q * 32) << 16);
+        constexpr uint32_t kColStep = 16 * (kConvWarps / 4);
         if (PHASE == 0) {
             const uint32_t f = r0 + trow;
-            const bool f_ok = f < F;
+            const bool f_ok = f < F && ok;
             float gab = 0.f, uab = 0.f;
-            if (a.expert_bias && f_ok) {
+            if (a.expert_bias && f < F) {
                 gab = bf16_bits_to_f32(((const uint16_t*)(base + off.ab[0]))[f]);
                 uab = bf16_bits_to_f32(((const uint16_t*)(base + off.ab[1]))[f]);
             }
             uint16_t* dst = (shared ? a.acts_shared : a.acts) + (size_t)in.first * F + perm_index(f, BITS == 4);
-            for (uint32_t c0 = h * 16; c0 < N; c0 += 32) {
+            for (uint32_t c0 = h * 16; c0 < N; c0 += kColStep) {
                 uint32_t g[16], u[16];
                 tmem_ld16_issue(taddr + c0, g);
                 tmem_ld16_issue(taddr + ncols + c0, u);
                 tmem_ld_wait();
+                uint16_t* p = dst + (size_t)c0 * F;
+                const uint32_t live = f_ok ? min(16u, in.count > c0 ? in.count - c0 : 0u) : 0u;   // rows of this group
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
                     const float v = glu_epilogue(__uint_as_float(g[j]) + gab, __uint_as_float(u[j]) + uab, a.activation);
-                    if (ok && f_ok && c0 + j < in.count) dst[(size_t)(c0 + j) * F] = __half_as_ushort(__float2half_rn(v));
+                    if ((uint32_t)j < live) *p = __half_as_ushort(__float2half_rn(v));
+                    p += F;
                 }
             }
         } else {
@@ -434,32 +457,34 @@ umma_expert_kernel(const ExpertArgs a, const ChunkInstance* __restrict__ inst, c
                 if (d1 < a.d) ab1 = bf16_bits_to_f32(dab[d1]);
             }
             float* out = shared ? partial_shared : partials;
-            for (uint32_t c0 = h * 16; c0 < N; c0 += 32) {
+            const bool ok0 = ok && d0 < a.d, ok1 = ok && d1 < a.d;
+            for (uint32_t c0 = h * 16; c0 < N; c0 += kColStep) {
                 uint32_t v0[16], v1[16];
                 tmem_ld16_issue(taddr + c0, v0);
                 tmem_ld16_issue(taddr + ncols + c0, v1);
                 tmem_ld_wait();
+                const uint32_t live = min(16u, in.count > c0 ? in.count - c0 : 0u);
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
-                    if (ok && c0 + j < in.count) {
-                        float* o = out + (size_t)rowid[c0 + j] * a.d;
-                        if (d0 < a.d) o[d0] = __uint_as_float(v0[j]) + ab0;
-                        if (d1 < a.d) o[d1] = __uint_as_float(v1[j]) + ab1;
+                    if ((uint32_t)j < live) {
+                        float* o = out + (size_t)rowid[c0 + j] * a.d + d0;
+                        if (ok0) o[0] = __uint_as_float(v0[j]) + ab0;
+                        if (ok1) o[128] = __uint_as_float(v1[j]) + ab1;
                     }
                 }
             }
         }
     }
-#if SHRIKE_EXP == 9
+#ifdef SHRIKE_UMMA_TRACE
     if (tr && tid == 0) tr[6] = globaltimer_ns();
 #endif
-    if (*(volatile uint32_t*)&s_failed && lane == 0 && warp >= 9) {
+    if (*(volatile uint32_t*)&s_failed && lane == 0 && warp > kConvWarps) {
         // a copy of this block may still be in flight: give it a bounded time to land
         for (int i = 0; i < 200; ++i) __nanosleep(1000);
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 8) {
+    if (warp == kConvWarps) {
         __syncwarp();
         tmem_dealloc(tmem_base, 2 * ncols);
     }
@@ -548,11 +573,11 @@ static EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
-// fp16 activation rows [rows][cols]: box = 64 columns (one 128-byte swizzle row) x 256 rows.
-static bool make_rows_map(CUtensorMap* map, const uint16_t* base, uint64_t cols, uint64_t rows) {
+// fp16 activation rows [rows][cols]: box = 64 columns (one 128-byte swizzle row) x box_rows rows.
+static bool make_rows_map(CUtensorMap* map, const uint16_t* base, uint64_t cols, uint64_t rows, uint32_t box_rows) {
     const cuuint64_t dims[2] = {cols, rows};
     const cuuint64_t strides[1] = {cols * 2};
-    const cuuint32_t box[2] = {64, kUmmaMaxN};
+    const cuuint32_t box[2] = {64, box_rows};
     const cuuint32_t elem[2] = {1, 1};
     return encode_tiled_fn()(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, (void*)base, dims, strides, box, elem,
                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -601,12 +626,18 @@ cudaError_t umma_prepare(shrike_moe* m) {
     const shrike_moe_config& c = m->cfg;
     Workspace& ws = m->ws;
     if (!ws.xs || !umma_supported(c)) return cudaSuccess;
+    // maps[operand][box]: operands xs, acts, xh, acts_shared; boxes of 32, 64, 128, 256 rows
     CUtensorMap* am = (CUtensorMap*)ws.tensor_maps;
     const uint64_t pairs = (uint64_t)c.max_tokens * c.top_k;
-    bool ok = make_rows_map(&am[0], ws.xs, c.d, pairs) && make_rows_map(&am[1], ws.acts, c.f, pairs);
-    if (c.has_shared)
-        ok = ok && make_rows_map(&am[2], ws.xh, c.d, c.max_tokens) &&
-             make_rows_map(&am[3], ws.acts_shared, c.shared_f, c.max_tokens);
+    bool ok = true;
+    for (uint32_t bi = 0; bi < 4 && ok; ++bi) {
+        const uint32_t box_rows = 32u << bi;
+        ok = make_rows_map(&am[0 * 4 + bi], ws.xs, c.d, pairs, box_rows) &&
+             make_rows_map(&am[1 * 4 + bi], ws.acts, c.f, pairs, box_rows);
+        if (ok && c.has_shared)
+            ok = make_rows_map(&am[2 * 4 + bi], ws.xh, c.d, c.max_tokens, box_rows) &&
+                 make_rows_map(&am[3 * 4 + bi], ws.acts_shared, c.shared_f, c.max_tokens, box_rows);
+    }
     return ok ? cudaSuccess : cudaErrorInvalidValue;
 }
 
@@ -638,7 +669,7 @@ uint32_t umma_max_chunk_instances(const shrike_moe_config& c, uint32_t T) {
 }
 
 size_t umma_chunk_instance_bytes() { return sizeof(ChunkInstance); }
-size_t umma_tensor_map_bytes() { return 4 * sizeof(CUtensorMap); }
+size_t umma_tensor_map_bytes() { return 16 * sizeof(CUtensorMap); }
 
 // Gate/up + GLU, then down, for the instances built from the grouping the
 // prefill plan left in the workspace.
@@ -662,16 +693,16 @@ cudaError_t launch_umma_prefill(const shrike_moe* m, cudaStream_t st, const Expe
                 return cudaErrorInvalidValue;
             left -= cells;
         }
-        mp.act_routed = am[phase];
+        for (int bi = 0; bi < 4; ++bi) mp.act_routed[bi] = am[phase * 4 + bi];
         if (c.has_shared) {
             const uint32_t kds = phase == 0 ? c.d : c.shared_f, rws = phase == 0 ? c.shared_f : c.d;
             if (!make_weight_maps(&mp.shared, a.shared_block, a.shared, phase, kds, rws, c.weight_bits, c.group_size, 1,
                                   16))
                 return cudaErrorInvalidValue;
-            mp.act_shared = am[2 + phase];
+            for (int bi = 0; bi < 4; ++bi) mp.act_shared[bi] = am[(2 + phase) * 4 + bi];
         } else {
             mp.shared = mp.routed[0];
-            mp.act_shared = mp.act_routed;
+            for (int bi = 0; bi < 4; ++bi) mp.act_shared[bi] = mp.act_routed[bi];
         }
     }
     ChunkInstance* inst = (ChunkInstance*)ws.chunk_inst;
