@@ -294,6 +294,106 @@ __device__ __forceinline__ void select_row(const float* lg, const RouterArgs& a,
     out_w = w;
 }
 
+// Order-preserving key of expert e's selection score (0 = not a candidate); the same
+// arithmetic as select_row.
+template <bool CG>
+__device__ __forceinline__ uint32_t selection_key(const float* lg, const RouterArgs& a, uint32_t e) {
+    if (e >= a.ne) return 0u;
+    const float raw = CG ? __ldcg(lg + e) : lg[e];
+    const float bias = a.logit_bias ? bf16_bits_to_f32(a.logit_bias[e]) : 0.0f;
+    const float s = __fadd_rn(__fadd_rn(a.sigmoid_scores ? sigmoid_det(raw) : raw, bias), 0.0f);  // -0 -> +0
+    const uint32_t b = __float_as_uint(s);
+    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+
+// Route weights of the picks (lane r holds the r-th pick): moe.metal:458-490, sums in rank order.
+template <bool CG>
+__device__ __forceinline__ float selection_weight(const float* lg, const RouterArgs& a, uint32_t lane, float my_score,
+                                                  uint32_t my_id) {
+    const uint32_t top_k = a.top_k;
+    float val;
+    if (a.sigmoid_scores) {
+        val = lane < top_k ? sigmoid_det(CG ? __ldcg(lg + my_id) : lg[my_id]) : 0.f;
+    } else {
+        const float mx = __shfl_sync(0xffffffffu, my_score, 0);
+        val = lane < top_k ? exp_det(__fsub_rn(my_score, mx)) : 0.f;
+    }
+    float sum = 0.f;
+    for (uint32_t r = 0; r < top_k; ++r) sum = __fadd_rn(sum, __shfl_sync(0xffffffffu, val, r));
+    float w;
+    if (a.sigmoid_scores) w = __fmul_rn(val, __fdiv_rn(a.scaling, __fadd_rn(sum, 1e-20f)));
+    else w = __fdiv_rn(val, sum);
+    const float pes = a.per_expert_scale ? bf16_bits_to_f32(a.per_expert_scale[my_id]) : 1.0f;
+    w = __fmul_rn(w, pes);
+    if (a.round_f16) w = __half2float(__float2half_rn(w));
+    return w;
+}
+
+struct alignas(16) SelectSmem {
+    uint32_t keys[SHRIKE_MAX_EXPERTS];   // read back 16 bytes at a time
+    uint32_t cand_key[32], cand_id[32];
+    uint32_t sel_key[SHRIKE_MAX_TOP_K], sel_id[SHRIKE_MAX_TOP_K];
+};
+
+// The same picks as select_row, by the whole block (4 warps) for one row, without the K serial
+// rounds: every expert counts the experts that beat it ((score desc, id asc) is a total order, so
+// the count is its rank). Warp w ranks its 64 experts among themselves and keeps the best 8;
+// warp 0 ranks the 32 survivors. Lane r of warp 0 returns the r-th pick; call from all threads.
+__device__ __forceinline__ void select_row_block(const float* lg, const RouterArgs& a, SelectSmem& ss, uint32_t& out_id,
+                                                 float& out_w) {
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    ss.keys[tid] = selection_key<true>(lg, a, tid);
+    ss.keys[tid + 128] = selection_key<true>(lg, a, tid + 128);
+    if (tid < 32) { ss.cand_key[tid] = 0u; ss.cand_id[tid] = 0u; }
+    if (tid < SHRIKE_MAX_TOP_K) { ss.sel_key[tid] = 0u; ss.sel_id[tid] = 0u; }
+    __syncthreads();
+    {
+        const uint32_t base = warp * 64;
+        const uint32_t k0 = ss.keys[base + lane], k1 = ss.keys[base + 32 + lane];
+        uint32_t r0a = 0, r0b = 0, r1a = 0, r1b = 0;
+        const uint4* kv = (const uint4*)(ss.keys + base);
+#pragma unroll
+        for (uint32_t j4 = 0; j4 < 16; ++j4) {
+            const uint4 v = kv[j4];
+            const uint32_t kj[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (uint32_t q = 0; q < 4; ++q) {
+                const uint32_t j = 4 * j4 + q;
+                const uint32_t b0 = (kj[q] > k0 || (kj[q] == k0 && j < lane)) ? 1u : 0u;
+                const uint32_t b1 = (kj[q] > k1 || (kj[q] == k1 && j < lane + 32u)) ? 1u : 0u;
+                if (q & 1) { r0b += b0; r1b += b1; } else { r0a += b0; r1a += b1; }
+            }
+        }
+        const uint32_t r0 = r0a + r0b, r1 = r1a + r1b;
+        if (k0 != 0u && r0 < 8u) { ss.cand_key[warp * 8 + r0] = k0; ss.cand_id[warp * 8 + r0] = base + lane; }
+        if (k1 != 0u && r1 < 8u) { ss.cand_key[warp * 8 + r1] = k1; ss.cand_id[warp * 8 + r1] = base + 32 + lane; }
+    }
+    __syncthreads();
+    out_id = 0;
+    out_w = 0.f;
+    if (warp == 0) {
+        const uint32_t ck = ss.cand_key[lane], ci = ss.cand_id[lane];
+        uint32_t rank = 0;
+#pragma unroll
+        for (uint32_t j = 0; j < 32; ++j) {
+            const uint32_t okey = __shfl_sync(0xffffffffu, ck, j), oid = __shfl_sync(0xffffffffu, ci, j);
+            rank += (okey > ck || (okey == ck && oid < ci)) ? 1u : 0u;
+        }
+        if (ck != 0u && rank < a.top_k) { ss.sel_key[rank] = ck; ss.sel_id[rank] = ci; }
+        __syncwarp();
+        float my_score = 0.f;
+        uint32_t my_id = 0;
+        if (lane < a.top_k) {
+            const uint32_t k = ss.sel_key[lane];
+            my_score = __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k);
+            my_id = ss.sel_id[lane];
+        }
+        out_w = selection_weight<true>(lg, a, lane, my_score, my_id);
+        out_id = my_id;
+    }
+    __syncthreads();   // the scratch is reused by the next row
+}
+
 // grid (ceil((ne + has_gate)/4), token blocks)
 __global__ void __launch_bounds__(kRouterWarps * 32) router_logits_kernel(const RouterArgs a) {
     logits_body(a, [] {});
@@ -487,6 +587,7 @@ __global__ void __launch_bounds__(128) router_select_kernel(const RouterArgs a) 
 __global__ void __launch_bounds__(kRouterWarps * 32) route_fused_kernel(const RouterArgs a) {
     __shared__ PlanSmem sm;
     __shared__ uint32_t ids_sm[kPlanMaxPairs];
+    __shared__ SelectSmem sel;
     __shared__ uint32_t s_last, s_miss;
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     uint64_t ts[8] = {0, 0, 0, 0, 0, 0, 0, 0};
@@ -525,11 +626,11 @@ __global__ void __launch_bounds__(kRouterWarps * 32) route_fused_kernel(const Ro
     }
     __threadfence();
 
-    for (uint32_t row = warp; row < a.T; row += kRouterWarps) {
+    for (uint32_t row = 0; row < a.T; ++row) {
         uint32_t id;
         float w;
-        select_row<true>(a.logits + (size_t)row * a.ne, a, lane, id, w);
-        if (lane < a.top_k) {
+        select_row_block(a.logits + (size_t)row * a.ne, a, sel, id, w);
+        if (warp == 0 && lane < a.top_k) {
             a.ids[(size_t)row * a.top_k + lane] = id;
             a.weights[(size_t)row * a.top_k + lane] = w;
             ids_sm[row * a.top_k + lane] = id;
