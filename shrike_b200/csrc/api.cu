@@ -559,9 +559,9 @@ int shrike_encode_moe_prefill(shrike_moe* m, void* stream, const shrike_pool* po
     if (rc) return rc;
     cudaStream_t st = (cudaStream_t)stream;
     const uint32_t mi = max_instances(m->cfg, query_count);
-    // The default runs the expert-grouped GEMM on the tcgen05 tensor cores. Shapes whose scale rows are
-    // not whole 16-byte units (the TMA copies need that), and SHRIKE_PREFILL_PATH=mma, keep every expert
-    // on the 8-row warp-MMA tiles (the decode kernels).
+    // The default runs the expert-grouped GEMM on the tcgen05 tensor cores. Shapes whose K is not a
+    // multiple of 64, and SHRIKE_PREFILL_PATH=mma, keep every expert on the 8-row warp-MMA tiles (the
+    // decode kernels).
     const char* path = getenv("SHRIKE_PREFILL_PATH");
     const bool warp_mma = (path && strcmp(path, "mma") == 0) || !umma_supported(m->cfg);
     CU(launch_prefill_plan(m, st, topk_indices, resolved_slots, x, query_count, m->cfg.has_shared != 0,

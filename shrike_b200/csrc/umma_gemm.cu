@@ -237,6 +237,9 @@ umma_expert_kernel(const ExpertArgs a, const ChunkInstance* __restrict__ inst, c
     const Offsets3& off = shared ? a.shared : a.routed;
     const uint8_t* base = shared ? a.shared_block : pool_cell_base(a.pool, in.slot);
     const uint32_t KB = kdim / 64;
+    const uint32_t G = kdim / GROUP;
+    // scale rows that are whole 16-byte units come by TMA; others (G % 8 != 0) are read by the converters
+    const bool sc_tma = (G & 7u) == 0;
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t N = (in.count + 15u) & ~15u;           // MMA N: rows padded to 16
     uint32_t ncols = 32;                                   // TMEM columns of one accumulator
@@ -295,14 +298,46 @@ umma_expert_kernel(const ExpertArgs a, const ChunkInstance* __restrict__ inst, c
         constexpr uint32_t kWordsPerThread = kWordsPerBlock / 2;   // 4 (int4) or 8 (int8)
         const uint32_t pk_row = kOffPk + tile * (kPkSlotBytes / 2) + r * 64, pk_xor = (r >> 1) & 3;
         uint32_t sreg[4] = {0, 0, 0, 0}, breg[4] = {0, 0, 0, 0};
+        uint32_t snext[4] = {0, 0, 0, 0}, bnext[4] = {0, 0, 0, 0};
+        const uint32_t mrow = r0 + (PHASE == 0 ? r : tile * 128 + r);
+        const int mat = PHASE == 0 ? (int)tile : 2;
+        const uint16_t* srow = (const uint16_t*)(base + off.s[mat]) + (size_t)mrow * G;
+        const uint16_t* brow = (const uint16_t*)(base + off.b[mat]) + (size_t)mrow * G;
+        // groups 8*blk .. 8*blk+7 of this thread's row, straight from global memory (rows past the matrix
+        // and groups past the row read as zero: the converted weights are then zero)
+        auto fetch_scales = [&](uint32_t blk) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const uint32_t gi = blk * 8 + 2 * i;
+                uint32_t sv = 0, bv = 0;
+                if (mrow < out_rows && gi < G) {
+                    sv = __ldg(srow + gi);
+                    bv = __ldg(brow + gi);
+                    if (gi + 1 < G) {
+                        sv |= (uint32_t)__ldg(srow + gi + 1) << 16;
+                        bv |= (uint32_t)__ldg(brow + gi + 1) << 16;
+                    }
+                }
+                snext[i] = sv;
+                bnext[i] = bv;
+            }
+        };
+        if (!sc_tma) fetch_scales(0);
         for (uint32_t kb = 0; kb < KB; ++kb) {
             if (*(volatile uint32_t*)&s_failed) break;
             if (kb % kKbPerSc == 0) {
-                if (!pipe_wait(sc_full, (kb / kKbPerSc) & 1)) give_up();
-                const uint4 sv = *(const uint4*)(smem + kOffSc + tile * (kScHalfBytes / 2) + r * 16);
-                const uint4 bv = *(const uint4*)(smem + kOffSc + kScHalfBytes + tile * (kScHalfBytes / 2) + r * 16);
-                sreg[0] = sv.x; sreg[1] = sv.y; sreg[2] = sv.z; sreg[3] = sv.w;
-                breg[0] = bv.x; breg[1] = bv.y; breg[2] = bv.z; breg[3] = bv.w;
+                if (sc_tma) {
+                    if (!pipe_wait(sc_full, (kb / kKbPerSc) & 1)) give_up();
+                    const uint4 sv = *(const uint4*)(smem + kOffSc + tile * (kScHalfBytes / 2) + r * 16);
+                    const uint4 bv = *(const uint4*)(smem + kOffSc + kScHalfBytes + tile * (kScHalfBytes / 2) + r * 16);
+                    sreg[0] = sv.x; sreg[1] = sv.y; sreg[2] = sv.z; sreg[3] = sv.w;
+                    breg[0] = bv.x; breg[1] = bv.y; breg[2] = bv.z; breg[3] = bv.w;
+                } else {
+                    // this block's 8 groups were fetched one block ago; fetch the next block's now
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) { sreg[i] = snext[i]; breg[i] = bnext[i]; }
+                    fetch_scales(kb / kKbPerSc + 1);
+                }
             }
             const uint32_t u = kb / kKbPerPk, slot = u % kPkSlots;
             if (kb % kKbPerPk == 0 && !pipe_wait(&pk_full[slot], (u / kPkSlots) & 1)) give_up();
@@ -345,7 +380,7 @@ umma_expert_kernel(const ExpertArgs a, const ChunkInstance* __restrict__ inst, c
                 // The ring slots are handed back only here: by now the values read from them have been
                 // consumed, so the reads are complete before the copy thread may overwrite the slot.
                 if ((kb + 1) % kKbPerPk == 0 || kb + 1 == KB) mbar_arrive(&pk_empty[slot]);
-                if (kb % kKbPerSc == 0) mbar_arrive(sc_empty);
+                if (sc_tma && kb % kKbPerSc == 0) mbar_arrive(sc_empty);
             }
         }
     } else if (warp == kConvWarps && lane == 0) {
@@ -391,7 +426,7 @@ umma_expert_kernel(const ExpertArgs a, const ChunkInstance* __restrict__ inst, c
         const int32_t y0 = (int32_t)r0, y1 = (int32_t)(PHASE == 0 ? r0 : r0 + 128);
         for (uint32_t kb = 0; kb < KB; ++kb) {
             if (*(volatile uint32_t*)&s_failed) break;
-            if (kb % kKbPerSc == 0) {
+            if (sc_tma && kb % kKbPerSc == 0) {
                 const uint32_t blk = kb / kKbPerSc;
                 if (blk > 0 && !pipe_wait(sc_empty, (blk - 1) & 1)) { give_up(); break; }
                 mbar_expect_tx(sc_full, 2 * kScHalfBytes);
@@ -605,19 +640,20 @@ static bool make_weight_maps(WeightMaps* wm, const uint8_t* base, const Offsets3
                              uint32_t rows, uint32_t bits, uint32_t group, uint64_t cells, uint64_t cell_stride) {
     for (int t = 0; t < 2; ++t) {
         const int mat = phase == 0 ? t : 2;
-        if (!make_matrix_map(&wm->w[t], base + off.w[mat], false, (uint64_t)kdim * bits / 8, rows, cells, cell_stride) ||
-            !make_matrix_map(&wm->s[t], base + off.s[mat], true, kdim / group, rows, cells, cell_stride) ||
+        if (!make_matrix_map(&wm->w[t], base + off.w[mat], false, (uint64_t)kdim * bits / 8, rows, cells, cell_stride))
+            return false;
+        if ((kdim / group) % 8 != 0) continue;   // such scale rows are read by the converter threads
+        if (!make_matrix_map(&wm->s[t], base + off.s[mat], true, kdim / group, rows, cells, cell_stride) ||
             !make_matrix_map(&wm->b[t], base + off.b[mat], true, kdim / group, rows, cells, cell_stride))
             return false;
     }
     return true;
 }
 
-// The TMA path needs 16-byte row pitches everywhere: whole groups of 8 scales per row.
+// K in whole 64-wide blocks (packed rows are then whole 16-byte units, which the TMA copies need).
 bool umma_supported(const shrike_moe_config& c) {
-    const uint32_t g = c.group_size;
-    if (c.d % 64 || c.f % 64 || (c.d / g) % 8 || (c.f / g) % 8) return false;
-    if (c.has_shared && (c.shared_f % 64 || (c.shared_f / g) % 8)) return false;
+    if (c.d % 64 || c.f % 64) return false;
+    if (c.has_shared && c.shared_f % 64) return false;
     return encode_tiled_fn() != nullptr;
 }
 
