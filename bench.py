@@ -40,7 +40,7 @@ def parse_args():
     ap.add_argument("--tokens", type=int, default=1, help="decode batch: 1, 4 or 16")
     ap.add_argument("--layers", type=int, default=LAYERS)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--workload", choices=["decode", "prefill"], default="decode",
+    ap.add_argument("--workload", choices=["decode", "prefill", "ep"], default="decode",
                     help="decode: the 40-layer sweep (headline); prefill: one layer, 4096 rows, Zipf(1.1)-skewed routing")
     ap.add_argument("--rows", type=int, default=4096, help="rows of the prefill workload")
     ap.add_argument("--no-sweep", action="store_true", help="skip the T=4 / T=16 lines of the sweep")
@@ -464,6 +464,89 @@ def run_prefill(args, local_rank: int):
     return line
 
 
+
+def run_ep(args, rank: int, world: int, local_rank: int):
+    """Expert-parallel Kimi-Linear-shape layer (int8 g64, 256 experts top-8 sigmoid, shared expert): every rank
+    holds 256/N experts and its own mixed batch of 16 decode rows + one 2048-row prefill chunk; rows are
+    dispatched and combined with all-to-all over NCCL. Weak scaling: N x 2064 rows per step."""
+    import torch
+    import torch.distributed as dist
+    from shrike_b200 import capi, fixtures as fx
+    from shrike_b200.ep import ExpertParallelLayer
+    from shrike_b200.moe import RouterOperands, expert_offsets
+
+    rows, K, W = 16 + 2048, args.steps, max(3, args.warmup)
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    cfg = fx.kimi_config(max_tokens=rows)
+    group = None
+    layer = ExpertParallelLayer(cfg, rank, world, local_rank, rows, group)
+    layer.pool.fill_synthetic(0, layer.epr, SEED, 0, first_expert=layer.lo)
+    soff, sbytes = expert_offsets(cfg, shared=True)
+    sh = torch.from_numpy(fx.synth_block(cfg, SEED, 0, 100000, shared=True).copy()).to(dev)
+    layer.set_shared(capi.SharedExpert(sh.data_ptr(), soff))
+    ops = RouterOperands(weights=torch.from_numpy(router_weights(0, cfg.num_experts, cfg.d)).to(dev))
+    # every rank routes its own rows
+    xr = np.random.default_rng(SEED + 1000 + rank).normal(0, 1, (rows, cfg.d)).astype(np.float32)
+    x_host = torch.from_numpy(xr).to(torch.bfloat16).pin_memory()
+    y_host = torch.empty_like(x_host).pin_memory()
+    x = x_host.to(dev)
+    y = torch.empty_like(x)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, n):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    def step():
+        layer.forward(ops, x, y)
+
+    def step_e2e():
+        x.copy_(x_host, non_blocking=True)
+        layer.forward(ops, x, y)
+        y_host.copy_(y, non_blocking=True)
+
+    for _ in range(W):
+        step()
+    layer.home.status()
+    layer.routed.status()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    ms = timed(step, K)
+    clocks = sampler.stop()
+    ms_e2e = timed(step_e2e, K)
+    sent = int(layer.send_counts.sum().item())
+    line = {
+        "metric": METRIC, "value": world * rows * K / (ms / 1e3), "unit": "tokens/s", "n_gpus": world, "steps": K,
+        "warmup": W, "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "int8 weights dequantised to fp16 operands, fp32 accumulate (TMEM)", "data": "synthetic",
+        "config": {"workload": "kimi-linear-48b-shape layer, expert parallel: 256 experts top-8 sigmoid + shared "
+                               "expert, D 2304, F 1024, int8 g64; 16 decode rows + one 2048-row prefill chunk per "
+                               "rank; all-to-all dispatch and combine over NCCL",
+                   "rows_per_rank": rows, "experts_per_rank": layer.epr, "parallelism": f"ep{world}",
+                   "rows_sent_by_rank0": sent,
+                   "l2": f"inputs larger than L2: {layer.epr * layer.block_bytes / 1e6:.0f} MB of expert blocks per rank"},
+        "e2e": {"value": world * rows * K / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e / K,
+                "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": y_host.numel() * 2},
+        "gpu_launches": None, "clocks": clocks,
+    }
+    layer.close()
+    return line
+
+
 def main():
     args = parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -493,6 +576,17 @@ def main():
     if args.workload == "prefill":
         if rank == 0:
             print(json.dumps(run_prefill(args, local_rank)))
+        return
+    if args.workload == "ep":
+        import torch.distributed as dist
+        if world > 1:
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        line = run_ep(args, rank, world, local_rank)
+        if rank == 0:
+            print(json.dumps(line))
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
         return
     if world > 1:
         import torch.distributed as dist
