@@ -485,7 +485,11 @@ def run_ep(args, rank: int, world: int, local_rank: int):
     soff, sbytes = expert_offsets(cfg, shared=True)
     sh = torch.from_numpy(fx.synth_block(cfg, SEED, 0, 100000, shared=True).copy()).to(dev)
     layer.set_shared(capi.SharedExpert(sh.data_ptr(), soff))
-    ops = RouterOperands(weights=torch.from_numpy(router_weights(0, cfg.num_experts, cfg.d)).to(dev))
+    sys.path.insert(0, str(ROOT / "tests"))
+    from gpu_harness import bf16_tensor
+    correction = np.random.default_rng(SEED + 7).uniform(-0.1, 0.1, cfg.num_experts).astype(np.float32)
+    ops = RouterOperands(weights=torch.from_numpy(router_weights(0, cfg.num_experts, cfg.d)).to(dev),
+                         logit_bias=bf16_tensor(correction, dev))
     # every rank routes its own rows
     xr = np.random.default_rng(SEED + 1000 + rank).normal(0, 1, (rows, cfg.d)).astype(np.float32)
     x_host = torch.from_numpy(xr).to(torch.bfloat16).pin_memory()

@@ -529,12 +529,39 @@ int shrike_encode_decode_layer(shrike_moe* m, void* stream, const shrike_pool* p
     uint32_t* ids = out_indices ? out_indices : w.ids_dev;
     float* wt = out_weights ? out_weights : w.w_dev;
     float* gate = m->cfg.shared_gated ? w.gate_dev : nullptr;
-    int rc = shrike_encode_route_decode(m, stream, router, residency_table_row, pool, x, query_count, m->cfg.d,
+    // One row: the route launch stops after the logits and the fp16 operand copy, and every block of
+    // phase 1 and phase 2 repeats the selection itself -- no block waits for another to publish picks,
+    // cells and work lists. More rows keep the route kernel's tail (selection, lookup, grouping).
+    const bool self_route = query_count == 1;
+    int rc;
+    if (self_route) {
+        if (!router || !router->weights || !residency_table_row || !pool)
+            return fail(m, SHRIKE_EINVAL, "decode_layer: null operand");
+        const shrike_moe_config& c = m->cfg;
+        if (c.router_weight_bits != 0 && (!router->scales || !router->biases))
+            return fail(m, SHRIKE_EINVAL, "router: affine weights need scales and biases");
+        if (c.shared_gated && !router->shared_gate)
+            return fail(m, SHRIKE_EINVAL, "router: a shared_gated handle needs shared_gate");
+        CU(launch_route_fused(m, (cudaStream_t)stream, *router, x, 1, c.d, residency_table_row, pool->view.cells,
+                              io_status, ids, wt, gate, w.slots_dev, nullptr, true, true));
+    } else {
+        rc = shrike_encode_route_decode(m, stream, router, residency_table_row, pool, x, query_count, m->cfg.d,
                                         io_status, ids, wt, gate, w.slots_dev, nullptr);
-    if (rc) return rc;
+        if (rc) return rc;
+    }
     ExpertArgs a;
     rc = fill_expert_args(m, pool, routed_offsets, shared, wt, gate, a);
     if (rc) return rc;
+    if (self_route) {
+        const shrike_moe_config& c = m->cfg;
+        SelfRoute& r = a.sr;
+        r.logits = w.logits; r.logit_bias = router->logit_bias; r.per_expert_scale = router->per_expert_scale;
+        r.table = residency_table_row; r.io_status = io_status;
+        r.out_ids = ids; r.out_w = wt; r.out_slots = w.slots_dev; r.out_counts = nullptr;
+        r.ne = c.num_experts; r.top_k = c.top_k; r.sigmoid_scores = c.router_kind == SHRIKE_ROUTER_SIGMOID;
+        r.round_f16 = c.round_route_weights_f16; r.pool_cells = pool->view.cells; r.scaling = c.routed_scaling;
+        r.enabled = 1; r.publish = 0;
+    }
     const uint32_t mi = max_instances(m->cfg, query_count);
     // phase 1 and phase 2 may start before their predecessor has drained
     CU(launch_phase1(m, (cudaStream_t)stream, a, mi, true));

@@ -21,6 +21,7 @@
 // the tile's scales and zero-point biases are staged in shared memory by the
 // TMA engine (1-D bulk copies completing on an mbarrier).
 #include "internal.h"
+#include "select.cuh"
 
 namespace shrike {
 
@@ -227,13 +228,40 @@ __global__ void __launch_bounds__(kP1Warps * 32) phase1_kernel(const ExpertArgs 
     extern __shared__ __align__(16) uint8_t smem[];
     const uint32_t ii = blockIdx.y;
     const uint64_t t_start = a.trace ? globaltimer_ns() : 0;
-    // the work lists come from the kernel launched just before this one
+    // Self-routing: the residency row does not depend on the launch before this one (the host publishes
+    // it ahead of the layer), so it is staged while that launch is still running.
+    __shared__ SelfRouteSmem srs;
+    __shared__ uint64_t table_sm[SHRIKE_MAX_EXPERTS];
+    if (a.sr.enabled)
+        for (uint32_t e = threadIdx.x; e < a.sr.ne; e += blockDim.x) table_sm[e] = a.sr.table[e];
+    // the work lists (or, self-routing, the logits) come from the kernel launched just before this one
     pdl_wait();
-    const uint32_t n_inst = *a.n_inst;
-    const Instance in = load_instance(a.inst + ii);
-    if (ii >= n_inst) return;
+    Instance in;
+    if (a.sr.enabled) {
+        // one decode row: instance ii is the ii-th pick, the one after the picks the shared expert
+        SelfRoute r = a.sr;
+        r.publish = blockIdx.x == 0 && blockIdx.y == 0;
+        self_route_block(r, srs, a.status, table_sm);
+        pdl_launch_dependents();
+        in.first = 0; in.count = 1;
+        uint32_t pair = 0;
+        if (ii < srs.n_routed) {
+            pair = srs.order[ii];
+            in.kind = 0; in.slot = srs.slot[pair];
+        } else if (ii == srs.n_routed && a.shared_block) {
+            in.kind = 1; in.slot = 0;
+        } else {
+            return;
+        }
+#pragma unroll
+        for (int q = 0; q < 8; ++q) in.pair[q] = pair;
+    } else {
+        const uint32_t n_inst = *a.n_inst;
+        in = load_instance(a.inst + ii);
+        if (ii >= n_inst) return;
+        pdl_launch_dependents();
+    }
     const uint64_t t_inst = a.trace ? globaltimer_ns() : 0;
-    pdl_launch_dependents();
     const bool shared = in.kind == 1;
     const uint32_t F = shared ? a.f_shared : a.f;
     const uint32_t f0 = blockIdx.x * 16;
@@ -335,7 +363,7 @@ __global__ void __launch_bounds__(kP1Warps * 32) phase1_kernel(const ExpertArgs 
         }
     }
     if (a.trace && tid == 0) {
-        uint64_t* tr = a.trace + 8 * (size_t)(blockIdx.y * gridDim.x + blockIdx.x);
+        uint64_t* tr = a.trace + 8 * (size_t)(128 + blockIdx.y * gridDim.x + blockIdx.x);   // after the route kernel's blocks
         tr[0] = t_start; tr[1] = t_loads; tr[2] = t_acc; tr[3] = globaltimer_ns();
         tr[4] = t_inst; tr[5] = t_sync; tr[6] = t_red; tr[7] = 0;
     }
@@ -371,6 +399,8 @@ __global__ void __launch_bounds__(kP2Warps * 32) phase2_kernel(const ExpertArgs 
     float* yacc_all = (float*)(smem + nw * per_warp);
     float* yacc = yacc_all + (size_t)warp * T * 16;
 
+    const uint64_t t2_start = a.trace ? globaltimer_ns() : 0;
+    uint64_t t2_wait = 0;
     for (uint32_t i = lane; i < T * 16; i += 32) yacc[i] = 0.f;
     if (lane == 0) {
         mbar_init(bar, 1);
@@ -378,13 +408,31 @@ __global__ void __launch_bounds__(kP2Warps * 32) phase2_kernel(const ExpertArgs 
     }
     __syncwarp();
 
-    const uint32_t n_inst = *a.n_inst;
+    // Self-routing (one decode row): the logits were complete before phase 1 began, so this block
+    // repeats the selection now and fetches its weights while phase 1 runs.
+    __shared__ SelfRouteSmem srs;
+    if (a.sr.enabled) {
+        SelfRoute r = a.sr;
+        r.publish = 0;
+        self_route_block(r, srs, a.status);
+    }
+    const uint32_t n_inst = a.sr.enabled ? srs.n_routed + (a.shared_block ? 1u : 0u) : *a.n_inst;
     const uint32_t units = n_inst * ksplit;
     uint32_t parity = 0;
     bool first = true;
     for (uint32_t u = warp; u < units; u += nw) {
         const uint32_t ii = u / ksplit, ks = u % ksplit;
-        const Instance in = load_instance(a.inst + ii);
+        Instance in;
+        if (a.sr.enabled) {
+            in.first = 0; in.count = 1;
+            in.kind = ii < srs.n_routed ? 0u : 1u;
+            const uint32_t pair = in.kind == 0 ? srs.order[ii] : 0u;
+            in.slot = in.kind == 0 ? srs.slot[pair] : 0u;
+#pragma unroll
+            for (int q = 0; q < 8; ++q) in.pair[q] = pair;
+        } else {
+            in = load_instance(a.inst + ii);
+        }
         const bool shared = in.kind == 1;
         const uint32_t F = shared ? a.f_shared : a.f;
         const uint32_t G = F / GROUP;
@@ -415,6 +463,7 @@ __global__ void __launch_bounds__(kP2Warps * 32) phase2_kernel(const ExpertArgs 
             pdl_wait();  // the activations of phase 1
             pdl_launch_dependents();
             first = false;
+            if (a.trace) t2_wait = globaltimer_ns();
         }
 
         const uint32_t bpair = pick(in.pair, g < in.count ? g : 0);
@@ -440,7 +489,7 @@ __global__ void __launch_bounds__(kP2Warps * 32) phase2_kernel(const ExpertArgs 
                     w = a.shared_gate ? a.shared_gate[token] : 1.0f;
                 } else {
                     token = pair / a.top_k;
-                    w = a.route_w[pair];
+                    w = a.sr.enabled ? srs.w[pair] : a.route_w[pair];
                 }
                 yacc[token * 16 + g] += w * (tot[0][c] + ab0);
                 yacc[token * 16 + g + 8] += w * (tot[0][2 + c] + ab1);
@@ -464,6 +513,10 @@ __global__ void __launch_bounds__(kP2Warps * 32) phase2_kernel(const ExpertArgs 
             const float h = load_act(hidden, o, a.act_dtype) + round_act(a.act_dtype, acc);
             store_act(hidden, o, a.act_dtype, h);
         }
+    }
+    if (a.trace && tid == 0) {
+        uint64_t* tr = a.trace + 8 * (size_t)(1024 + blockIdx.x);   // after the blocks of phase 1
+        tr[0] = t2_start; tr[1] = t2_wait; tr[2] = globaltimer_ns();
     }
 }
 

@@ -40,6 +40,23 @@ inline Offsets3 to_offsets3(const shrike_expert_offsets& o) {
     return r;
 }
 
+// Routing of one decode row by the expert kernels themselves (see select.cuh).
+struct SelfRoute {
+    const float* logits;          // [num_experts], written by the launch before phase 1
+    const uint16_t* logit_bias;
+    const uint16_t* per_expert_scale;
+    const uint64_t* table;        // residency row
+    const uint32_t* io_status;
+    uint32_t* out_ids;
+    float* out_w;
+    uint32_t* out_slots;
+    uint32_t* out_counts;
+    uint32_t ne, top_k, sigmoid_scores, round_f16, pool_cells;
+    float scaling;
+    uint32_t enabled;             // 0: the work lists of a route kernel are used instead
+    uint32_t publish;             // this block also writes ids / weights / slots / counts
+};
+
 // Everything the expert kernels need that does not change between launches of
 // one call.
 struct ExpertArgs {
@@ -61,6 +78,7 @@ struct ExpertArgs {
     const float* shared_gate;     // [tokens] or NULL
     uint32_t* status;
     uint64_t* trace;              // diagnostics: per-block timestamps of phase 1, or NULL
+    SelfRoute sr;
 };
 
 struct Workspace {
@@ -121,7 +139,8 @@ cudaError_t launch_router(const shrike_moe* m, cudaStream_t st, const shrike_rou
 cudaError_t launch_route_fused(const shrike_moe* m, cudaStream_t st, const shrike_router_operands& ops,
                                const void* hidden, uint32_t T, uint32_t stride, const uint64_t* table,
                                uint32_t pool_cells, const uint32_t* io_status, uint32_t* ids, float* weights,
-                               float* shared_gate, uint32_t* slots, uint32_t* counts, bool pdl);
+                               float* shared_gate, uint32_t* slots, uint32_t* counts, bool pdl,
+                               bool no_tail = false);
 cudaError_t launch_classify(const shrike_moe* m, cudaStream_t st, const uint32_t* ids,
                             const uint64_t* table, uint32_t T, uint32_t* slots, uint32_t* counts,
                             uint32_t* miss_pos, uint32_t* miss_exp);
