@@ -543,7 +543,7 @@ int shrike_encode_decode_layer(shrike_moe* m, void* stream, const shrike_pool* p
         if (c.shared_gated && !router->shared_gate)
             return fail(m, SHRIKE_EINVAL, "router: a shared_gated handle needs shared_gate");
         CU(launch_route_fused(m, (cudaStream_t)stream, *router, x, 1, c.d, residency_table_row, pool->view.cells,
-                              io_status, ids, wt, gate, w.slots_dev, nullptr, true, true));
+                              io_status, ids, wt, gate, w.slots_dev, nullptr, getenv("SHRIKE_NO_PDL") == nullptr, true));
     } else {
         rc = shrike_encode_route_decode(m, stream, router, residency_table_row, pool, x, query_count, m->cfg.d,
                                         io_status, ids, wt, gate, w.slots_dev, nullptr);
@@ -560,12 +560,14 @@ int shrike_encode_decode_layer(shrike_moe* m, void* stream, const shrike_pool* p
         r.out_ids = ids; r.out_w = wt; r.out_slots = w.slots_dev; r.out_counts = nullptr;
         r.ne = c.num_experts; r.top_k = c.top_k; r.sigmoid_scores = c.router_kind == SHRIKE_ROUTER_SIGMOID;
         r.round_f16 = c.round_route_weights_f16; r.pool_cells = pool->view.cells; r.scaling = c.routed_scaling;
+        r.pub = (uint32_t*)w.inst;   // the work-list buffer is free when the kernels route themselves
         r.enabled = 1; r.publish = 0;
     }
     const uint32_t mi = max_instances(m->cfg, query_count);
     // phase 1 and phase 2 may start before their predecessor has drained
-    CU(launch_phase1(m, (cudaStream_t)stream, a, mi, true));
-    CU(launch_phase2(m, (cudaStream_t)stream, a, query_count, mi, y, hidden, true));
+    static const bool pdl = getenv("SHRIKE_NO_PDL") == nullptr;   // diagnostics: plain stream order instead
+    CU(launch_phase1(m, (cudaStream_t)stream, a, mi, pdl && getenv("SHRIKE_P1_PLAIN") == nullptr));
+    CU(launch_phase2(m, (cudaStream_t)stream, a, query_count, mi, y, hidden, pdl));
     return SHRIKE_OK;
 }
 

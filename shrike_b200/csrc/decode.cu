@@ -408,18 +408,18 @@ __global__ void __launch_bounds__(kP2Warps * 32) phase2_kernel(const ExpertArgs 
     }
     __syncwarp();
 
-    // Self-routing (one decode row): the logits were complete before phase 1 began, so this block
-    // repeats the selection now and fetches its weights while phase 1 runs.
-    __shared__ SelfRouteSmem srs;
+        __shared__ SelfRouteSmem srs;
+    bool first = true;
     if (a.sr.enabled) {
-        SelfRoute r = a.sr;
-        r.publish = 0;
-        self_route_block(r, srs, a.status);
+        // phase 1's publishing block left the picks, cells and weights: they are visible once phase 1 is
+        pdl_wait();
+        pdl_launch_dependents();
+        first = false;
+        self_route_read(a.sr, srs);
     }
     const uint32_t n_inst = a.sr.enabled ? srs.n_routed + (a.shared_block ? 1u : 0u) : *a.n_inst;
     const uint32_t units = n_inst * ksplit;
     uint32_t parity = 0;
-    bool first = true;
     for (uint32_t u = warp; u < units; u += nw) {
         const uint32_t ii = u / ksplit, ks = u % ksplit;
         Instance in;
@@ -633,6 +633,9 @@ static cudaError_t launch_p2_t(cudaStream_t st, const ExpertArgs& a, uint32_t T,
     const uint32_t most = gmin / QT<BITS, GROUP>::kBatch;
     if (ksplit > most) ksplit = most;
     if (ksplit < 1) ksplit = 1;
+    // no more warps than units: the registers left over let the next launch's blocks start (and fetch
+    // their weights) on the same SMs while this one runs
+    if (max_inst * ksplit < warps) warps = max_inst * ksplit;
     const uint32_t smem = p2_smem(gmax, T, warps);
     auto k = phase2_kernel<BITS, GROUP, META>;
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

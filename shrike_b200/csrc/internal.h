@@ -51,6 +51,7 @@ struct SelfRoute {
     float* out_w;
     uint32_t* out_slots;
     uint32_t* out_counts;
+    uint32_t* pub;                // 32 words: the routing result phase 1 leaves for phase 2
     uint32_t ne, top_k, sigmoid_scores, round_f16, pool_cells;
     float scaling;
     uint32_t enabled;             // 0: the work lists of a route kernel are used instead

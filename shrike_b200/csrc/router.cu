@@ -462,9 +462,10 @@ __global__ void __launch_bounds__(kRouterWarps * 32) route_fused_kernel(const Ro
     if (a.trace) ts[0] = globaltimer_ns();
 
     // the weight rows do not depend on the previous kernel: fetch them first
-    logits_body(a, [] {
+    logits_body(a, [&] {
         pdl_wait();
         pdl_launch_dependents();
+        if (a.trace) ts[4] = globaltimer_ns();
     });
     if (a.trace) ts[1] = globaltimer_ns();
 
@@ -478,7 +479,10 @@ __global__ void __launch_bounds__(kRouterWarps * 32) route_fused_kernel(const Ro
     }
 
     if (a.trace) ts[2] = globaltimer_ns();
-    if (a.no_tail) return;
+    if (a.no_tail) {
+        if (a.trace && tid == 0) for (int i = 0; i < 8; ++i) a.trace[8 * blockIdx.x + i] = ts[i];
+        return;
+    }
     __threadfence();
     __syncthreads();
     if (tid == 0) {

@@ -211,12 +211,34 @@ __device__ __forceinline__ void self_route_block(const SR& r, SelfRouteSmem& sm,
         }
         if (mine != SHRIKE_SLOT_MISS) sm.order[pos] = tid;
         const uint32_t n_routed = __popc(__ballot_sync(0xffffffffu, mine != SHRIKE_SLOT_MISS));
+        if (r.publish && r.pub) {
+            // what phase 2 needs, in one place: [0..7] cell, [8..15] order, [16..23] weight bits, [24] count
+            if (tid < SHRIKE_MAX_TOP_K) {
+                r.pub[tid] = tid < r.top_k ? slot : SHRIKE_SLOT_MISS;
+                r.pub[16 + tid] = tid < r.top_k ? __float_as_uint(w) : 0u;
+            }
+            if (mine != SHRIKE_SLOT_MISS) r.pub[8 + pos] = tid;
+            if (tid == 0) r.pub[24] = n_routed;
+        }
         if (tid == 0) {
             sm.n_routed = n_routed;
             sm.misses = misses;
             if (r.publish && r.out_counts) { r.out_counts[0] = r.top_k - misses; r.out_counts[1] = misses; }
         }
     }
+    __syncthreads();
+}
+
+// Phase 2 reads what phase 1's publishing block left (complete and visible once phase 1 is).
+template <class SR>
+__device__ __forceinline__ void self_route_read(const SR& r, SelfRouteSmem& sm) {
+    const uint32_t tid = threadIdx.x;
+    if (tid < SHRIKE_MAX_TOP_K) {
+        sm.slot[tid] = __ldcg(r.pub + tid);
+        sm.order[tid] = __ldcg(r.pub + 8 + tid);
+        sm.w[tid] = __uint_as_float(__ldcg(r.pub + 16 + tid));
+    }
+    if (tid == 0) sm.n_routed = __ldcg(r.pub + 24);
     __syncthreads();
 }
 
