@@ -93,33 +93,70 @@ __device__ __forceinline__ void load_row_f32(const float* row, uint32_t chunks, 
 #pragma unroll
     for (int i = 0; i < N; ++i) {
         const uint32_t c = lane + 32 * i;
-        if (!PRED || c < chunks) wr[i] = __ldg((const float4*)row + c);
+        if (!PRED || c < chunks) {
+            // a volatile load: it must stay ahead of the dependency wait that follows the prefetch
+            const uint4 v = ldg_stream_u128((const float4*)row + c);
+            wr[i] = make_float4(__uint_as_float(v.x), __uint_as_float(v.y), __uint_as_float(v.z), __uint_as_float(v.w));
+        }
     }
 }
 
 // One lane's share of an fp32 row against one activation row: float4 chunks
-// lane, lane+32, ... in order, four fused multiply-adds each.
+// lane, lane+32, ... in order, four fused multiply-adds each. The activation
+// chunks are fetched eight at a time ahead of the arithmetic: issued one by
+// one between the dependent multiply-adds they cost one L2 round trip each.
 template <int N, bool PRED>
 __device__ __forceinline__ float lane_dot_f32(const float4 (&wr)[N], uint32_t chunks, uint32_t lane,
                                               const void* xrow, uint32_t dt, const uint16_t* eff_scale) {
     float acc = 0.f;
+    constexpr int kBatch = 8;
 #pragma unroll
-    for (int i = 0; i < N; ++i) {
-        const uint32_t c = lane + 32 * i;
-        if (!PRED || c < chunks) {
-            float x[4];
-            load_act4(xrow, c, dt, x);
-            if (eff_scale) {
-                const uint2 s = __ldg((const uint2*)eff_scale + c);
-                x[0] = __fmul_rn(x[0], __uint_as_float(s.x << 16));
-                x[1] = __fmul_rn(x[1], __uint_as_float(s.x & 0xffff0000u));
-                x[2] = __fmul_rn(x[2], __uint_as_float(s.y << 16));
-                x[3] = __fmul_rn(x[3], __uint_as_float(s.y & 0xffff0000u));
+    for (int i0 = 0; i0 < N; i0 += kBatch) {
+        uint4 raw[kBatch];
+        uint2 es[kBatch];
+#pragma unroll
+        for (int j = 0; j < kBatch; ++j) {
+            const int i = i0 + j;
+            const uint32_t c = lane + 32 * i;
+            raw[j] = make_uint4(0, 0, 0, 0);
+            es[j] = make_uint2(0x3f803f80u, 0x3f803f80u);   // bf16 ones
+            if (i < N && (!PRED || c < chunks)) {
+                if (dt == SHRIKE_DTYPE_FP32) {
+                    raw[j] = __ldg((const uint4*)xrow + c);
+                } else {
+                    const uint2 v = __ldg((const uint2*)xrow + c);
+                    raw[j].x = v.x; raw[j].y = v.y;
+                }
+                if (eff_scale) es[j] = __ldg((const uint2*)eff_scale + c);
             }
-            acc = __fmaf_rn(wr[i].x, x[0], acc);
-            acc = __fmaf_rn(wr[i].y, x[1], acc);
-            acc = __fmaf_rn(wr[i].z, x[2], acc);
-            acc = __fmaf_rn(wr[i].w, x[3], acc);
+        }
+#pragma unroll
+        for (int j = 0; j < kBatch; ++j) {
+            const int i = i0 + j;
+            const uint32_t c = lane + 32 * i;
+            if (i < N && (!PRED || c < chunks)) {
+                float x[4];
+                if (dt == SHRIKE_DTYPE_FP32) {
+                    x[0] = __uint_as_float(raw[j].x); x[1] = __uint_as_float(raw[j].y);
+                    x[2] = __uint_as_float(raw[j].z); x[3] = __uint_as_float(raw[j].w);
+                } else if (dt == SHRIKE_DTYPE_FP16) {
+                    x[0] = f16_bits_to_f32(raw[j].x & 0xffff); x[1] = f16_bits_to_f32(raw[j].x >> 16);
+                    x[2] = f16_bits_to_f32(raw[j].y & 0xffff); x[3] = f16_bits_to_f32(raw[j].y >> 16);
+                } else {
+                    x[0] = __uint_as_float(raw[j].x << 16); x[1] = __uint_as_float(raw[j].x & 0xffff0000u);
+                    x[2] = __uint_as_float(raw[j].y << 16); x[3] = __uint_as_float(raw[j].y & 0xffff0000u);
+                }
+                if (eff_scale) {
+                    x[0] = __fmul_rn(x[0], __uint_as_float(es[j].x << 16));
+                    x[1] = __fmul_rn(x[1], __uint_as_float(es[j].x & 0xffff0000u));
+                    x[2] = __fmul_rn(x[2], __uint_as_float(es[j].y << 16));
+                    x[3] = __fmul_rn(x[3], __uint_as_float(es[j].y & 0xffff0000u));
+                }
+                acc = __fmaf_rn(wr[i].x, x[0], acc);
+                acc = __fmaf_rn(wr[i].y, x[1], acc);
+                acc = __fmaf_rn(wr[i].z, x[2], acc);
+                acc = __fmaf_rn(wr[i].w, x[3], acc);
+            }
         }
     }
     return acc;

@@ -47,14 +47,19 @@ __device__ __forceinline__ float sigmoid_det(float x) { return __fdiv_rn(1.0f, _
 
 // Order-preserving key of expert e's selection score (0 = not a candidate); the same
 // arithmetic as select_row.
+template <class A>
+__device__ __forceinline__ uint32_t selection_key_of(float raw, float bias, const A& a) {
+    const float s = __fadd_rn(__fadd_rn(a.sigmoid_scores ? sigmoid_det(raw) : raw, bias), 0.0f);  // -0 -> +0
+    const uint32_t b = __float_as_uint(s);
+    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+
 template <bool CG, class A>
 __device__ __forceinline__ uint32_t selection_key(const float* lg, const A& a, uint32_t e) {
     if (e >= a.ne) return 0u;
     const float raw = CG ? __ldcg(lg + e) : lg[e];
     const float bias = a.logit_bias ? bf16_bits_to_f32(a.logit_bias[e]) : 0.0f;
-    const float s = __fadd_rn(__fadd_rn(a.sigmoid_scores ? sigmoid_det(raw) : raw, bias), 0.0f);  // -0 -> +0
-    const uint32_t b = __float_as_uint(s);
-    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+    return selection_key_of(raw, bias, a);
 }
 
 // Route weights of the picks (lane r holds the r-th pick): moe.metal:458-490, sums in rank order.
@@ -96,8 +101,16 @@ __device__ __forceinline__ void select_row_block(const float* lg, const A& a, Se
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     // the first four warps do the work; larger blocks only join the barriers
     if (tid < 128) {
-        ss.keys[tid] = selection_key<true>(lg, a, tid);
-        ss.keys[tid + 128] = selection_key<true>(lg, a, tid + 128);
+        // both logits (and biases) are requested before either is used: one L2 round trip, not two
+        const uint32_t e0 = tid, e1 = tid + 128;
+        const float raw0 = e0 < a.ne ? __ldcg(lg + e0) : 0.f, raw1 = e1 < a.ne ? __ldcg(lg + e1) : 0.f;
+        uint16_t lb0 = 0, lb1 = 0;
+        if (a.logit_bias) {
+            if (e0 < a.ne) lb0 = a.logit_bias[e0];
+            if (e1 < a.ne) lb1 = a.logit_bias[e1];
+        }
+        ss.keys[e0] = e0 < a.ne ? selection_key_of(raw0, bf16_bits_to_f32(lb0), a) : 0u;
+        ss.keys[e1] = e1 < a.ne ? selection_key_of(raw1, bf16_bits_to_f32(lb1), a) : 0u;
     }
     if (tid < 32) { ss.cand_key[tid] = 0u; ss.cand_id[tid] = 0u; }
     if (tid < SHRIKE_MAX_TOP_K) { ss.sel_key[tid] = 0u; ss.sel_id[tid] = 0u; }
@@ -169,14 +182,13 @@ __device__ __forceinline__ void self_route_block(const SR& r, SelfRouteSmem& sm,
                                                  const uint64_t* table_sm = nullptr) {
     uint32_t id;
     float w;
-    select_row_block(r.logits, r, sm.sel, id, w);
     const uint32_t tid = threadIdx.x;
+    // requested before the selection so that its round trip overlaps it
+    uint32_t io = 1u;
+    if (tid < 32 && r.io_status) io = *(const volatile uint32_t*)r.io_status;
+    select_row_block(r.logits, r, sm.sel, id, w);
     if (tid < 32) {
-        bool ready = true;
-        if (r.io_status) {
-            const uint32_t s = *r.io_status;
-            ready = s == 1u || s == 3u;
-        }
+        const bool ready = io == 1u || io == 3u;
         uint32_t slot = SHRIKE_SLOT_MISS;
         bool miss = false;
         if (tid < r.top_k) {
