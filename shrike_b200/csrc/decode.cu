@@ -32,7 +32,9 @@ struct QT {
     static constexpr int kMmas = GROUP / 16;           // k16 steps per group
     static constexpr int kBRegs = GROUP / 8;           // u32 of activations per thread and group
     static constexpr int kBatch = 8 / kWords;          // groups whose weights are in flight together
-    static constexpr float kZero = BITS == 4 ? 8.0f : 128.0f;
+    // The tiles multiply (1024 + q): sum((1024 + q) x) = 1024 sum(x) + sum(q x), so a group contributes
+    // scale * c + (bias - 1024 * scale) * sum(x); products and sums stay exact in fp32 (|c| < 2^24 * ulp).
+    static constexpr float kOffset = -1024.0f;
 };
 
 template <int W>
@@ -53,14 +55,15 @@ template <int BITS, int W>
 __device__ __forceinline__ void unpack_step(const uint32_t (&w)[W], int m, uint32_t& lo, uint32_t& hi) {
     if constexpr (BITS == 4) {
         const uint32_t v = w[m >> 1] >> ((m & 1) * 8);
-        // (1024 + n_i, 1024 + n_{i+4}) - 1032 = (n_i - 8, n_{i+4} - 8), exact in fp16
-        lo = hsub2_u32(lop3_and_or(v, 0x000F000Fu, 0x64006400u), 0x64086408u);
-        hi = hsub2_u32(lop3_and_or(v >> 4, 0x000F000Fu, 0x64006400u), 0x64086408u);
+        // (1024 + n_i, 1024 + n_{i+4}) as fp16, exact: the 1024 is taken out again per group together
+        // with the zero point (QT::kOffset), which saves the packed subtract per register
+        lo = lop3_and_or(v, 0x000F000Fu, 0x64006400u);
+        hi = lop3_and_or(v >> 4, 0x000F000Fu, 0x64006400u);
     } else {
         const uint32_t v = w[m];
-        // (1024 + b0, 1024 + b1) - 1152 = (b0 - 128, b1 - 128)
-        lo = hsub2_u32(prmt(v, 0x64646464u, 0x5140u), 0x64806480u);
-        hi = hsub2_u32(prmt(v, 0x64646464u, 0x5342u), 0x64806480u);
+        // (1024 + b0, 1024 + b1)
+        lo = prmt(v, 0x64646464u, 0x5140u);
+        hi = prmt(v, 0x64646464u, 0x5342u);
     }
 }
 
@@ -75,7 +78,7 @@ __device__ __forceinline__ void load_bfrag(const uint16_t* p, uint32_t (&b)[G / 
 }
 
 // One group of NMAT matrices (rows g and g+8 of each) against one B fragment.
-// c[mat] = sum((q-Z)*x); with ONES also xs = column sums of x (identical in
+// c[mat] = sum((1024+q)*x); with ONES also xs = column sums of x (identical in
 // every row), otherwise the caller supplies them.
 template <int BITS, int GROUP, int NMAT, bool ONES>
 __device__ __forceinline__ void group_mma(const uint32_t (&raw)[NMAT][2][QT<BITS, GROUP>::kWords],
@@ -129,7 +132,7 @@ __device__ __forceinline__ void load_bfrags(const uint16_t* xrow, uint32_t g0, u
     }
 }
 
-// tot += scale * sum((q-Z)x) + (bias + Z*scale) * sum(x) for every group of the batch.
+// tot += scale * sum((1024+q)x) + (bias - 1024*scale) * sum(x) for every group of the batch.
 // s_sm/b_sm[mat]: the tile's [16 x G] scales / biases in shared memory.
 template <int BITS, int GROUP, int META, int NMAT, bool ONES>
 __device__ __forceinline__ void compute_batch(
@@ -153,8 +156,8 @@ __device__ __forceinline__ void compute_batch(
             for (int mat = 0; mat < NMAT; ++mat) {
                 const float s0 = meta_to_f32<META>(s_sm[mat][g * G + grp]);
                 const float s1 = meta_to_f32<META>(s_sm[mat][(g + 8) * G + grp]);
-                const float z0 = fmaf(Q::kZero, s0, meta_to_f32<META>(b_sm[mat][g * G + grp]));
-                const float z1 = fmaf(Q::kZero, s1, meta_to_f32<META>(b_sm[mat][(g + 8) * G + grp]));
+                const float z0 = fmaf(Q::kOffset, s0, meta_to_f32<META>(b_sm[mat][g * G + grp]));
+                const float z1 = fmaf(Q::kOffset, s1, meta_to_f32<META>(b_sm[mat][(g + 8) * G + grp]));
                 tot[mat][0] = fmaf(z0, xs[0], fmaf(s0, c[mat][0], tot[mat][0]));
                 tot[mat][1] = fmaf(z0, xs[1], fmaf(s0, c[mat][1], tot[mat][1]));
                 tot[mat][2] = fmaf(z1, xs[0], fmaf(s1, c[mat][2], tot[mat][2]));
