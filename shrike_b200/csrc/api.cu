@@ -93,7 +93,7 @@ cudaError_t dev_alloc(P** p, size_t bytes) {
 }
 
 void free_workspace(Workspace& w) {
-    void* ptrs[] = {w.xs, w.chunk_inst, w.n_chunk_inst, w.done_counter, w.xsum, w.logits, w.xh, w.acts, w.acts_shared, w.sorted, w.inst, w.n_inst, w.status, w.block_hist,
+    void* ptrs[] = {w.route_pub, w.xs, w.chunk_inst, w.n_chunk_inst, w.done_counter, w.xsum, w.logits, w.xh, w.acts, w.acts_shared, w.sorted, w.inst, w.n_inst, w.status, w.block_hist,
                     w.expert_offsets, w.expert_counts, w.slot_of_expert, w.partials, w.x_dev, w.y_dev,
                     w.ids_dev, w.w_dev, w.gate_dev, w.slots_dev, w.counts_dev};
     for (void* p : ptrs)
@@ -198,6 +198,7 @@ int shrike_moe_create(const shrike_moe_config* config, int device, shrike_moe** 
     A(&w.partials, T > SHRIKE_MAX_DECODE_TOKENS ? (T * K + (c.has_shared ? T : 0)) * c.d * 4 : 0);
     A(&w.chunk_inst, T > SHRIKE_MAX_DECODE_TOKENS ? umma_max_chunk_instances(c, c.max_tokens) * umma_chunk_instance_bytes() : 0);
     A(&w.n_chunk_inst, 8);
+    A(&w.route_pub, 128);
     A(&w.xs, T > SHRIKE_MAX_DECODE_TOKENS ? T * K * c.d * 2 : 0);
     A(&w.x_dev, T * c.d * ab);
     A(&w.y_dev, T * c.d * ab);
@@ -560,7 +561,7 @@ int shrike_encode_decode_layer(shrike_moe* m, void* stream, const shrike_pool* p
         r.out_ids = ids; r.out_w = wt; r.out_slots = w.slots_dev; r.out_counts = nullptr;
         r.ne = c.num_experts; r.top_k = c.top_k; r.sigmoid_scores = c.router_kind == SHRIKE_ROUTER_SIGMOID;
         r.round_f16 = c.round_route_weights_f16; r.pool_cells = pool->view.cells; r.scaling = c.routed_scaling;
-        r.pub = (uint32_t*)w.inst;   // the work-list buffer is free when the kernels route themselves
+        r.pub = w.route_pub;
         r.enabled = 1; r.publish = 0;
     }
     const uint32_t mi = max_instances(m->cfg, query_count);

@@ -102,6 +102,7 @@ struct Workspace {
     uint32_t* n_chunk_inst = nullptr; // [0] instances, [1] sorted rows
     uint16_t* xs = nullptr;         // prefill: fp16 activation rows in expert-sorted order [max_tokens x top_k x d]
     void* tensor_maps = nullptr;    // host: the TMA descriptors of xs, acts, xh, acts_shared
+    uint32_t* route_pub = nullptr;  // 32 words: the routing result phase 1 publishes for phase 2 (one-row decode)
     // forward_host staging
     void* x_dev = nullptr; void* y_dev = nullptr;
     uint32_t* ids_dev = nullptr; float* w_dev = nullptr; float* gate_dev = nullptr;
