@@ -418,8 +418,11 @@ __global__ void __launch_bounds__(kP2Warps * 32) phase2_kernel(const ExpertArgs 
         pdl_wait();
         pdl_launch_dependents();
         first = false;
+        if (a.trace) t2_wait = globaltimer_ns();
         self_route_read(a.sr, srs);
     }
+    const uint64_t t2_pub = a.trace ? globaltimer_ns() : 0;
+    uint64_t t2_loads = 0, t2_acc = 0;
     const uint32_t n_inst = a.sr.enabled ? srs.n_routed + (a.shared_block ? 1u : 0u) : *a.n_inst;
     const uint32_t units = n_inst * ksplit;
     uint32_t parity = 0;
@@ -452,6 +455,7 @@ __global__ void __launch_bounds__(kP2Warps * 32) phase2_kernel(const ExpertArgs 
         wrow[0][1] = base + off.w[2] + (size_t)(d0 + g + 8) * row_bytes + toff;
         uint32_t raw[Q::kBatch][1][2][Q::kWords];
         load_batch<BITS, GROUP, 1>(wrow, gbeg, 1, gend, raw);
+        if (a.trace && t2_loads == 0) t2_loads = globaltimer_ns();
 
         if (lane == 0) {
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -477,6 +481,7 @@ __global__ void __launch_bounds__(kP2Warps * 32) phase2_kernel(const ExpertArgs 
         tile_accumulate<BITS, GROUP, META, 1, true>(wrow, s_sm, b_sm, brow, G, gbeg, gend, 1, g, t, bar, parity,
                                               a.status, tot, true, raw);
         parity ^= 1;
+        if (a.trace && t2_acc == 0) t2_acc = globaltimer_ns();
 
         const float ab0 = add_bias ? bf16_bits_to_f32(ab_sm[g]) : 0.f;
         const float ab1 = add_bias ? bf16_bits_to_f32(ab_sm[g + 8]) : 0.f;
@@ -504,7 +509,12 @@ __global__ void __launch_bounds__(kP2Warps * 32) phase2_kernel(const ExpertArgs 
         pdl_wait();
         pdl_launch_dependents();
     }
+    // the residual of this thread's first output is requested before the barrier: its round trip
+    // would otherwise be the last thing the block waits for
+    float h_first = 0.f;
+    if (hidden && tid < T * 16) h_first = load_act(hidden, (size_t)(tid >> 4) * a.d + d0 + (tid & 15), a.act_dtype);
     __syncthreads();
+    const uint64_t t2_sync = a.trace ? globaltimer_ns() : 0;
     // y = sum over warps; hidden += y (moe_phase2_finish, moe.metal:889-893)
     for (uint32_t i = tid; i < T * 16; i += nw * 32) {
         const uint32_t token = i >> 4, row = i & 15;
@@ -513,13 +523,14 @@ __global__ void __launch_bounds__(kP2Warps * 32) phase2_kernel(const ExpertArgs 
         const size_t o = (size_t)token * a.d + d0 + row;
         store_act(y, o, a.act_dtype, acc);
         if (hidden) {
-            const float h = load_act(hidden, o, a.act_dtype) + round_act(a.act_dtype, acc);
+            const float h = (i == tid ? h_first : load_act(hidden, o, a.act_dtype)) + round_act(a.act_dtype, acc);
             store_act(hidden, o, a.act_dtype, h);
         }
     }
     if (a.trace && tid == 0) {
         uint64_t* tr = a.trace + 8 * (size_t)(1024 + blockIdx.x);   // after the blocks of phase 1
-        tr[0] = t2_start; tr[1] = t2_wait; tr[2] = globaltimer_ns();
+        tr[0] = t2_start; tr[1] = t2_wait; tr[2] = globaltimer_ns(); tr[3] = t2_pub; tr[4] = t2_loads; tr[5] = t2_acc;
+        tr[6] = t2_sync;
     }
 }
 
