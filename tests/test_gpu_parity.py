@@ -296,6 +296,35 @@ def test_fused_decode_layer_equals_the_separate_calls(cuda_device, T, kw):
     layer.close()
 
 
+@pytest.mark.parametrize("T", [1, 5])
+def test_fused_layer_ties_misses_and_unready_batches(cuda_device, T):
+    """The one-call decode layer (at one row the expert kernels route themselves): equal scores pick the
+    lower id, an expert that is not resident contributes nothing, a batch that is not ready leaves the
+    shared term only -- all as the oracle has it."""
+    cfg = small_config(d=256, num_experts=16, top_k=4)
+    layer = Layer(cfg)
+    w = layer.router_w.copy()
+    w[5] = w[2]
+    w[9] = w[2]
+    layer.router_w = w
+    layer._rw.copy_(torch.from_numpy(w))
+    x = inputs(T, 256, seed=60 + T)
+    ids_ref, w_ref, _ = layer.oracle_route(x)
+    y, ids, wt, _ = layer.forward(x, fused=True)
+    assert (ids == ids_ref).all() and (wt == w_ref).all()
+    assert rel_l2(y, layer.oracle_forward(x, ids_ref, w_ref)) <= TOL
+    # the first pick of row 0 is loading, not resident
+    gone = int(ids_ref[0, 0])
+    layer.moe.residency_set(0, gone, 0, 1)
+    y, ids, wt, _ = layer.forward(x, fused=True)
+    assert (ids == ids_ref).all() and (wt == w_ref).all()
+    assert rel_l2(y, layer.oracle_forward(x, ids_ref, w_ref, skip_experts={gone})) <= TOL
+    layer.moe.residency_set(0, gone, gone, 2)
+    y, _, w3, _ = layer.forward(x, io_status=capi.IO_FAILED, fused=True)
+    assert rel_l2(y, layer.oracle_forward(x, ids_ref, np.zeros_like(w3))) <= TOL
+    layer.close()
+
+
 def test_fused_route_reports_slots_counts_and_status(cuda_device):
     cfg = small_config()
     layer = Layer(cfg)
