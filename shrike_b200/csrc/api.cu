@@ -567,7 +567,7 @@ int shrike_encode_decode_layer(shrike_moe* m, void* stream, const shrike_pool* p
     const uint32_t mi = max_instances(m->cfg, query_count);
     // phase 1 and phase 2 may start before their predecessor has drained
     static const bool pdl = getenv("SHRIKE_NO_PDL") == nullptr;   // diagnostics: plain stream order instead
-    CU(launch_phase1(m, (cudaStream_t)stream, a, mi, pdl && getenv("SHRIKE_P1_PLAIN") == nullptr));
+    CU(launch_phase1(m, (cudaStream_t)stream, a, mi, pdl));
     CU(launch_phase2(m, (cudaStream_t)stream, a, query_count, mi, y, hidden, pdl));
     return SHRIKE_OK;
 }
