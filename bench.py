@@ -40,7 +40,7 @@ def parse_args():
     ap.add_argument("--tokens", type=int, default=1, help="decode batch: 1, 4 or 16")
     ap.add_argument("--layers", type=int, default=LAYERS)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--workload", choices=["decode", "prefill", "ep"], default="decode",
+    ap.add_argument("--workload", choices=["decode", "prefill", "ep", "gptoss"], default="decode",
                     help="decode: the 40-layer sweep (headline); prefill: one layer, 4096 rows, Zipf(1.1)-skewed routing")
     ap.add_argument("--rows", type=int, default=4096, help="rows of the prefill workload")
     ap.add_argument("--no-sweep", action="store_true", help="skip the T=4 / T=16 lines of the sweep")
@@ -175,7 +175,7 @@ def cpu_reference_run(T: int, layers: int, steps: int, warmup: int, budget_s: fl
 class Workload:
     """All layers resident on one GPU; per-layer handles so that every layer keeps its own work lists."""
 
-    def __init__(self, T: int, layers: int, device_index: int):
+    def __init__(self, T: int, layers: int, device_index: int, cfg=None):
         import torch
         from shrike_b200 import capi, fixtures as fx
         from shrike_b200.moe import ExpertCellArena, MoE, RouterOperands, expert_offsets, round_up
@@ -184,25 +184,27 @@ class Workload:
         self.T, self.L = T, layers
         torch.cuda.set_device(device_index)
         self.dev = torch.device("cuda", device_index)
-        self.cfg = cfg = fx.qwen_config(max_tokens=16)
+        self.cfg = cfg = cfg if cfg is not None else fx.qwen_config(max_tokens=16)
         self.moes = [MoE(cfg, device_index) for _ in range(layers)]
         self.off, self.block_bytes = expert_offsets(cfg)
-        self.soff, self.sblock_bytes = expert_offsets(cfg, shared=True)
+        self.soff, self.sblock_bytes = expert_offsets(cfg, shared=True) if cfg.has_shared else (None, 0)
         stride = round_up(max(self.block_bytes, self.sblock_bytes), 256)
         ne = cfg.num_experts
         self.pool = ExpertCellArena(self.moes[0], layers * (ne + 1), stride, chunks=8)
         self.routers, self.shared, self._keep = [], [], []
         for l in range(layers):
             self.pool.fill_synthetic(l * ne, ne, SEED, l)
-            self.pool.fill_synthetic(layers * ne + l, 1, SEED, l, first_expert=100000, shared=True)
+            if cfg.has_shared:
+                self.pool.fill_synthetic(layers * ne + l, 1, SEED, l, first_expert=100000, shared=True)
             m = self.moes[l]
             m.create_residency(1)
             m.residency_set_layer_identity(0, l * ne)
             rw = torch.from_numpy(router_weights(l, ne, cfg.d)).to(self.dev)
-            gw = torch.from_numpy(gate_weights(l, cfg.d)).to(self.dev)
+            gw = torch.from_numpy(gate_weights(l, cfg.d)).to(self.dev) if cfg.shared_gated else None
             self._keep += [rw, gw]
             self.routers.append(RouterOperands(weights=rw, shared_gate=gw))
-            self.shared.append(capi.SharedExpert(self.pool.cell_address(layers * ne + l), self.soff))
+            self.shared.append(capi.SharedExpert(self.pool.cell_address(layers * ne + l), self.soff)
+                               if cfg.has_shared else None)
         k = cfg.top_k
         self.ids = [torch.zeros((T, k), dtype=torch.int32, device=self.dev) for _ in range(layers)]
         self.slots = [torch.zeros((T, k), dtype=torch.int32, device=self.dev) for _ in range(layers)]
@@ -474,6 +476,47 @@ def run_prefill(args, local_rank: int):
 
 
 
+def run_gptoss(args, local_rank: int):
+    """gpt-oss-20B-shape layers (D = F = 2880, 32 experts top-4, int4 g32, additive biases, clamped SwiGLU, no
+    shared expert) at --tokens rows (1 or 64): 8 independently seeded layers chained like the decode sweep, so
+    every layer call streams its own cold expert blocks."""
+    import torch
+    from shrike_b200 import fixtures as fx
+    T, L, K, W = args.tokens, min(args.layers, 8), args.steps, max(3, args.warmup)
+    cfg = fx.gpt_oss_config(max_tokens=128)
+    wl = Workload(T, L, local_rank, cfg)
+    g_step = wl.capture(wl.step_resident)
+    g_e2e = wl.capture(wl.step_e2e)
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    ms = wl.time_graph(g_step, K, W)
+    ms_e2e = wl.time_graph(g_e2e, K, W)
+    clocks = sampler.stop()
+    wl.check_status()
+    distinct = wl.distinct_experts()
+    mean_units = sum(distinct) / L
+    peak, peak_src = measured_peaks()
+    gbs = mean_units * wl.block_bytes / (ms / L * 1e-3) / 1e9
+    line = {
+        "metric": METRIC, "value": T / (ms / 1e3) , "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "int4 weights x fp16 operands, fp32 accumulate", "data": "synthetic",
+        "config": {"workload": f"gpt-oss-20b expert shape, {L} chained layers, batch {T} (D 2880, F 2880, 32 experts top-4, "
+                               "int4 g32, bf16 additive biases, clamped SwiGLU)",
+                   "layers": L, "distinct_experts_per_layer": mean_units,
+                   "l2": f"inputs larger than L2: {mean_units * L * wl.block_bytes / 1e6:.0f} MB of distinct expert "
+                         "blocks per step"},
+        "roofline": {"bound": "hbm", "kernel": "whole layer call (one row: route + phase 1 + phase 2; more than 16 rows: router + expert-grouped tcgen05 path)", "achieved": gbs, "peak": peak,
+                     "unit": "GB/s", "frac": gbs / peak, "peak_source": peak_src, "traffic": None,
+                     "us_per_layer": ms / L * 1e3},
+        "e2e": {"value": T / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e,
+                "h2d_bytes_per_step": wl.x_host.numel() * 2, "d2h_bytes_per_step": wl.out_host.numel() * 2},
+        "gpu_launches": (K + W) * wl.launches_per_step, "clocks": clocks,
+    }
+    wl.close()
+    return line
+
+
 def run_ep(args, rank: int, world: int, local_rank: int):
     """Expert-parallel Kimi-Linear-shape layer (int8 g64, 256 experts top-8 sigmoid, shared expert): every rank
     holds 256/N experts and its own mixed batch of 16 decode rows + one 2048-row prefill chunk; rows are
@@ -589,6 +632,10 @@ def main():
     if args.workload == "prefill":
         if rank == 0:
             print(json.dumps(run_prefill(args, local_rank)))
+        return
+    if args.workload == "gptoss":
+        if rank == 0:
+            print(json.dumps(run_gptoss(args, local_rank)))
         return
     if args.workload == "ep":
         import torch.distributed as dist

@@ -243,7 +243,10 @@ int shrike_encode_route_decode(shrike_moe* moe, void* stream, const shrike_route
  * predecessor drains): what encodeDecodeTailStage's router + classification
  * (RealForwardRunner.swift:2834) and encodeSpeculativeRouted
  * (RealForwardRunner.swift:5520-5572) encode for one routed layer.
- * out_indices / out_weights may be NULL. */
+ * out_indices / out_weights may be NULL. With more than 16 rows, no io_status
+ * and a handle created for prefill (max_tokens > 64) the call runs the router,
+ * the classification and the expert-grouped tensor-core path instead: the same
+ * result within the parity tolerance, every expert read once for all its rows. */
 int shrike_encode_decode_layer(shrike_moe* moe, void* stream, const shrike_pool* pool,
                                const shrike_expert_offsets* routed_offsets,
                                const uint64_t* residency_table_row,

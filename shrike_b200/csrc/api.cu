@@ -530,6 +530,18 @@ int shrike_encode_decode_layer(shrike_moe* m, void* stream, const shrike_pool* p
     uint32_t* ids = out_indices ? out_indices : w.ids_dev;
     float* wt = out_weights ? out_weights : w.w_dev;
     float* gate = m->cfg.shared_gated ? w.gate_dev : nullptr;
+    // A few dozen rows on a handle that owns the prefill operands: the expert-grouped tensor-core call reads
+    // every expert once for all its rows, where the 8-row tiles read it once per 8 (gpt-oss shape, 64 rows:
+    // 279 us per layer against 740). The status word of a streamed batch is only honoured by the tiles.
+    if (query_count > 16 && !io_status && w.xs && umma_supported(m->cfg)) {
+        int rcg = shrike_encode_router(m, stream, router, x, query_count, m->cfg.d, ids, wt, gate);
+        if (rcg) return rcg;
+        rcg = shrike_encode_residency_classification(m, stream, ids, residency_table_row, query_count, w.slots_dev,
+                                                     nullptr, nullptr, nullptr);
+        if (rcg) return rcg;
+        return shrike_encode_moe_prefill(m, stream, pool, routed_offsets, ids, w.slots_dev, wt, x, query_count, shared,
+                                         gate, y, hidden);
+    }
     // One row: the route launch stops after the logits and the fp16 operand copy, and every block of
     // phase 1 and phase 2 repeats the selection itself -- no block waits for another to publish picks,
     // cells and work lists. More rows keep the route kernel's tail (selection, lookup, grouping).

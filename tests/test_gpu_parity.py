@@ -325,6 +325,24 @@ def test_fused_layer_ties_misses_and_unready_batches(cuda_device, T):
     layer.close()
 
 
+@pytest.mark.parametrize("T", [17, 40, 64])
+def test_decode_layer_call_on_a_prefill_handle_with_dozens_of_rows(cuda_device, T):
+    """More than 16 rows on a handle that owns the prefill operands: the one-call layer runs the router, the
+    classification and the expert-grouped tensor-core path. Same ids and weights, outputs inside the tolerance,
+    the residual updated in place."""
+    cfg = small_config(d=256, f=128, shared_f=128, max_tokens=128)
+    layer = Layer(cfg)
+    x = inputs(T, 256, seed=70 + T)
+    h0 = inputs(T, 256, seed=71 + T)
+    y, ids, w, h = layer.forward(x, hidden=h0, fused=True)
+    ids_ref, w_ref, _ = layer.oracle_route(x)
+    assert (ids == ids_ref).all() and (w == w_ref).all()
+    y_ref = layer.oracle_forward(x, ids_ref, w_ref)
+    assert rel_l2(y, y_ref) <= TOL
+    assert np.abs(h - (h0 + y)).max() <= 1e-5 * max(1.0, np.abs(h0).max())
+    layer.close()
+
+
 def test_fused_route_reports_slots_counts_and_status(cuda_device):
     cfg = small_config()
     layer = Layer(cfg)
