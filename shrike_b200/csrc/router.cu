@@ -471,6 +471,24 @@ __global__ void __launch_bounds__(256, 1) router_logits_tiled_kernel(const Route
     }
 }
 
+// The shared expert's scalar gate for many rows (the tiled router covers the expert rows only): one
+// warp per row of activations at a time, the gate row held in registers, the same lane order, fused
+// multiply-adds and butterfly as everywhere else. grid ceil(T / 32), block 256: a warp takes 4 rows.
+__global__ void __launch_bounds__(256) router_gate_rows_kernel(const RouterArgs a) {
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t chunks = a.d / 4;
+    const size_t esz = a.dt == SHRIKE_DTYPE_FP32 ? 4 : 2;
+    float4 wr[kRouterMaxChunks];
+    load_row_f32<kRouterMaxChunks, true>(a.gate_row, chunks, lane, wr);
+    for (uint32_t j = 0; j < 4; ++j) {
+        const uint32_t tk = blockIdx.x * 32 + warp * 4 + j;
+        if (tk >= a.T) break;
+        const void* xrow = (const uint8_t*)a.hidden + (size_t)tk * a.stride * esz;
+        const float acc = butterfly_sum(lane_dot_f32<kRouterMaxChunks, true>(wr, chunks, lane, xrow, a.dt, nullptr));
+        if (lane == 0) a.gate_out[tk] = sigmoid_det(acc);
+    }
+}
+
 __global__ void __launch_bounds__(128) router_select_kernel(const RouterArgs a) {
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t row = blockIdx.x * 4 + warp;
@@ -693,10 +711,7 @@ cudaError_t launch_router(const shrike_moe* m, cudaStream_t st, const shrike_rou
         e = cudaGetLastError();
         if (e != cudaSuccess) return e;
         if (a.gate_row) {
-            RouterArgs g = a;
-            g.row_base = a.ne;
-            g.tokens_per_block = 1;
-            router_logits_kernel<<<dim3(1, T), kRouterWarps * 32, 0, st>>>(g);
+            router_gate_rows_kernel<<<(T + 31) / 32, 256, 0, st>>>(a);
             e = cudaGetLastError();
             if (e != cudaSuccess) return e;
         }
