@@ -444,8 +444,8 @@ __global__ void __launch_bounds__(kP2Warps * 32) phase2_kernel(const ExpertArgs 
         const uint32_t G = F / GROUP;
         const Offsets3& off = shared ? a.shared : a.routed;
         const uint8_t* base = shared ? a.shared_block : pool_cell_base(a.pool, in.slot);
-        const uint32_t gbeg = (uint32_t)((uint64_t)G * ks / ksplit);
-        const uint32_t gend = (uint32_t)((uint64_t)G * (ks + 1) / ksplit);
+        const uint32_t gbeg = G * ks / ksplit;          // G * ksplit is far below 2^32: no 64-bit division
+        const uint32_t gend = G * (ks + 1) / ksplit;
         const bool add_bias = a.expert_bias && ks == 0;
 
         const size_t row_bytes = (size_t)F * BITS / 8;
