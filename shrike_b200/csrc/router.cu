@@ -80,13 +80,6 @@ struct RouterArgs {
     uint64_t* trace;               // diagnostics: 8 timestamps per block, or NULL
 };
 
-__device__ __forceinline__ uint32_t affine_value(const uint8_t* packed, uint32_t element, uint32_t bits) {
-    const uint32_t bit = element * bits, byte = bit >> 3, shift = bit & 7u;
-    uint32_t word = packed[byte];
-    if (shift + bits > 8u) word |= ((uint32_t)packed[byte + 1u]) << 8;
-    return (word >> shift) & ((1u << bits) - 1u);
-}
-
 // N chunks per lane; PRED: the row may be shorter than 32*N chunks.
 template <int N, bool PRED>
 __device__ __forceinline__ void load_row_f32(const float* row, uint32_t chunks, uint32_t lane, float4 (&wr)[N]) {
@@ -162,25 +155,59 @@ __device__ __forceinline__ float lane_dot_f32(const float4 (&wr)[N], uint32_t ch
     return acc;
 }
 
-// router_gemv_body (moe.metal:324-364): lane l takes elements 64g+2l, 64g+2l+1.
+// router_gemv_body (moe.metal:324-364): lane l takes elements 64g+2l, 64g+2l+1 of every group g.
+// The operands of eight groups are requested before the first is used (one memory round trip per
+// eight groups instead of one per group); the arithmetic and its order are the shader's.
 __device__ __forceinline__ float lane_dot_affine(const uint8_t* row, const uint16_t* s_row,
                                                  const uint16_t* b_row, uint32_t bits, uint32_t groups,
                                                  uint32_t lane, const void* xrow, uint32_t dt,
                                                  const uint16_t* eff_scale) {
     float acc = 0.f;
-    for (uint32_t gi = 0; gi < groups; ++gi) {
-        const float s = bf16_bits_to_f32(s_row[gi]);
-        const float b = bf16_bits_to_f32(b_row[gi]);
-        const uint32_t idx = gi * 64 + lane * 2;
-        const float q0 = (float)affine_value(row, idx, bits);
-        const float q1 = (float)affine_value(row, idx + 1, bits);
-        float x0 = load_act(xrow, idx, dt), x1 = load_act(xrow, idx + 1, dt);
-        if (eff_scale) {
-            x0 = __fmul_rn(x0, bf16_bits_to_f32(eff_scale[idx]));
-            x1 = __fmul_rn(x1, bf16_bits_to_f32(eff_scale[idx + 1]));
+    constexpr uint32_t kBatch = 8;
+    for (uint32_t g0 = 0; g0 < groups; g0 += kBatch) {
+        uint16_t sr[kBatch], br[kBatch];
+        uint32_t qr[kBatch], er[kBatch];
+        float x0r[kBatch], x1r[kBatch];
+#pragma unroll
+        for (uint32_t j = 0; j < kBatch; ++j) {
+            const uint32_t gi = g0 + j;
+            if (gi < groups) {
+                const uint32_t idx = gi * 64 + lane * 2;
+                sr[j] = s_row[gi];
+                br[j] = b_row[gi];
+                // both elements: one byte (int4) or two bytes (int8), the low one first
+                qr[j] = bits == 4 ? (uint32_t)row[idx >> 1] : (uint32_t)*(const uint16_t*)(row + idx);
+                if (dt == SHRIKE_DTYPE_FP32) {
+                    const float2 v = *(const float2*)((const float*)xrow + idx);
+                    x0r[j] = v.x; x1r[j] = v.y;
+                } else {
+                    const uint32_t v = *(const uint32_t*)((const uint16_t*)xrow + idx);
+                    if (dt == SHRIKE_DTYPE_FP16) {
+                        x0r[j] = f16_bits_to_f32(v & 0xffff); x1r[j] = f16_bits_to_f32(v >> 16);
+                    } else {
+                        x0r[j] = __uint_as_float(v << 16); x1r[j] = __uint_as_float(v & 0xffff0000u);
+                    }
+                }
+                er[j] = eff_scale ? *(const uint32_t*)(eff_scale + idx) : 0x3f803f80u;
+            }
         }
-        acc = __fmaf_rn(s, __fadd_rn(__fmul_rn(q0, x0), __fmul_rn(q1, x1)), acc);
-        acc = __fmaf_rn(b, __fadd_rn(x0, x1), acc);
+#pragma unroll
+        for (uint32_t j = 0; j < kBatch; ++j) {
+            const uint32_t gi = g0 + j;
+            if (gi < groups) {
+                const float sc = bf16_bits_to_f32(sr[j]);
+                const float bi = bf16_bits_to_f32(br[j]);
+                const float q0 = (float)(bits == 4 ? (qr[j] & 0xfu) : (qr[j] & 0xffu));
+                const float q1 = (float)(bits == 4 ? (qr[j] >> 4) : (qr[j] >> 8));
+                float x0 = x0r[j], x1 = x1r[j];
+                if (eff_scale) {
+                    x0 = __fmul_rn(x0, __uint_as_float(er[j] << 16));
+                    x1 = __fmul_rn(x1, __uint_as_float(er[j] & 0xffff0000u));
+                }
+                acc = __fmaf_rn(sc, __fadd_rn(__fmul_rn(q0, x0), __fmul_rn(q1, x1)), acc);
+                acc = __fmaf_rn(bi, __fadd_rn(x0, x1), acc);
+            }
+        }
     }
     return acc;
 }
