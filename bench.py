@@ -26,6 +26,7 @@ import numpy as np
 
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
+sys.path.insert(1, str(ROOT / "tests"))   # fixtures, the oracle bindings and the GPU harness (test infrastructure)
 
 SEED = 20240
 LAYERS = 40
@@ -65,7 +66,7 @@ def gate_weights(layer: int, d: int) -> np.ndarray:
 
 
 def input_tokens(T: int, d: int) -> np.ndarray:
-    from shrike_b200 import fixtures as fx
+    import fixtures as fx
     return fx.round_bf16(np.random.default_rng(SEED).normal(0, 1, (T, d)).astype(np.float32))
 
 
@@ -122,7 +123,7 @@ def cpu_reference_run(T: int, layers: int, steps: int, warmup: int, budget_s: fl
     int4 GEMV (oracle/_ref) under the restated expert FFN, router and combine (oracle/)."""
     sys.path.insert(0, str(ROOT / "tests"))
     import oracle_lib as O
-    from shrike_b200 import fixtures as fx
+    import fixtures as fx
 
     cfg = fx.qwen_config(max_tokens=16)
     kind = "reference" if O.use_reference_gemv(True) else "port"
@@ -177,7 +178,8 @@ class Workload:
 
     def __init__(self, T: int, layers: int, device_index: int, cfg=None):
         import torch
-        from shrike_b200 import capi, fixtures as fx
+        from shrike_b200 import capi
+        import fixtures as fx
         from shrike_b200.moe import ExpertCellArena, MoE, RouterOperands, expert_offsets, round_up
 
         self.torch = torch
@@ -380,7 +382,8 @@ def run_prefill(args, local_rank: int):
     """Ragged prefill through one Qwen-shape int4 layer: rows routed top-8 of 256 with a Zipf(1.1) prior on the
     expert ids, permuted by expert on the device, expert-grouped GEMM on the tcgen05 tensor cores."""
     import torch
-    from shrike_b200 import capi, fixtures as fx
+    from shrike_b200 import capi
+    import fixtures as fx
     from shrike_b200.moe import ExpertCellArena, MoE, RouterOperands, expert_offsets, round_up
     sys.path.insert(0, str(ROOT / "tests"))
     from gpu_harness import bf16_tensor
@@ -481,7 +484,7 @@ def run_gptoss(args, local_rank: int):
     shared expert) at --tokens rows (1 or 64): 8 independently seeded layers chained like the decode sweep, so
     every layer call streams its own cold expert blocks."""
     import torch
-    from shrike_b200 import fixtures as fx
+    import fixtures as fx
     T, L, K, W = args.tokens, min(args.layers, 8), args.steps, max(3, args.warmup)
     cfg = fx.gpt_oss_config(max_tokens=128)
     wl = Workload(T, L, local_rank, cfg)
@@ -523,7 +526,8 @@ def run_ep(args, rank: int, world: int, local_rank: int):
     dispatched and combined with all-to-all over NCCL. Weak scaling: N x 2064 rows per step."""
     import torch
     import torch.distributed as dist
-    from shrike_b200 import capi, fixtures as fx
+    from shrike_b200 import capi
+    import fixtures as fx
     from shrike_b200.ep import ExpertParallelLayer
     from shrike_b200.moe import RouterOperands, expert_offsets
 

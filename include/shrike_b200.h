@@ -15,7 +15,25 @@
  * `shrike_moe_status` after the stream is synchronised.
  *
  * Threading: one host thread per handle at a time (the reference's runner is
- * single-owner, RealForwardRunner.swift:95-101). One handle per GPU.
+ * single-owner, RealForwardRunner.swift:95-101). One handle per GPU; every
+ * encode call must be made with the handle's device current (checked:
+ * SHRIKE_EINVAL otherwise). shrike_moe_create leaves the caller's current
+ * device as it found it.
+ *
+ * Operand precision: the expert tiles multiply on the tensor cores with fp16
+ * operands and fp32 accumulation (the reference's matrix path does the same,
+ * tensorops.metal:106). bf16 and fp16 activations convert exactly; an fp32
+ * activation is rounded to fp16 (2^-11 relative) before the expert
+ * projections -- the router reads x at full precision. An activation whose
+ * magnitude exceeds 65504 is clamped to it and the call's status becomes
+ * SHRIKE_ERANGE (shrike_moe_status) instead of an infinity propagating.
+ *
+ * Alignment (checked at the call, SHRIKE_EINVAL otherwise): x / hidden given
+ * to a router or layer call 16 bytes when fp32, 8 bytes when 16-bit, with a row
+ * stride that is a multiple of 4 elements; router weights and the shared gate
+ * row 16 bytes; effective_scale 8 bytes; the other bf16 operand vectors, scales
+ * and biases 2 bytes; expert sub-tensor offsets and the shared block 16 bytes;
+ * cell stride 256 bytes.
  */
 #ifndef SHRIKE_B200_H
 #define SHRIKE_B200_H
@@ -58,7 +76,7 @@ typedef struct shrike_moe_config {
     uint32_t weight_bits;       /* 4 or 8 (routedWeightBits) */
     uint32_t group_size;        /* 64 (the reference's only value) or 32 */
     uint32_t meta_dtype;        /* dtype of scales and zero-point biases: BF16 (reference) or FP16 */
-    uint32_t act_dtype;         /* dtype of x, y, hidden: BF16, FP16 or FP32 */
+    uint32_t act_dtype;         /* dtype of x and hidden: BF16, FP16 or FP32 */
     uint32_t activation;        /* SHRIKE_ACT_* (siluActivation / clampedSwiGLU) */
     uint32_t expert_bias;       /* expertAdditiveBiases */
     uint32_t router_kind;       /* SHRIKE_ROUTER_* (sigmoidRouterScores) */
@@ -69,6 +87,11 @@ typedef struct shrike_moe_config {
     uint32_t shared_gated;      /* shared output is multiplied by sigmoid(gate . x) */
     uint32_t shared_f;          /* shared expert intermediate size */
     uint32_t max_tokens;        /* largest query_count of any call; sizes the workspace */
+    uint32_t y_dtype;           /* dtype of y: BF16, FP16 or FP32, independent of act_dtype. The sums are
+                                 * formed in fp32; FP32 here returns them unrounded (bf16 x in, fp32 y out is
+                                 * the configuration the 1e-3 relative-L2 parity bar is stated for), a 16-bit
+                                 * type rounds once on store as moe_phase2_finish does (moe.metal:889-893).
+                                 * hidden += y adds the value as stored in y and rounds to act_dtype. */
 } shrike_moe_config;
 
 /* Field-for-field `MoEExpertOffsets` (MoE.swift:4-39) = `ExpertOffsets`
@@ -120,12 +143,6 @@ const char* shrike_last_error(const shrike_moe* moe);
  * kernel's bounded wait gave up, or SHRIKE_EIO for a CUDA error
  * (the reference inspects commandBuffer.error, RealForwardRunner.swift:5360-5363). */
 int shrike_moe_status(shrike_moe* moe, void* stream);
-
-/* Diagnostics (the counterpart of SHRIKE_KERNEL_STATS, RealForwardRunner.swift:1305-1415):
- * when given a device buffer of 4 u64 per phase-1 block, every block records the
- * nanosecond timer at entry, after issuing its weight loads, after its last
- * multiply-accumulate and at exit. NULL switches it off. */
-int shrike_debug_set_trace(shrike_moe* moe, uint64_t* trace_device_buffer);
 
 /* CPUExpertFFN.Offsets (CPUExpertFFN.swift:34-61) / Model.routedExpertOffsets
  * (ModelExpertIO.swift:69-94): offsets and unpadded size of one block. */

@@ -29,7 +29,7 @@ class MoEConfig(C.Structure):
         ("router_kind", C.c_uint32), ("routed_scaling", C.c_float),
         ("router_weight_bits", C.c_uint32), ("round_route_weights_f16", C.c_uint32),
         ("has_shared", C.c_uint32), ("shared_gated", C.c_uint32), ("shared_f", C.c_uint32),
-        ("max_tokens", C.c_uint32),
+        ("max_tokens", C.c_uint32), ("y_dtype", C.c_uint32),
     ]
 
 
@@ -60,7 +60,6 @@ SIGNATURES = {
     "shrike_moe_destroy": (None, [_P]),
     "shrike_last_error": (C.c_char_p, [_P]),
     "shrike_moe_status": (_INT, [_P, _P]),
-    "shrike_debug_set_trace": (_INT, [_P, _P]),
     "shrike_expert_offsets_make": (_INT, [C.POINTER(MoEConfig), _INT, C.POINTER(ExpertOffsets), C.POINTER(_U64)]),
     "shrike_pool_create": (_INT, [_P, _U32, _U64, _U32, C.POINTER(_P)]),
     "shrike_pool_destroy": (None, [_P]),

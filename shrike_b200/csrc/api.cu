@@ -51,6 +51,7 @@ bool valid_config(const shrike_moe_config& c, std::string& why) {
     if (c.has_shared && (c.shared_f == 0 || c.shared_f % 64 != 0)) return bad("shared_f must be a multiple of 64");
     if (c.shared_gated && !c.has_shared) return bad("shared_gated needs has_shared");
     if (c.max_tokens == 0 || c.max_tokens > 65536) return bad("max_tokens must be 1..65536");
+    if (c.y_dtype > SHRIKE_DTYPE_FP32) return bad("y_dtype must be BF16, FP16 or FP32");
     return true;
 }
 
@@ -80,12 +81,46 @@ bool offsets_aligned(const shrike_expert_offsets& o) {
     return true;
 }
 
-uint32_t max_instances(const shrike_moe_config& c, uint32_t T) {
-    const uint32_t pairs = T * c.top_k;
-    uint32_t routed = c.num_experts + pairs / 8;
-    if (routed > pairs) routed = pairs;
-    return routed + (c.has_shared ? (T + 7) / 8 : 0);
+// Every encode call launches on the current device against this handle's workspace and pool.
+int check_device(shrike_moe* m) {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev != m->device)
+        return fail(m, SHRIKE_EINVAL, "the handle lives on device %d but device %d is current", m->device, dev);
+    return SHRIKE_OK;
 }
+
+bool aligned_to(const void* p, uintptr_t a) { return ((uintptr_t)p & (a - 1)) == 0; }
+
+// Makes `device` current for the scope and puts the caller's device back afterwards.
+struct DeviceGuard {
+    int prev = -1;
+    explicit DeviceGuard(int device) {
+        cudaGetDevice(&prev);
+        if (prev != device) cudaSetDevice(device);
+    }
+    ~DeviceGuard() { if (prev >= 0) cudaSetDevice(prev); }
+};
+
+}  // namespace
+
+namespace shrike {
+// What the router kernels' vector loads rely on; `why` receives the first violation.
+bool router_operands_aligned(const shrike_moe_config& c, const shrike_router_operands& o, const void* hidden,
+                             const char** why) {
+    auto bad = [&](const char* s) { *why = s; return false; };
+    if (!aligned_to(hidden, c.act_dtype == SHRIKE_DTYPE_FP32 ? 16 : 8))
+        return bad("hidden must be 16-byte aligned (fp32) or 8-byte aligned (16-bit activations)");
+    if (!aligned_to(o.weights, 16)) return bad("router weights must be 16-byte aligned");
+    if (o.shared_gate && !aligned_to(o.shared_gate, 16)) return bad("shared_gate must be 16-byte aligned");
+    if (o.effective_scale && !aligned_to(o.effective_scale, 8)) return bad("effective_scale must be 8-byte aligned");
+    if (!aligned_to(o.scales, 2) || !aligned_to(o.biases, 2) || !aligned_to(o.logit_bias, 2) ||
+        !aligned_to(o.per_expert_scale, 2))
+        return bad("scales, biases, logit_bias and per_expert_scale must be 2-byte aligned");
+    return true;
+}
+}  // namespace shrike
+
+namespace {
 
 template <typename P>
 cudaError_t dev_alloc(P** p, size_t bytes) {
@@ -93,8 +128,8 @@ cudaError_t dev_alloc(P** p, size_t bytes) {
 }
 
 void free_workspace(Workspace& w) {
-    void* ptrs[] = {w.route_pub, w.xs, w.chunk_inst, w.n_chunk_inst, w.done_counter, w.xsum, w.logits, w.xh, w.acts, w.acts_shared, w.sorted, w.inst, w.n_inst, w.status, w.block_hist,
-                    w.expert_offsets, w.expert_counts, w.slot_of_expert, w.partials, w.x_dev, w.y_dev,
+    void* ptrs[] = {w.yacc, w.xs, w.chunk_inst, w.n_chunk_inst, w.done_counter, w.xsum, w.logits, w.xh, w.acts, w.acts_shared, w.sorted, w.inst, w.n_inst, w.status, w.block_hist,
+                    w.expert_offsets, w.expert_counts, w.slot_of_expert, w.x_dev, w.y_dev,
                     w.ids_dev, w.w_dev, w.gate_dev, w.slots_dev, w.counts_dev};
     for (void* p : ptrs)
         if (p) cudaFree(p);
@@ -123,12 +158,51 @@ int fill_expert_args(shrike_moe* m, const shrike_pool* pool, const shrike_expert
         a.shared_block = (const uint8_t*)shared->block;
     }
     a.d = c.d; a.f = c.f; a.f_shared = c.has_shared ? c.shared_f : 0; a.top_k = c.top_k;
-    a.activation = c.activation; a.expert_bias = c.expert_bias; a.act_dtype = c.act_dtype;
+    a.activation = c.activation; a.expert_bias = c.expert_bias; a.act_dtype = c.act_dtype; a.y_dtype = c.y_dtype;
     a.inst = m->ws.inst; a.n_inst = m->ws.n_inst; a.sorted = m->ws.sorted; a.xh = m->ws.xh;
     a.xsum = m->ws.xsum;
-    a.acts = m->ws.acts; a.acts_shared = m->ws.acts_shared;
+    a.acts = m->ws.acts; a.acts_shared = m->ws.acts_shared; a.yacc = m->ws.yacc;
     a.route_w = weights; a.shared_gate = shared_gate; a.status = m->ws.status;
+#ifdef SHRIKE_TRACE
     a.trace = m->trace;
+#endif
+    return SHRIKE_OK;
+}
+
+
+// The prefill call with the status word of a streamed batch (moe.metal:36-39, 918-921): when io_status is
+// given and the word is neither READY nor 3, the routed experts are skipped and y is the shared term alone.
+int encode_prefill(shrike_moe* m, void* stream, const shrike_pool* pool,
+                   const shrike_expert_offsets* routed_offsets, const uint32_t* topk_indices,
+                   const uint32_t* resolved_slots, const float* routing_weights, const void* x,
+                   uint32_t query_count, const shrike_shared_expert* shared, const float* shared_gate,
+                   const uint32_t* io_status, void* y, void* hidden) {
+    if (!m) return SHRIKE_EINVAL;
+    if (!topk_indices || !resolved_slots || !routing_weights || !x || !y)
+        return fail(m, SHRIKE_EINVAL, "prefill: null operand");
+    if (query_count > m->cfg.max_tokens) return fail(m, SHRIKE_ERANGE, "query_count exceeds max_tokens");
+    if (m->cfg.max_tokens <= SHRIKE_MAX_DECODE_TOKENS)
+        return fail(m, SHRIKE_EINVAL, "handle was created for decode only (max_tokens <= %u)", SHRIKE_MAX_DECODE_TOKENS);
+    if (query_count == 0) return SHRIKE_OK;
+    ExpertArgs a;
+    int rc = fill_expert_args(m, pool, routed_offsets, shared, routing_weights, shared_gate, a);
+    if (rc) return rc;
+    if ((rc = check_device(m))) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    const uint32_t mi = max_instances(m->cfg, query_count);
+    // The expert-grouped GEMM runs on the tcgen05 tensor cores. Shapes whose K is not a multiple of 64 keep
+    // every expert on the 8-row warp-MMA tiles (the decode kernels); SHRIKE_PREFILL_PATH=mma in the
+    // environment of shrike_moe_create forces them for a handle (a test switch).
+    const bool warp_mma = m->force_warp_mma || !umma_supported(m->cfg);
+    CU(launch_prefill_plan(m, st, topk_indices, resolved_slots, x, query_count, m->cfg.has_shared != 0,
+                           pool->view.cells, warp_mma, io_status));
+    if (warp_mma) {
+        CU(launch_phase1(m, st, a, mi, false));
+        CU(launch_phase2_accumulate(m, st, a, mi));
+    } else {
+        CU(launch_umma_prefill(m, st, a, query_count, pool->view.cells));
+    }
+    CU(launch_prefill_combine(m, st, query_count, y, hidden));
     return SHRIKE_OK;
 }
 
@@ -167,18 +241,26 @@ int shrike_moe_create(const shrike_moe_config* config, int device, shrike_moe** 
         return fail(nullptr, SHRIKE_EIO, "no CUDA device: %s (this library has no CPU path)",
                     cudaGetErrorString(e));
     if (device < 0 || device >= count) return fail(nullptr, SHRIKE_ERANGE, "device %d out of range", device);
+    int caller_device = device;
+    cudaGetDevice(&caller_device);
     e = cudaSetDevice(device);
     if (e != cudaSuccess) return cuda_fail(nullptr, e, "cudaSetDevice");
+    // the caller's current device is put back on every way out
+    struct Restore { int dev; ~Restore() { cudaSetDevice(dev); } } restore{caller_device};
     shrike_moe* m = new (std::nothrow) shrike_moe();
     if (!m) return fail(nullptr, SHRIKE_ENOMEM, "host allocation failed");
     m->cfg = *config;
     m->device = device;
     cudaDeviceGetAttribute(&m->sm_count, cudaDevAttrMultiProcessorCount, device);
+    // switches for tests and diagnostics, read once here and never on the per-layer path
+    m->no_pdl = getenv("SHRIKE_NO_PDL") != nullptr;
+    const char* path = getenv("SHRIKE_PREFILL_PATH");
+    m->force_warp_mma = path && strcmp(path, "mma") == 0;
     const shrike_moe_config& c = m->cfg;
     Workspace& w = m->ws;
     const size_t T = c.max_tokens, K = c.top_k;
     w.max_inst = max_instances(c, c.max_tokens);
-    const size_t ab = act_bytes(c.act_dtype);
+    const size_t ab = act_bytes(c.act_dtype), yb = act_bytes(c.y_dtype);
     bool ok = true;
     auto A = [&](auto** p, size_t bytes) { if (ok && dev_alloc(p, bytes) != cudaSuccess) ok = false; };
     A(&w.logits, T * c.num_experts * 4);
@@ -195,13 +277,12 @@ int shrike_moe_create(const shrike_moe_config* config, int device, shrike_moe** 
     A(&w.expert_offsets, c.num_experts * 4);
     A(&w.expert_counts, c.num_experts * 4);
     A(&w.slot_of_expert, c.num_experts * 4);
-    A(&w.partials, T > SHRIKE_MAX_DECODE_TOKENS ? (T * K + (c.has_shared ? T : 0)) * c.d * 4 : 0);
+    A(&w.yacc, T > SHRIKE_MAX_DECODE_TOKENS ? T * c.d * 4 : 0);
     A(&w.chunk_inst, T > SHRIKE_MAX_DECODE_TOKENS ? umma_max_chunk_instances(c, c.max_tokens) * umma_chunk_instance_bytes() : 0);
     A(&w.n_chunk_inst, 8);
-    A(&w.route_pub, 128);
     A(&w.xs, T > SHRIKE_MAX_DECODE_TOKENS ? T * K * c.d * 2 : 0);
     A(&w.x_dev, T * c.d * ab);
-    A(&w.y_dev, T * c.d * ab);
+    A(&w.y_dev, T * c.d * yb);
     A(&w.ids_dev, T * K * 4);
     A(&w.w_dev, T * K * 4);
     A(&w.gate_dev, T * 4);
@@ -235,7 +316,7 @@ int shrike_moe_create(const shrike_moe_config* config, int device, shrike_moe** 
 
 void shrike_moe_destroy(shrike_moe* moe) {
     if (!moe) return;
-    cudaSetDevice(moe->device);
+    DeviceGuard guard(moe->device);
     free_workspace(moe->ws);
     if (moe->residency) cudaFree(moe->residency);
     delete moe;
@@ -249,16 +330,20 @@ int shrike_moe_status(shrike_moe* m, void* stream) {
     if (st != kStatusOk) {
         cudaMemset(m->ws.status, 0, 4);
         if (st == kStatusWaitTimeout) return fail(m, SHRIKE_ETIMEDOUT, "a device-side wait gave up");
+        if (st == kStatusOperandRange)
+            return fail(m, SHRIKE_ERANGE, "an activation beyond the fp16 operand range (|x| > 65504) was clamped");
         return fail(m, SHRIKE_ERANGE, "a kernel met a slot id outside the pool");
     }
     return SHRIKE_OK;
 }
 
+#ifdef SHRIKE_TRACE
 int shrike_debug_set_trace(shrike_moe* m, uint64_t* trace_device_buffer) {
     if (!m) return SHRIKE_EINVAL;
     m->trace = trace_device_buffer;
     return SHRIKE_OK;
 }
+#endif
 
 // ---- pool -------------------------------------------------------------------
 
@@ -270,7 +355,7 @@ int shrike_pool_create(shrike_moe* m, uint32_t cells, uint64_t cell_stride, uint
         return fail(m, SHRIKE_EINVAL, "cells must be > 0 and chunks 1..8");
     if (cell_stride == 0 || cell_stride % 256 != 0)
         return fail(m, SHRIKE_EINVAL, "cell_stride must be a positive multiple of 256 bytes");
-    CU(cudaSetDevice(m->device));
+    DeviceGuard guard(m->device);
     shrike_pool* p = new (std::nothrow) shrike_pool();
     if (!p) return fail(m, SHRIKE_ENOMEM, "host allocation failed");
     memset(p, 0, sizeof *p);
@@ -300,7 +385,7 @@ int shrike_pool_create(shrike_moe* m, uint32_t cells, uint64_t cell_stride, uint
 
 void shrike_pool_destroy(shrike_pool* pool) {
     if (!pool) return;
-    cudaSetDevice(pool->owner->device);
+    DeviceGuard guard(pool->owner->device);
     for (uint32_t i = 0; i < pool->chunks; ++i)
         if (pool->chunk[i]) cudaFree(pool->chunk[i]);
     delete pool;
@@ -353,7 +438,7 @@ int shrike_pool_fill_synthetic(shrike_moe* m, shrike_pool* pool, uint32_t first_
 
 int shrike_residency_create(shrike_moe* m, uint32_t layers, uint64_t** table_out) {
     if (!m || layers == 0) return SHRIKE_EINVAL;
-    CU(cudaSetDevice(m->device));
+    DeviceGuard guard(m->device);
     if (m->residency) { cudaFree(m->residency); m->residency = nullptr; }
     const size_t n = (size_t)layers * m->cfg.num_experts;
     cudaError_t e = cudaMalloc((void**)&m->residency, n * 8);
@@ -398,22 +483,34 @@ int shrike_residency_set_layer_identity(shrike_moe* m, uint32_t layer, uint32_t 
 
 // ---- the path -------------------------------------------------------------------
 
+// Argument checks shared by the router entry points: operands, counts, stride, alignment.
+static int check_router_call(shrike_moe* m, const shrike_router_operands* ops, const void* hidden,
+                             uint32_t query_count, uint32_t limit, uint32_t hidden_stride_elements,
+                             bool need_gate_out, const void* out_shared_gate) {
+    const shrike_moe_config& c = m->cfg;
+    if (!ops || !ops->weights || !hidden) return fail(m, SHRIKE_EINVAL, "router: null operand");
+    if (c.router_weight_bits != 0 && (!ops->scales || !ops->biases))
+        return fail(m, SHRIKE_EINVAL, "router: affine weights need scales and biases");
+    if (query_count > limit) return fail(m, SHRIKE_ERANGE, "query_count %u exceeds %u", query_count, limit);
+    if (hidden_stride_elements < c.d || hidden_stride_elements % 4 != 0)
+        return fail(m, SHRIKE_EINVAL, "hidden stride must be >= d and a multiple of 4 elements");
+    if (c.shared_gated && (!ops->shared_gate || (need_gate_out && !out_shared_gate)))
+        return fail(m, SHRIKE_EINVAL, "router: a shared_gated handle needs shared_gate and out_shared_gate");
+    const char* why = nullptr;
+    if (!router_operands_aligned(c, *ops, hidden, &why)) return fail(m, SHRIKE_EINVAL, "router: %s", why);
+    return SHRIKE_OK;
+}
+
 int shrike_encode_router(shrike_moe* m, void* stream, const shrike_router_operands* ops, const void* hidden,
                          uint32_t query_count, uint32_t hidden_stride_elements, uint32_t* out_indices,
                          float* out_weights, float* out_shared_gate) {
     if (!m) return SHRIKE_EINVAL;
     if (query_count == 0) return SHRIKE_OK;
-    if (!ops || !ops->weights || !hidden || !out_indices || !out_weights)
-        return fail(m, SHRIKE_EINVAL, "router: null operand");
-    const shrike_moe_config& c = m->cfg;
-    if (c.router_weight_bits != 0 && (!ops->scales || !ops->biases))
-        return fail(m, SHRIKE_EINVAL, "router: affine weights need scales and biases");
-    if (query_count > c.max_tokens) return fail(m, SHRIKE_ERANGE, "query_count %u exceeds max_tokens %u", query_count, c.max_tokens);
-    if (hidden_stride_elements < c.d || hidden_stride_elements % 4 != 0)
-        return fail(m, SHRIKE_EINVAL, "hidden stride must be >= d and a multiple of 4 elements");
-    if (c.shared_gated && (!ops->shared_gate || !out_shared_gate))
-        return fail(m, SHRIKE_EINVAL, "router: a shared_gated handle needs shared_gate and out_shared_gate");
-    if (query_count == 0) return SHRIKE_OK;
+    if (!out_indices || !out_weights) return fail(m, SHRIKE_EINVAL, "router: null operand");
+    int rc = check_router_call(m, ops, hidden, query_count, m->cfg.max_tokens, hidden_stride_elements, true,
+                               out_shared_gate);
+    if (rc) return rc;
+    if ((rc = check_device(m))) return rc;
     CU(launch_router(m, (cudaStream_t)stream, *ops, hidden, query_count, hidden_stride_elements, out_indices,
                      out_weights, out_shared_gate));
     return SHRIKE_OK;
@@ -427,6 +524,7 @@ int shrike_encode_residency_classification(shrike_moe* m, void* stream, const ui
     if (!topk_indices || !residency_table_row || !resolved_slots)
         return fail(m, SHRIKE_EINVAL, "classification: null operand");
     if (query_count > m->cfg.max_tokens) return fail(m, SHRIKE_ERANGE, "query_count exceeds max_tokens");
+    if (int rc = check_device(m)) return rc;
     if (query_count == 0) {
         if (counts) CU(cudaMemsetAsync(counts, 0, 8, (cudaStream_t)stream));
         return SHRIKE_OK;
@@ -444,6 +542,7 @@ int shrike_encode_decode_plan(shrike_moe* m, void* stream, const shrike_pool* po
     if (query_count == 0 || query_count > SHRIKE_MAX_DECODE_TOKENS || query_count > m->cfg.max_tokens)
         return fail(m, SHRIKE_ERANGE, "decode handles 1..%u rows (max_tokens %u); use the prefill call",
                     SHRIKE_MAX_DECODE_TOKENS, m->cfg.max_tokens);
+    if (int rc = check_device(m)) return rc;
     CU(launch_decode_plan(m, (cudaStream_t)stream, resolved_slots, x, query_count, io_status,
                           m->cfg.has_shared != 0, pool->view.cells));
     return SHRIKE_OK;
@@ -458,6 +557,7 @@ int shrike_encode_phase1(shrike_moe* m, void* stream, const shrike_pool* pool,
     ExpertArgs a;
     int rc = fill_expert_args(m, pool, routed_offsets, shared, nullptr, nullptr, a, false);
     if (rc) return rc;
+    if ((rc = check_device(m))) return rc;
     CU(launch_phase1(m, (cudaStream_t)stream, a, max_instances(m->cfg, query_count), false));
     return SHRIKE_OK;
 }
@@ -473,6 +573,7 @@ int shrike_encode_phase2_reduce(shrike_moe* m, void* stream, const shrike_pool* 
     ExpertArgs a;
     int rc = fill_expert_args(m, pool, routed_offsets, shared, routing_weights, shared_gate, a, true);
     if (rc) return rc;
+    if ((rc = check_device(m))) return rc;
     CU(launch_phase2(m, (cudaStream_t)stream, a, query_count, max_instances(m->cfg, query_count), y, hidden, false));
     return SHRIKE_OK;
 }
@@ -500,20 +601,15 @@ int shrike_encode_route_decode(shrike_moe* m, void* stream, const shrike_router_
                                float* out_shared_gate, uint32_t* out_resolved_slots, uint32_t* out_counts) {
     if (!m) return SHRIKE_EINVAL;
     if (query_count == 0) return SHRIKE_OK;
-    if (!ops || !ops->weights || !hidden || !out_indices || !out_weights || !residency_table_row || !pool)
+    if (!out_indices || !out_weights || !residency_table_row || !pool)
         return fail(m, SHRIKE_EINVAL, "route_decode: null operand");
-    const shrike_moe_config& c = m->cfg;
-    if (c.router_weight_bits != 0 && (!ops->scales || !ops->biases))
-        return fail(m, SHRIKE_EINVAL, "router: affine weights need scales and biases");
-    if (query_count > SHRIKE_MAX_DECODE_TOKENS || query_count > c.max_tokens)
-        return fail(m, SHRIKE_ERANGE, "route_decode handles at most %u rows", SHRIKE_MAX_DECODE_TOKENS);
-    if (hidden_stride_elements < c.d || hidden_stride_elements % 4 != 0)
-        return fail(m, SHRIKE_EINVAL, "hidden stride must be >= d and a multiple of 4 elements");
-    if (c.shared_gated && (!ops->shared_gate || !out_shared_gate))
-        return fail(m, SHRIKE_EINVAL, "router: a shared_gated handle needs shared_gate and out_shared_gate");
+    const uint32_t limit = m->cfg.max_tokens < SHRIKE_MAX_DECODE_TOKENS ? m->cfg.max_tokens : SHRIKE_MAX_DECODE_TOKENS;
+    int rc = check_router_call(m, ops, hidden, query_count, limit, hidden_stride_elements, true, out_shared_gate);
+    if (rc) return rc;
+    if ((rc = check_device(m))) return rc;
     CU(launch_route_fused(m, (cudaStream_t)stream, *ops, hidden, query_count, hidden_stride_elements,
                           residency_table_row, pool->view.cells, io_status, out_indices, out_weights,
-                          out_shared_gate, out_resolved_slots, out_counts, true));
+                          out_shared_gate, out_resolved_slots, out_counts, !m->no_pdl));
     return SHRIKE_OK;
 }
 
@@ -532,55 +628,26 @@ int shrike_encode_decode_layer(shrike_moe* m, void* stream, const shrike_pool* p
     float* gate = m->cfg.shared_gated ? w.gate_dev : nullptr;
     // A few dozen rows on a handle that owns the prefill operands: the expert-grouped tensor-core call reads
     // every expert once for all its rows, where the 8-row tiles read it once per 8 (gpt-oss shape, 64 rows:
-    // 279 us per layer against 740). The status word of a streamed batch is only honoured by the tiles.
-    if (query_count > 16 && !io_status && w.xs && umma_supported(m->cfg)) {
+    // 279 us per layer against 740).
+    if (query_count > 16 && w.xs && umma_supported(m->cfg) && !m->force_warp_mma) {
         int rcg = shrike_encode_router(m, stream, router, x, query_count, m->cfg.d, ids, wt, gate);
         if (rcg) return rcg;
         rcg = shrike_encode_residency_classification(m, stream, ids, residency_table_row, query_count, w.slots_dev,
                                                      nullptr, nullptr, nullptr);
         if (rcg) return rcg;
-        return shrike_encode_moe_prefill(m, stream, pool, routed_offsets, ids, w.slots_dev, wt, x, query_count, shared,
-                                         gate, y, hidden);
+        return encode_prefill(m, stream, pool, routed_offsets, ids, w.slots_dev, wt, x, query_count, shared, gate,
+                              io_status, y, hidden);
     }
-    // One row: the route launch stops after the logits and the fp16 operand copy, and every block of
-    // phase 1 and phase 2 repeats the selection itself -- no block waits for another to publish picks,
-    // cells and work lists. More rows keep the route kernel's tail (selection, lookup, grouping).
-    const bool self_route = query_count == 1;
-    int rc;
-    if (self_route) {
-        if (!router || !router->weights || !residency_table_row || !pool)
-            return fail(m, SHRIKE_EINVAL, "decode_layer: null operand");
-        const shrike_moe_config& c = m->cfg;
-        if (c.router_weight_bits != 0 && (!router->scales || !router->biases))
-            return fail(m, SHRIKE_EINVAL, "router: affine weights need scales and biases");
-        if (c.shared_gated && !router->shared_gate)
-            return fail(m, SHRIKE_EINVAL, "router: a shared_gated handle needs shared_gate");
-        CU(launch_route_fused(m, (cudaStream_t)stream, *router, x, 1, c.d, residency_table_row, pool->view.cells,
-                              io_status, ids, wt, gate, w.slots_dev, nullptr, getenv("SHRIKE_NO_PDL") == nullptr, true));
-    } else {
-        rc = shrike_encode_route_decode(m, stream, router, residency_table_row, pool, x, query_count, m->cfg.d,
+    int rc = shrike_encode_route_decode(m, stream, router, residency_table_row, pool, x, query_count, m->cfg.d,
                                         io_status, ids, wt, gate, w.slots_dev, nullptr);
-        if (rc) return rc;
-    }
+    if (rc) return rc;
     ExpertArgs a;
     rc = fill_expert_args(m, pool, routed_offsets, shared, wt, gate, a);
     if (rc) return rc;
-    if (self_route) {
-        const shrike_moe_config& c = m->cfg;
-        SelfRoute& r = a.sr;
-        r.logits = w.logits; r.logit_bias = router->logit_bias; r.per_expert_scale = router->per_expert_scale;
-        r.table = residency_table_row; r.io_status = io_status;
-        r.out_ids = ids; r.out_w = wt; r.out_slots = w.slots_dev; r.out_counts = nullptr;
-        r.ne = c.num_experts; r.top_k = c.top_k; r.sigmoid_scores = c.router_kind == SHRIKE_ROUTER_SIGMOID;
-        r.round_f16 = c.round_route_weights_f16; r.pool_cells = pool->view.cells; r.scaling = c.routed_scaling;
-        r.pub = w.route_pub;
-        r.enabled = 1; r.publish = 0;
-    }
     const uint32_t mi = max_instances(m->cfg, query_count);
     // phase 1 and phase 2 may start before their predecessor has drained
-    static const bool pdl = getenv("SHRIKE_NO_PDL") == nullptr;   // diagnostics: plain stream order instead
-    CU(launch_phase1(m, (cudaStream_t)stream, a, mi, pdl));
-    CU(launch_phase2(m, (cudaStream_t)stream, a, query_count, mi, y, hidden, pdl));
+    CU(launch_phase1(m, (cudaStream_t)stream, a, mi, !m->no_pdl));
+    CU(launch_phase2(m, (cudaStream_t)stream, a, query_count, mi, y, hidden, !m->no_pdl));
     return SHRIKE_OK;
 }
 
@@ -589,34 +656,8 @@ int shrike_encode_moe_prefill(shrike_moe* m, void* stream, const shrike_pool* po
                               const uint32_t* resolved_slots, const float* routing_weights, const void* x,
                               uint32_t query_count, const shrike_shared_expert* shared,
                               const float* shared_gate, void* y, void* hidden) {
-    if (!m) return SHRIKE_EINVAL;
-    if (!topk_indices || !resolved_slots || !routing_weights || !x || !y)
-        return fail(m, SHRIKE_EINVAL, "prefill: null operand");
-    if (query_count > m->cfg.max_tokens) return fail(m, SHRIKE_ERANGE, "query_count exceeds max_tokens");
-    if (m->cfg.max_tokens <= SHRIKE_MAX_DECODE_TOKENS)
-        return fail(m, SHRIKE_EINVAL, "handle was created for decode only (max_tokens <= %u)", SHRIKE_MAX_DECODE_TOKENS);
-    if (query_count == 0) return SHRIKE_OK;
-    ExpertArgs a;
-    int rc = fill_expert_args(m, pool, routed_offsets, shared, routing_weights, shared_gate, a);
-    if (rc) return rc;
-    cudaStream_t st = (cudaStream_t)stream;
-    const uint32_t mi = max_instances(m->cfg, query_count);
-    // The default runs the expert-grouped GEMM on the tcgen05 tensor cores. Shapes whose K is not a
-    // multiple of 64, and SHRIKE_PREFILL_PATH=mma, keep every expert on the 8-row warp-MMA tiles (the
-    // decode kernels).
-    const char* path = getenv("SHRIKE_PREFILL_PATH");
-    const bool warp_mma = (path && strcmp(path, "mma") == 0) || !umma_supported(m->cfg);
-    CU(launch_prefill_plan(m, st, topk_indices, resolved_slots, x, query_count, m->cfg.has_shared != 0,
-                           pool->view.cells, warp_mma));
-    float* partial_shared = m->ws.partials + (size_t)m->cfg.max_tokens * m->cfg.top_k * m->cfg.d;
-    if (warp_mma) {
-        CU(launch_phase1(m, st, a, mi, false));
-        CU(launch_phase2_partials(m, st, a, mi, m->ws.partials, partial_shared));
-    } else {
-        CU(launch_umma_prefill(m, st, a, query_count, pool->view.cells, m->ws.partials, partial_shared));
-    }
-    CU(launch_prefill_combine(m, st, routing_weights, shared_gate, resolved_slots, query_count, y, hidden));
-    return SHRIKE_OK;
+    return encode_prefill(m, stream, pool, routed_offsets, topk_indices, resolved_slots, routing_weights, x,
+                          query_count, shared, shared_gate, nullptr, y, hidden);
 }
 
 int shrike_encode_group_pairs(shrike_moe* m, void* stream, const uint32_t* topk_indices,

@@ -14,7 +14,7 @@ namespace shrike {
 // ---- status word ------------------------------------------------------------
 // Kernels never trap or spin without bound: a wait that runs out records a
 // code here and the kernel carries on to its exit.
-enum : uint32_t { kStatusOk = 0, kStatusWaitTimeout = 1, kStatusBadIndex = 2 };
+enum : uint32_t { kStatusOk = 0, kStatusWaitTimeout = 1, kStatusBadIndex = 2, kStatusOperandRange = 3 };
 
 __device__ __forceinline__ void report_status(uint32_t* status, uint32_t code) {
     if (status) atomicMax(status, code);
@@ -145,11 +145,13 @@ __device__ __forceinline__ void cp_async_wait() {
     asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
+#ifdef SHRIKE_TRACE   // debug builds only: per-block timestamps
 __device__ __forceinline__ uint64_t globaltimer_ns() {
     uint64_t t;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
     return t;
 }
+#endif
 
 // ---- programmatic dependent launch ---------------------------------------
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
@@ -189,11 +191,27 @@ __host__ __device__ __forceinline__ uint32_t perm_index(uint32_t i, bool int4) {
 // Converts the aligned block of 8 activations `blk` of a row to the fp16
 // operand layout and returns the sum of the 8 rounded values. Thread-to-block
 // assignment is up to the caller; group sums are formed with xprep_group_sum.
+// The tiles take fp16 operands: an activation whose magnitude exceeds the largest fp16 value is
+// clamped to it and reported through the status word (kStatusOperandRange) instead of turning
+// into an infinity.
+constexpr float kHalfMax = 65504.0f;
+
 __device__ __forceinline__ float xprep_block8(const void* xrow, uint32_t blk, uint32_t dt, bool int4,
-                                              uint16_t* xh_row) {
+                                              uint16_t* xh_row, uint32_t* status) {
     float v[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) v[j] = load_act(xrow, (size_t)blk * 8 + j, dt);
+    if (dt != SHRIKE_DTYPE_FP16) {
+        bool over = false;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            if (fabsf(v[j]) > kHalfMax) {   // false for NaN, which passes through
+                over = true;
+                v[j] = copysignf(kHalfMax, v[j]);
+            }
+        }
+        if (over) report_status(status, kStatusOperandRange);
+    }
     __half h[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) h[j] = __float2half_rn(v[j]);
@@ -216,14 +234,15 @@ __device__ __forceinline__ float xprep_block8(const void* xrow, uint32_t blk, ui
 // shuffles. Every lane of a warp must call this together.
 __device__ __forceinline__ void xprep_item(const void* x, size_t row_stride_bytes, uint32_t d, uint32_t group,
                                            uint32_t dt, bool int4, uint32_t item, bool valid, uint16_t* xh,
-                                           float* xsum) {
+                                           float* xsum, uint32_t* status) {
     const uint32_t per_row = d / 8;
     float sum = 0.f;
     uint32_t row = 0, blk = 0;
     if (valid) {
         row = item / per_row;
         blk = item - row * per_row;
-        sum = xprep_block8((const uint8_t*)x + (size_t)row * row_stride_bytes, blk, dt, int4, xh + (size_t)row * d);
+        sum = xprep_block8((const uint8_t*)x + (size_t)row * row_stride_bytes, blk, dt, int4, xh + (size_t)row * d,
+                           status);
     }
     const uint32_t lanes = group / 8;  // 8 or 4 lanes per group
     for (uint32_t o = 1; o < lanes; o <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);

@@ -21,7 +21,6 @@
 // the tile's scales and zero-point biases are staged in shared memory by the
 // TMA engine (1-D bulk copies completing on an mbarrier).
 #include "internal.h"
-#include "select.cuh"
 
 namespace shrike {
 
@@ -230,41 +229,12 @@ __global__ void __launch_bounds__(kP1Warps * 32) phase1_kernel(const ExpertArgs 
     using Q = QT<BITS, GROUP>;
     extern __shared__ __align__(16) uint8_t smem[];
     const uint32_t ii = blockIdx.y;
-    const uint64_t t_start = a.trace ? globaltimer_ns() : 0;
-    // Self-routing: the residency row does not depend on the launch before this one (the host publishes
-    // it ahead of the layer), so it is staged while that launch is still running.
-    __shared__ SelfRouteSmem srs;
-    __shared__ uint64_t table_sm[SHRIKE_MAX_EXPERTS];
-    if (a.sr.enabled)
-        for (uint32_t e = threadIdx.x; e < a.sr.ne; e += blockDim.x) table_sm[e] = a.sr.table[e];
-    // the work lists (or, self-routing, the logits) come from the kernel launched just before this one
+    // the work lists come from the kernel launched just before this one
     pdl_wait();
-    Instance in;
-    if (a.sr.enabled) {
-        // one decode row: instance ii is the ii-th pick, the one after the picks the shared expert
-        SelfRoute r = a.sr;
-        r.publish = blockIdx.x == 0 && blockIdx.y == 0;
-        self_route_block(r, srs, a.status, table_sm);
-        pdl_launch_dependents();
-        in.first = 0; in.count = 1;
-        uint32_t pair = 0;
-        if (ii < srs.n_routed) {
-            pair = srs.order[ii];
-            in.kind = 0; in.slot = srs.slot[pair];
-        } else if (ii == srs.n_routed && a.shared_block) {
-            in.kind = 1; in.slot = 0;
-        } else {
-            return;
-        }
-#pragma unroll
-        for (int q = 0; q < 8; ++q) in.pair[q] = pair;
-    } else {
-        const uint32_t n_inst = *a.n_inst;
-        in = load_instance(a.inst + ii);
-        if (ii >= n_inst) return;
-        pdl_launch_dependents();
-    }
-    const uint64_t t_inst = a.trace ? globaltimer_ns() : 0;
+    const uint32_t n_inst = *a.n_inst;
+    const Instance in = load_instance(a.inst + ii);
+    if (ii >= n_inst) return;
+    pdl_launch_dependents();
     const bool shared = in.kind == 1;
     const uint32_t F = shared ? a.f_shared : a.f;
     const uint32_t f0 = blockIdx.x * 16;
@@ -285,7 +255,6 @@ __global__ void __launch_bounds__(kP1Warps * 32) phase1_kernel(const ExpertArgs 
     }
     uint32_t raw[Q::kBatch][2][2][Q::kWords];
     load_batch<BITS, GROUP, 2>(wrow, warp, kP1Warps, G, raw);
-    const uint64_t t_loads = a.trace ? globaltimer_ns() : 0;
 
     // shared memory: [gate s][gate b][up s][up b] (16*G u16 each) | ab gate, ab up (16 u16 each)
     // | mbarrier | cross-warp reduction buffer
@@ -315,7 +284,6 @@ __global__ void __launch_bounds__(kP1Warps * 32) phase1_kernel(const ExpertArgs 
         }
     }
     __syncthreads();  // the barrier word is initialised before anyone polls it
-    const uint64_t t_sync = a.trace ? globaltimer_ns() : 0;
 
     // B operand: column n = g is row `n` of this instance (columns past the
     // count repeat row 0; their results are never stored).
@@ -334,7 +302,6 @@ __global__ void __launch_bounds__(kP1Warps * 32) phase1_kernel(const ExpertArgs 
     tile_accumulate<BITS, GROUP, META, 2, true>(wrow, s_sm, b_sm, xrow, G, warp, G, kP1Warps, g, t, bar, 0,
                                                 a.status, tot, true, raw, xs0, xs1);
 
-    const uint64_t t_acc = a.trace ? globaltimer_ns() : 0;
     // split-K reduction across the warps, fixed order
 #pragma unroll
     for (int mat = 0; mat < 2; ++mat) {
@@ -345,7 +312,6 @@ __global__ void __launch_bounds__(kP1Warps * 32) phase1_kernel(const ExpertArgs 
         r[(g + 8) * 8 + 2 * t + 1] = tot[mat][3];
     }
     __syncthreads();
-    const uint64_t t_red = a.trace ? globaltimer_ns() : 0;
     if (tid < 128) {
         const uint32_t row = tid >> 3, c = tid & 7;
         if (c < in.count) {
@@ -364,11 +330,6 @@ __global__ void __launch_bounds__(kP1Warps * 32) phase1_kernel(const ExpertArgs 
             uint16_t* dst = shared ? a.acts_shared : a.acts;
             dst[(size_t)pick(in.pair, c) * F + fi] = __half_as_ushort(__float2half_rn(act));
         }
-    }
-    if (a.trace && tid == 0) {
-        uint64_t* tr = a.trace + 8 * (size_t)(128 + blockIdx.y * gridDim.x + blockIdx.x);   // after the route kernel's blocks
-        tr[0] = t_start; tr[1] = t_loads; tr[2] = t_acc; tr[3] = globaltimer_ns();
-        tr[4] = t_inst; tr[5] = t_sync; tr[6] = t_red; tr[7] = 0;
     }
 }
 
@@ -402,8 +363,6 @@ __global__ void __launch_bounds__(kP2Warps * 32) phase2_kernel(const ExpertArgs 
     float* yacc_all = (float*)(smem + nw * per_warp);
     float* yacc = yacc_all + (size_t)warp * T * 16;
 
-    const uint64_t t2_start = a.trace ? globaltimer_ns() : 0;
-    uint64_t t2_wait = 0;
     for (uint32_t i = lane; i < T * 16; i += 32) yacc[i] = 0.f;
     if (lane == 0) {
         mbar_init(bar, 1);
@@ -411,34 +370,15 @@ __global__ void __launch_bounds__(kP2Warps * 32) phase2_kernel(const ExpertArgs 
     }
     __syncwarp();
 
-        __shared__ SelfRouteSmem srs;
+    // The work lists were complete before phase 1 began (its own dependency wait saw them), so they can
+    // be read, and this warp's first weights fetched, while phase 1 is still running.
     bool first = true;
-    if (a.sr.enabled) {
-        // phase 1's publishing block left the picks, cells and weights: they are visible once phase 1 is
-        pdl_wait();
-        pdl_launch_dependents();
-        first = false;
-        if (a.trace) t2_wait = globaltimer_ns();
-        self_route_read(a.sr, srs);
-    }
-    const uint64_t t2_pub = a.trace ? globaltimer_ns() : 0;
-    uint64_t t2_loads = 0, t2_acc = 0;
-    const uint32_t n_inst = a.sr.enabled ? srs.n_routed + (a.shared_block ? 1u : 0u) : *a.n_inst;
+    const uint32_t n_inst = *a.n_inst;
     const uint32_t units = n_inst * ksplit;
     uint32_t parity = 0;
     for (uint32_t u = warp; u < units; u += nw) {
         const uint32_t ii = u / ksplit, ks = u % ksplit;
-        Instance in;
-        if (a.sr.enabled) {
-            in.first = 0; in.count = 1;
-            in.kind = ii < srs.n_routed ? 0u : 1u;
-            const uint32_t pair = in.kind == 0 ? srs.order[ii] : 0u;
-            in.slot = in.kind == 0 ? srs.slot[pair] : 0u;
-#pragma unroll
-            for (int q = 0; q < 8; ++q) in.pair[q] = pair;
-        } else {
-            in = load_instance(a.inst + ii);
-        }
+        const Instance in = load_instance(a.inst + ii);
         const bool shared = in.kind == 1;
         const uint32_t F = shared ? a.f_shared : a.f;
         const uint32_t G = F / GROUP;
@@ -455,7 +395,6 @@ __global__ void __launch_bounds__(kP2Warps * 32) phase2_kernel(const ExpertArgs 
         wrow[0][1] = base + off.w[2] + (size_t)(d0 + g + 8) * row_bytes + toff;
         uint32_t raw[Q::kBatch][1][2][Q::kWords];
         load_batch<BITS, GROUP, 1>(wrow, gbeg, 1, gend, raw);
-        if (a.trace && t2_loads == 0) t2_loads = globaltimer_ns();
 
         if (lane == 0) {
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -470,7 +409,6 @@ __global__ void __launch_bounds__(kP2Warps * 32) phase2_kernel(const ExpertArgs 
             pdl_wait();  // the activations of phase 1
             pdl_launch_dependents();
             first = false;
-            if (a.trace) t2_wait = globaltimer_ns();
         }
 
         const uint32_t bpair = pick(in.pair, g < in.count ? g : 0);
@@ -481,7 +419,6 @@ __global__ void __launch_bounds__(kP2Warps * 32) phase2_kernel(const ExpertArgs 
         tile_accumulate<BITS, GROUP, META, 1, true>(wrow, s_sm, b_sm, brow, G, gbeg, gend, 1, g, t, bar, parity,
                                               a.status, tot, true, raw);
         parity ^= 1;
-        if (a.trace && t2_acc == 0) t2_acc = globaltimer_ns();
 
         const float ab0 = add_bias ? bf16_bits_to_f32(ab_sm[g]) : 0.f;
         const float ab1 = add_bias ? bf16_bits_to_f32(ab_sm[g + 8]) : 0.f;
@@ -497,7 +434,7 @@ __global__ void __launch_bounds__(kP2Warps * 32) phase2_kernel(const ExpertArgs 
                     w = a.shared_gate ? a.shared_gate[token] : 1.0f;
                 } else {
                     token = pair / a.top_k;
-                    w = a.sr.enabled ? srs.w[pair] : a.route_w[pair];
+                    w = a.route_w[pair];
                 }
                 yacc[token * 16 + g] += w * (tot[0][c] + ab0);
                 yacc[token * 16 + g + 8] += w * (tot[0][2 + c] + ab1);
@@ -514,36 +451,28 @@ __global__ void __launch_bounds__(kP2Warps * 32) phase2_kernel(const ExpertArgs 
     float h_first = 0.f;
     if (hidden && tid < T * 16) h_first = load_act(hidden, (size_t)(tid >> 4) * a.d + d0 + (tid & 15), a.act_dtype);
     __syncthreads();
-    const uint64_t t2_sync = a.trace ? globaltimer_ns() : 0;
     // y = sum over warps; hidden += y (moe_phase2_finish, moe.metal:889-893)
     for (uint32_t i = tid; i < T * 16; i += nw * 32) {
         const uint32_t token = i >> 4, row = i & 15;
         float acc = 0.f;
         for (uint32_t w = 0; w < nw; ++w) acc += yacc_all[(size_t)w * T * 16 + i];
         const size_t o = (size_t)token * a.d + d0 + row;
-        store_act(y, o, a.act_dtype, acc);
+        store_act(y, o, a.y_dtype, acc);
         if (hidden) {
-            const float h = (i == tid ? h_first : load_act(hidden, o, a.act_dtype)) + round_act(a.act_dtype, acc);
+            const float h = (i == tid ? h_first : load_act(hidden, o, a.act_dtype)) + round_act(a.y_dtype, acc);
             store_act(hidden, o, a.act_dtype, h);
         }
-    }
-    if (a.trace && tid == 0) {
-        uint64_t* tr = a.trace + 8 * (size_t)(1024 + blockIdx.x);   // after the blocks of phase 1
-        tr[0] = t2_start; tr[1] = t2_wait; tr[2] = globaltimer_ns(); tr[3] = t2_pub; tr[4] = t2_loads; tr[5] = t2_acc;
-        tr[6] = t2_sync;
     }
 }
 
 constexpr int kP2pWarps = 8;
 
-// Prefill form of the down projection: grid (d/16, ceil(max instances / 8)),
-// one instance per warp, output one fp32 row per (row, rank) pair
-// (route_partials of prefill_grouped_routed_moe_batched_down, prefill.metal:693)
-// and one per row for the shared expert; additive down bias included.
+// Prefill form of the down projection (prefill_grouped_routed_moe_batched_down, prefill.metal:693, with
+// the weighted reduce of prefill_moe_reduce_token_major folded in): grid (d/16, ceil(max instances / 8)),
+// one instance per warp; every row's output, additive down bias included, is multiplied by its route
+// weight (the shared expert's by its gate) and added into the token's fp32 accumulator row.
 template <int BITS, int GROUP, int META>
-__global__ void __launch_bounds__(kP2pWarps * 32) phase2_partials_kernel(const ExpertArgs a, uint32_t gmax,
-                                                                        float* __restrict__ partials,
-                                                                        float* __restrict__ partial_shared) {
+__global__ void __launch_bounds__(kP2pWarps * 32) phase2_accumulate_kernel(const ExpertArgs a, uint32_t gmax) {
     using Q = QT<BITS, GROUP>;
     extern __shared__ __align__(16) uint8_t smem[];
     const uint32_t d0 = blockIdx.x * 16;
@@ -594,9 +523,12 @@ __global__ void __launch_bounds__(kP2pWarps * 32) phase2_partials_kernel(const E
     for (int c = 0; c < 2; ++c) {
         const uint32_t cc = 2 * t + c;
         if (cc < in.count) {
-            float* out = (shared ? partial_shared : partials) + (size_t)pick(in.pair, cc) * a.d;
-            out[d0 + g] = tot[0][c] + ab0;
-            out[d0 + g + 8] = tot[0][2 + c] + ab1;
+            const uint32_t pair = pick(in.pair, cc);
+            const uint32_t token = shared ? pair : pair / a.top_k;
+            const float w = shared ? (a.shared_gate ? a.shared_gate[token] : 1.0f) : a.route_w[pair];
+            float* out = a.yacc + (size_t)token * a.d;
+            atomicAdd(out + d0 + g, w * (tot[0][c] + ab0));
+            atomicAdd(out + d0 + g + 8, w * (tot[0][2 + c] + ab1));
         }
     }
 }
@@ -658,16 +590,14 @@ static cudaError_t launch_p2_t(cudaStream_t st, const ExpertArgs& a, uint32_t T,
 }
 
 template <int BITS, int GROUP, int META>
-static cudaError_t launch_p2p_t(cudaStream_t st, const ExpertArgs& a, uint32_t max_inst, float* partials,
-                                float* partial_shared) {
+static cudaError_t launch_p2p_t(cudaStream_t st, const ExpertArgs& a, uint32_t max_inst) {
     const uint32_t fmax = a.f_shared > a.f ? a.f_shared : a.f;
     const uint32_t gmax = fmax / GROUP;
     const uint32_t smem = kP2pWarps * (2 * 32 * gmax + 48);
-    auto k = phase2_partials_kernel<BITS, GROUP, META>;
+    auto k = phase2_accumulate_kernel<BITS, GROUP, META>;
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    k<<<dim3(a.d / 16, (max_inst + kP2pWarps - 1) / kP2pWarps), kP2pWarps * 32, smem, st>>>(a, gmax, partials,
-                                                                                         partial_shared);
+    k<<<dim3(a.d / 16, (max_inst + kP2pWarps - 1) / kP2pWarps), kP2pWarps * 32, smem, st>>>(a, gmax);
     return cudaGetLastError();
 }
 
@@ -697,9 +627,9 @@ cudaError_t launch_phase2(const shrike_moe* m, cudaStream_t st, const ExpertArgs
     SHRIKE_DISPATCH(launch_p2_t, st, a, T, max_inst, y, hidden, pdl);
 }
 
-cudaError_t launch_phase2_partials(const shrike_moe* m, cudaStream_t st, const ExpertArgs& a,
-                                   uint32_t max_inst, float* partials, float* partial_shared) {
-    SHRIKE_DISPATCH(launch_p2p_t, st, a, max_inst, partials, partial_shared);
+cudaError_t launch_phase2_accumulate(const shrike_moe* m, cudaStream_t st, const ExpertArgs& a,
+                                     uint32_t max_inst) {
+    SHRIKE_DISPATCH(launch_p2p_t, st, a, max_inst);
 }
 
 }  // namespace shrike

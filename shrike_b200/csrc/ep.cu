@@ -100,18 +100,18 @@ ep_local_slots_kernel(const uint32_t* __restrict__ recv_ids, const uint64_t* __r
 __global__ void __launch_bounds__(256)
 ep_combine_kernel(const void* __restrict__ recv_y, const int32_t* __restrict__ row_of,
                   const void* __restrict__ y_home, uint32_t T, uint32_t world, uint32_t cap, uint32_t d,
-                  uint32_t act_dtype, void* __restrict__ y, void* __restrict__ hidden) {
+                  uint32_t act_dtype, uint32_t y_dtype, void* __restrict__ y, void* __restrict__ hidden) {
     const uint32_t t = blockIdx.y, i = blockIdx.x * blockDim.x + threadIdx.x;
     if (t >= T || i >= d) return;
     const size_t o = (size_t)t * d + i;
-    float acc = y_home ? load_act(y_home, o, act_dtype) : 0.0f;
+    float acc = y_home ? load_act(y_home, o, y_dtype) : 0.0f;
     for (uint32_t g = 0; g < world; ++g) {
         const int32_t row = row_of[(size_t)t * world + g];
-        if (row >= 0) acc += load_act(recv_y, ((size_t)g * cap + row) * d + i, act_dtype);
+        if (row >= 0) acc += load_act(recv_y, ((size_t)g * cap + row) * d + i, y_dtype);
     }
-    store_act(y, o, act_dtype, acc);
+    store_act(y, o, y_dtype, acc);
     if (hidden) {
-        const float h = load_act(hidden, o, act_dtype) + round_act(act_dtype, acc);
+        const float h = load_act(hidden, o, act_dtype) + round_act(y_dtype, acc);
         store_act(hidden, o, act_dtype, h);
     }
 }
@@ -141,7 +141,7 @@ cudaError_t launch_ep_combine(const shrike_moe* m, cudaStream_t st, const void* 
                               const void* y_home, uint32_t T, uint32_t world, uint32_t cap, void* y, void* hidden) {
     const shrike_moe_config& c = m->cfg;
     ep_combine_kernel<<<dim3((c.d + 255) / 256, T), 256, 0, st>>>(recv_y, row_of, y_home, T, world, cap, c.d,
-                                                                 c.act_dtype, y, hidden);
+                                                                 c.act_dtype, c.y_dtype, y, hidden);
     return cudaGetLastError();
 }
 

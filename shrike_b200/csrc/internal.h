@@ -40,24 +40,6 @@ inline Offsets3 to_offsets3(const shrike_expert_offsets& o) {
     return r;
 }
 
-// Routing of one decode row by the expert kernels themselves (see select.cuh).
-struct SelfRoute {
-    const float* logits;          // [num_experts], written by the launch before phase 1
-    const uint16_t* logit_bias;
-    const uint16_t* per_expert_scale;
-    const uint64_t* table;        // residency row
-    const uint32_t* io_status;
-    uint32_t* out_ids;
-    float* out_w;
-    uint32_t* out_slots;
-    uint32_t* out_counts;
-    uint32_t* pub;                // 32 words: the routing result phase 1 leaves for phase 2
-    uint32_t ne, top_k, sigmoid_scores, round_f16, pool_cells;
-    float scaling;
-    uint32_t enabled;             // 0: the work lists of a route kernel are used instead
-    uint32_t publish;             // this block also writes ids / weights / slots / counts
-};
-
 // Everything the expert kernels need that does not change between launches of
 // one call.
 struct ExpertArgs {
@@ -67,7 +49,8 @@ struct ExpertArgs {
     const uint8_t* shared_block;
     uint32_t d, f, f_shared, top_k;
     uint32_t activation, expert_bias;
-    uint32_t act_dtype;
+    uint32_t act_dtype;           // dtype of x and hidden
+    uint32_t y_dtype;             // dtype of y
     const Instance* inst;
     const uint32_t* n_inst;
     const uint32_t* sorted;       // sorted pair ids (token*top_k + rank)
@@ -75,11 +58,13 @@ struct ExpertArgs {
     const float* xsum;            // per-group sums of xh, [tokens x d/group]
     uint16_t* acts;               // fp16 operand copy of the routed activations [pairs x f]
     uint16_t* acts_shared;        // [tokens x f_shared]
+    float* yacc;                  // prefill: fp32 output accumulator [tokens x d]
     const float* route_w;         // [tokens x top_k]
     const float* shared_gate;     // [tokens] or NULL
     uint32_t* status;
-    uint64_t* trace;              // diagnostics: per-block timestamps of phase 1, or NULL
-    SelfRoute sr;
+#ifdef SHRIKE_TRACE
+    uint64_t* trace;              // debug builds: per-block timestamps, or NULL
+#endif
 };
 
 struct Workspace {
@@ -97,12 +82,11 @@ struct Workspace {
     uint32_t* expert_offsets = nullptr;
     uint32_t* expert_counts = nullptr;
     uint32_t* slot_of_expert = nullptr;
-    float* partials = nullptr;      // prefill: per-pair down outputs
+    float* yacc = nullptr;          // prefill: fp32 output accumulator [max_tokens x d]
     void* chunk_inst = nullptr;     // prefill: instances of up to 256 rows (tensor-core path)
     uint32_t* n_chunk_inst = nullptr; // [0] instances, [1] sorted rows
     uint16_t* xs = nullptr;         // prefill: fp16 activation rows in expert-sorted order [max_tokens x top_k x d]
     void* tensor_maps = nullptr;    // host: the TMA descriptors of xs, acts, xh, acts_shared
-    uint32_t* route_pub = nullptr;  // 32 words: the routing result phase 1 publishes for phase 2 (one-row decode)
     // forward_host staging
     void* x_dev = nullptr; void* y_dev = nullptr;
     uint32_t* ids_dev = nullptr; float* w_dev = nullptr; float* gate_dev = nullptr;
@@ -127,13 +111,34 @@ struct shrike_moe {
     uint64_t* residency = nullptr;
     uint32_t residency_layers = 0;
     int sm_count = 148;
+    bool no_pdl = false;          // SHRIKE_NO_PDL was set when the handle was created (diagnostics)
+    bool force_warp_mma = false;  // SHRIKE_PREFILL_PATH=mma was set when the handle was created (test switch)
+#ifdef SHRIKE_TRACE
     uint64_t* trace = nullptr;
+#endif
 };
+
+#ifdef SHRIKE_TRACE
+// Debug builds only (-DSHRIKE_TRACE): device buffer that receives per-block timestamps; NULL switches it off.
+extern "C" int shrike_debug_set_trace(shrike_moe* moe, uint64_t* trace_device_buffer);
+#endif
 
 namespace shrike {
 
 size_t act_bytes(uint32_t dt);
 
+// Most instances a decode call of T rows can have: one per distinct expert, one more per 8 further
+// rows of an expert, and the shared expert's.
+inline uint32_t max_instances(const shrike_moe_config& c, uint32_t T) {
+    const uint32_t pairs = T * c.top_k;
+    uint32_t routed = c.num_experts + pairs / 8;
+    if (routed > pairs) routed = pairs;
+    return routed + (c.has_shared ? (T + 7) / 8 : 0);
+}
+
+// api.cu: what the router kernels' vector loads rely on; `why` receives the first violation
+bool router_operands_aligned(const shrike_moe_config& c, const shrike_router_operands& o, const void* hidden,
+                             const char** why);
 // router.cu
 cudaError_t launch_router(const shrike_moe* m, cudaStream_t st, const shrike_router_operands& ops,
                           const void* hidden, uint32_t T, uint32_t stride, uint32_t* ids,
@@ -166,15 +171,13 @@ cudaError_t launch_synth_fill(const shrike_moe* m, cudaStream_t st, const PoolVi
 }  // namespace shrike
 
 namespace shrike {
-cudaError_t launch_phase2_partials(const shrike_moe* m, cudaStream_t st, const ExpertArgs& a,
-                                   uint32_t max_inst, float* partials, float* partial_shared);
+cudaError_t launch_phase2_accumulate(const shrike_moe* m, cudaStream_t st, const ExpertArgs& a,
+                                     uint32_t max_inst);
 // prefill.cu
 cudaError_t launch_prefill_plan(const shrike_moe* m, cudaStream_t st, const uint32_t* ids,
                                 const uint32_t* slots, const void* x, uint32_t T, bool with_shared,
-                                uint32_t pool_cells, bool warp_mma_instances);
-cudaError_t launch_prefill_combine(const shrike_moe* m, cudaStream_t st, const float* route_w,
-                                   const float* shared_gate, const uint32_t* slots, uint32_t T, void* y,
-                                   void* hidden);
+                                uint32_t pool_cells, bool warp_mma_instances, const uint32_t* io_status);
+cudaError_t launch_prefill_combine(const shrike_moe* m, cudaStream_t st, uint32_t T, void* y, void* hidden);
 }  // namespace shrike
 
 namespace shrike {
@@ -197,5 +200,5 @@ size_t umma_tensor_map_bytes();
 cudaError_t umma_prepare(shrike_moe* m);
 bool umma_supported(const shrike_moe_config& c);
 cudaError_t launch_umma_prefill(const shrike_moe* m, cudaStream_t st, const ExpertArgs& a, uint32_t T,
-                                uint32_t pool_cells, float* partials, float* partial_shared);
+                                uint32_t pool_cells);
 }  // namespace shrike

@@ -42,7 +42,7 @@ decode_plan_kernel(const uint32_t* __restrict__ slots, uint32_t T, uint32_t top_
                    Instance* __restrict__ inst, uint32_t* __restrict__ n_inst,
                    uint32_t* __restrict__ sorted, const void* __restrict__ x, uint32_t act_dtype,
                    uint32_t d, uint32_t int4, uint32_t group, uint16_t* __restrict__ xh,
-                   float* __restrict__ xsum, uint32_t* status) {
+                   float* __restrict__ xsum, uint32_t* status, uint32_t max_inst) {
     __shared__ PlanSmem sm;
     const uint32_t tid = threadIdx.x;
     const uint32_t n_pairs = T * top_k;
@@ -63,13 +63,13 @@ decode_plan_kernel(const uint32_t* __restrict__ slots, uint32_t T, uint32_t top_
         sm.key[p] = s;
     }
     __syncthreads();
-    plan_body(sm, n_pairs, T, with_shared, inst, n_inst, sorted);
+    plan_body(sm, n_pairs, T, with_shared, inst, n_inst, sorted, max_inst, status);
 
     // fp16 operand copy of the activation rows and their per-group sums
     const uint32_t items = T * (d / 8);
     const size_t row_bytes = (size_t)d * (act_dtype == SHRIKE_DTYPE_FP32 ? 4 : 2);
     for (uint32_t i0 = 0; i0 < items; i0 += kPlanThreads)
-        xprep_item(x, row_bytes, d, group, act_dtype, int4 != 0, i0 + tid, i0 + tid < items, xh, xsum);
+        xprep_item(x, row_bytes, d, group, act_dtype, int4 != 0, i0 + tid, i0 + tid < items, xh, xsum, status);
 }
 
 cudaError_t launch_decode_plan(const shrike_moe* m, cudaStream_t st, const uint32_t* slots,
@@ -78,7 +78,7 @@ cudaError_t launch_decode_plan(const shrike_moe* m, cudaStream_t st, const uint3
     decode_plan_kernel<<<1, kPlanThreads, 0, st>>>(
         slots, T, m->cfg.top_k, io_status, with_shared ? 1u : 0u, pool_cells,
         m->ws.inst, m->ws.n_inst, m->ws.sorted, x, m->cfg.act_dtype, m->cfg.d,
-        m->cfg.weight_bits == 4 ? 1u : 0u, m->cfg.group_size, m->ws.xh, m->ws.xsum, m->ws.status);
+        m->cfg.weight_bits == 4 ? 1u : 0u, m->cfg.group_size, m->ws.xh, m->ws.xsum, m->ws.status, max_instances(m->cfg, T));
     return cudaGetLastError();
 }
 
@@ -90,7 +90,7 @@ constexpr uint32_t kGroupTokens = 128;  // rows per block
 // per-(block, expert) counts.
 __global__ void __launch_bounds__(256)
 group_hist_kernel(const uint32_t* __restrict__ ids, uint32_t T, uint32_t top_k, uint32_t ne,
-                  uint32_t* __restrict__ block_hist) {
+                  uint32_t* __restrict__ block_hist, uint32_t* status) {
     __shared__ uint32_t bits[SHRIKE_MAX_EXPERTS][kGroupTokens / 32];
     const uint32_t t0 = blockIdx.x * kGroupTokens;
     for (uint32_t i = threadIdx.x; i < SHRIKE_MAX_EXPERTS * (kGroupTokens / 32); i += blockDim.x)
@@ -100,7 +100,13 @@ group_hist_kernel(const uint32_t* __restrict__ ids, uint32_t T, uint32_t top_k, 
         const uint32_t tl = i / top_k, t = t0 + tl;
         if (t < T) {
             const uint32_t e = ids[(size_t)t * top_k + (i - tl * top_k)];
-            if (e < ne) atomicOr(&bits[e][tl >> 5], 1u << (tl & 31));
+            if (e < ne) {
+                // a row that names one expert twice (no top-k router does) is counted once and reported
+                const uint32_t bit = 1u << (tl & 31);
+                if (atomicOr(&bits[e][tl >> 5], bit) & bit) report_status(status, kStatusBadIndex);
+            } else {
+                report_status(status, kStatusBadIndex);   // expert id out of range: the pair is dropped
+            }
         }
     }
     __syncthreads();
@@ -186,7 +192,7 @@ cudaError_t launch_group_pairs(const shrike_moe* m, cudaStream_t st, const uint3
         if (e != cudaSuccess) return e;
         return cudaMemsetAsync(offsets, 0xff, ne * 4, st);
     }
-    group_hist_kernel<<<nb, 256, 0, st>>>(ids, T, k, ne, m->ws.block_hist);
+    group_hist_kernel<<<nb, 256, 0, st>>>(ids, T, k, ne, m->ws.block_hist, m->ws.status);
     group_scan_kernel<<<1, 256, 0, st>>>(m->ws.block_hist, nb, ne, offsets, counts);
     group_place_kernel<<<nb, 256, 0, st>>>(ids, weights, T, k, ne, m->ws.block_hist, sorted_pairs,
                                            m->ws.sorted);

@@ -19,10 +19,12 @@ struct PlanSmem {
 };
 
 // sm.key[0 .. n_pairs) must hold the (validated) cells; entries past n_pairs
-// are ignored. Writes inst, n_inst, sorted.
+// are ignored. Writes inst, n_inst, sorted. `inst` holds max_inst entries (sized for at most
+// num_experts distinct cells): instances beyond it -- possible only when the caller's slots name more
+// distinct cells than the layer has experts -- are dropped and reported through the status word.
 __device__ __forceinline__ void plan_body(PlanSmem& sm, uint32_t n_pairs, uint32_t T, uint32_t with_shared,
                                           Instance* __restrict__ inst, uint32_t* __restrict__ n_inst,
-                                          uint32_t* __restrict__ sorted) {
+                                          uint32_t* __restrict__ sorted, uint32_t max_inst, uint32_t* status) {
     const uint32_t tid = threadIdx.x, bd = blockDim.x, lane = tid & 31, warp = tid >> 5;
     if (tid == 0) sm.n_valid = 0;
     __syncthreads();
@@ -76,16 +78,19 @@ __device__ __forceinline__ void plan_body(PlanSmem& sm, uint32_t n_pairs, uint32
         Instance in;
         in.kind = 0; in.slot = my; in.first = p; in.count = count;
         for (uint32_t j = 0; j < 8; ++j) in.pair[j] = sm.order[p + (j < count ? j : 0)];
-        inst[sm.index[p]] = in;
+        if (sm.index[p] < max_inst) inst[sm.index[p]] = in;
     }
     const uint32_t n_shared = with_shared ? (T + 7) / 8 : 0;
     for (uint32_t j = tid; j < n_shared; j += bd) {
         Instance in;
         in.kind = 1; in.slot = 0; in.first = j * 8; in.count = min(8u, T - j * 8);
         for (uint32_t q = 0; q < 8; ++q) in.pair[q] = j * 8 + (q < in.count ? q : 0);
-        inst[n_routed + j] = in;
+        if (n_routed + j < max_inst) inst[n_routed + j] = in;
     }
-    if (tid == 0) *n_inst = n_routed + n_shared;
+    if (tid == 0) {
+        if (n_routed + n_shared > max_inst) report_status(status, kStatusBadIndex);
+        *n_inst = min(n_routed + n_shared, max_inst);
+    }
 }
 
 }  // namespace shrike

@@ -1,9 +1,11 @@
 // Prefill path for ragged batches: rows are permuted by expert on the device
-// (plan.cu), every expert's rows run through the dequant-fused tiles in
-// instances of 8, the down projection writes one partial row per (row, rank)
-// pair, and a last pass does the weighted combine
-// (prefill_moe_reduce_token_major, prefill.metal:624-645, plus the two residual
-// adds of RealForwardRunner.swift:4658-4665 in one pass).
+// (plan.cu), every expert's rows run through the expert-grouped GEMM (or, for
+// shapes it does not take, the dequant-fused tiles in instances of 8), the
+// down projection's epilogue multiplies each row by its route weight and adds
+// it into one fp32 accumulator row per token (the weighted reduce of
+// prefill_moe_reduce_token_major, prefill.metal:624-645, without the
+// per-(row, rank) partial rows), and a last pass converts and does the two
+// residual adds of RealForwardRunner.swift:4658-4665.
 #include "internal.h"
 
 namespace shrike {
@@ -62,63 +64,58 @@ prefill_instances_kernel(const uint32_t* __restrict__ offsets, const uint32_t* _
 // x -> fp16 operand layout and per-group sums, all rows.
 __global__ void __launch_bounds__(256)
 prefill_xprep_kernel(const void* __restrict__ x, uint32_t T, uint32_t d, uint32_t group, uint32_t act_dtype,
-                     uint32_t int4, uint16_t* __restrict__ xh, float* __restrict__ xsum) {
+                     uint32_t int4, uint16_t* __restrict__ xh, float* __restrict__ xsum, uint32_t* status) {
     const uint32_t items = T * (d / 8);
     const size_t row_bytes = (size_t)d * (act_dtype == SHRIKE_DTYPE_FP32 ? 4 : 2);
     for (uint32_t i0 = blockIdx.x * blockDim.x; i0 < items; i0 += gridDim.x * blockDim.x)
         xprep_item(x, row_bytes, d, group, act_dtype, int4 != 0, i0 + threadIdx.x, i0 + threadIdx.x < items, xh,
-                   xsum);
+                   xsum, status);
 }
 
 // slot_of_expert[e] = the cell every pair of expert e resolved to.
+// A streamed batch whose status word is not READY (moe_io_ready, moe.metal:36-39) leaves every expert
+// without a cell: only the shared term remains.
 __global__ void __launch_bounds__(256)
 prefill_slot_of_expert_kernel(const uint32_t* __restrict__ ids, const uint32_t* __restrict__ slots,
-                              uint32_t n_pairs, uint32_t ne, uint32_t* __restrict__ slot_of_expert) {
+                              uint32_t n_pairs, uint32_t ne, const uint32_t* __restrict__ io_status,
+                              uint32_t* __restrict__ slot_of_expert) {
     const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (io_status) {
+        const uint32_t s = *io_status;
+        if (s != 1u && s != 3u) return;
+    }
     if (i < n_pairs) {
         const uint32_t e = ids[i];
         if (e < ne) slot_of_expert[e] = slots[i];
     }
 }
 
-// y[t] = sg[t]*partial_shared[t] + sum_r w[t,r]*partial[t*K+r]; hidden += y.
-// Pairs whose expert had no cell were never written and are skipped by slot.
+// y[t] = the accumulated row (shared term and weighted expert rows, fp32); hidden += y.
 __global__ void __launch_bounds__(256)
-prefill_combine_kernel(const float* __restrict__ partials, const float* __restrict__ partial_shared,
-                       const float* __restrict__ route_w, const float* __restrict__ shared_gate,
-                       const uint32_t* __restrict__ slots, uint32_t T, uint32_t top_k, uint32_t d,
-                       uint32_t has_shared, uint32_t act_dtype, void* __restrict__ y,
-                       void* __restrict__ hidden) {
-    const uint32_t t = blockIdx.y;
+prefill_combine_kernel(const float* __restrict__ yacc, uint32_t n, uint32_t act_dtype, uint32_t y_dtype,
+                       void* __restrict__ y, void* __restrict__ hidden) {
     const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (t >= T || i >= d) return;
-    float acc = 0.f;
-    if (has_shared) {
-        const float g = shared_gate ? shared_gate[t] : 1.0f;
-        acc = g * partial_shared[(size_t)t * d + i];
-    }
-    for (uint32_t r = 0; r < top_k; ++r) {
-        const uint32_t p = t * top_k + r;
-        if (slots[p] != SHRIKE_SLOT_MISS) acc = fmaf(route_w[p], partials[(size_t)p * d + i], acc);
-    }
-    const size_t o = (size_t)t * d + i;
-    store_act(y, o, act_dtype, acc);
+    if (i >= n) return;
+    const float acc = yacc[i];
+    store_act(y, i, y_dtype, acc);
     if (hidden) {
-        const float h = load_act(hidden, o, act_dtype) + round_act(act_dtype, acc);
-        store_act(hidden, o, act_dtype, h);
+        const float h = load_act(hidden, i, act_dtype) + round_act(y_dtype, acc);
+        store_act(hidden, i, act_dtype, h);
     }
 }
 
 cudaError_t launch_prefill_plan(const shrike_moe* m, cudaStream_t st, const uint32_t* ids,
                                 const uint32_t* slots, const void* x, uint32_t T, bool with_shared,
-                                uint32_t pool_cells, bool warp_mma_instances) {
+                                uint32_t pool_cells, bool warp_mma_instances, const uint32_t* io_status) {
     const shrike_moe_config& c = m->cfg;
     const Workspace& ws = m->ws;
     cudaError_t e = cudaMemsetAsync(ws.slot_of_expert, 0xff, c.num_experts * 4, st);
     if (e != cudaSuccess) return e;
+    e = cudaMemsetAsync(ws.yacc, 0, (size_t)T * c.d * 4, st);
+    if (e != cudaSuccess) return e;
     const uint32_t n_pairs = T * c.top_k;
     prefill_slot_of_expert_kernel<<<(n_pairs + 255) / 256, 256, 0, st>>>(ids, slots, n_pairs, c.num_experts,
-                                                                         ws.slot_of_expert);
+                                                                         io_status, ws.slot_of_expert);
     e = launch_group_pairs(m, st, ids, nullptr, T, nullptr, ws.expert_offsets, ws.expert_counts);
     if (e != cudaSuccess) return e;
     if (warp_mma_instances)   // the tensor-core path builds its own 256-row instances
@@ -127,17 +124,14 @@ cudaError_t launch_prefill_plan(const shrike_moe* m, cudaStream_t st, const uint
                                                     ws.inst, ws.n_inst, ws.status);
     const uint32_t items = T * (c.d / 8);
     prefill_xprep_kernel<<<min(2048u, (items + 255) / 256), 256, 0, st>>>(
-        x, T, c.d, c.group_size, c.act_dtype, c.weight_bits == 4 ? 1u : 0u, ws.xh, ws.xsum);
+        x, T, c.d, c.group_size, c.act_dtype, c.weight_bits == 4 ? 1u : 0u, ws.xh, ws.xsum, ws.status);
     return cudaGetLastError();
 }
 
-cudaError_t launch_prefill_combine(const shrike_moe* m, cudaStream_t st, const float* route_w,
-                                   const float* shared_gate, const uint32_t* slots, uint32_t T, void* y,
-                                   void* hidden) {
+cudaError_t launch_prefill_combine(const shrike_moe* m, cudaStream_t st, uint32_t T, void* y, void* hidden) {
     const shrike_moe_config& c = m->cfg;
-    prefill_combine_kernel<<<dim3((c.d + 255) / 256, T), 256, 0, st>>>(
-        m->ws.partials, m->ws.partials + (size_t)c.max_tokens * c.top_k * c.d, route_w, shared_gate, slots, T,
-        c.top_k, c.d, c.has_shared, c.act_dtype, y, hidden);
+    const uint32_t n = T * c.d;
+    prefill_combine_kernel<<<(n + 255) / 256, 256, 0, st>>>(m->ws.yacc, n, c.act_dtype, c.y_dtype, y, hidden);
     return cudaGetLastError();
 }
 

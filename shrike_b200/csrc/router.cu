@@ -77,7 +77,7 @@ struct RouterArgs {
     float* xsum;
     uint32_t* done_counter;
     uint32_t* status;
-    uint64_t* trace;               // diagnostics: 8 timestamps per block, or NULL
+    uint32_t max_inst;
 };
 
 // N chunks per lane; PRED: the row may be shorter than 32*N chunks.
@@ -264,28 +264,10 @@ template <bool CG>
 __device__ __forceinline__ void select_row(const float* lg, const RouterArgs& a, uint32_t lane,
                                            uint32_t& out_id, float& out_w) {
     const uint32_t ne = a.ne, top_k = a.top_k;
-    float sc[8];
-    uint32_t taken = 0;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        const uint32_t e = lane + 32 * i;
-        float s = -INFINITY;
-        if (e < ne) {
-            const float raw = CG ? __ldcg(lg + e) : lg[e];
-            const float b = a.logit_bias ? bf16_bits_to_f32(a.logit_bias[e]) : 0.0f;
-            s = __fadd_rn(__fadd_rn(a.sigmoid_scores ? sigmoid_det(raw) : raw, b), 0.0f);  // -0 -> +0
-        } else {
-            taken |= 1u << i;
-        }
-        sc[i] = s;
-    }
-    // order-preserving integer keys: one warp-wide max and one warp-wide min per pick
+    // order-preserving integer keys (0 = not a candidate): one warp-wide max and one warp-wide min per pick
     uint32_t key[8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        const uint32_t b = __float_as_uint(sc[i]);
-        key[i] = (taken & (1u << i)) ? 0u : ((b & 0x80000000u) ? ~b : (b | 0x80000000u));
-    }
+    for (int i = 0; i < 8; ++i) key[i] = selection_key<CG>(lg, a, lane + 32 * i);
     float my_score = 0.f;
     uint32_t my_id = 0;
     for (uint32_t r = 0; r < top_k; ++r) {
@@ -302,7 +284,7 @@ __device__ __forceinline__ void select_row(const float* lg, const RouterArgs& a,
             for (int i = 0; i < 8; ++i) key[i] = (win >> 5) == (uint32_t)i ? 0u : key[i];
         }
         if (lane == r) {
-            my_score = __uint_as_float((wmax & 0x80000000u) ? (wmax & 0x7fffffffu) : ~wmax);
+            my_score = score_of_key(wmax);
             my_id = win == 0xffffffffu ? 0u : win;
         }
     }
@@ -540,16 +522,12 @@ __global__ void __launch_bounds__(kRouterWarps * 32) route_fused_kernel(const Ro
     __shared__ SelectSmem sel;
     __shared__ uint32_t s_last, s_miss;
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    uint64_t ts[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    if (a.trace) ts[0] = globaltimer_ns();
 
     // the weight rows do not depend on the previous kernel: fetch them first
     logits_body(a, [&] {
         pdl_wait();
         pdl_launch_dependents();
-        if (a.trace) ts[4] = globaltimer_ns();
     });
-    if (a.trace) ts[1] = globaltimer_ns();
 
     // every block converts its share of the activation rows (blocks of 8 elements)
     {
@@ -557,14 +535,10 @@ __global__ void __launch_bounds__(kRouterWarps * 32) route_fused_kernel(const Ro
         const size_t esz = a.dt == SHRIKE_DTYPE_FP32 ? 4 : 2;
         for (uint32_t i0 = blockIdx.x * blockDim.x; i0 < items; i0 += gridDim.x * blockDim.x)
             xprep_item(a.hidden, (size_t)a.stride * esz, a.d, a.group, a.dt, a.int4 != 0, i0 + tid, i0 + tid < items,
-                       a.xh, a.xsum);
+                       a.xh, a.xsum, a.status);
     }
 
-    if (a.trace) ts[2] = globaltimer_ns();
-    if (a.no_tail) {
-        if (a.trace && tid == 0) for (int i = 0; i < 8; ++i) a.trace[8 * blockIdx.x + i] = ts[i];
-        return;
-    }
+    if (a.no_tail) return;
     __threadfence();
     __syncthreads();
     if (tid == 0) {
@@ -574,11 +548,7 @@ __global__ void __launch_bounds__(kRouterWarps * 32) route_fused_kernel(const Ro
         s_miss = 0;
     }
     __syncthreads();
-    if (a.trace) ts[3] = globaltimer_ns();
-    if (!s_last) {
-        if (a.trace && tid == 0) for (int i = 0; i < 8; ++i) a.trace[8 * blockIdx.x + i] = ts[i];
-        return;
-    }
+    if (!s_last) return;
     __threadfence();
 
     for (uint32_t row = 0; row < a.T; ++row) {
@@ -592,7 +562,6 @@ __global__ void __launch_bounds__(kRouterWarps * 32) route_fused_kernel(const Ro
         }
     }
     __syncthreads();
-    if (a.trace) ts[4] = globaltimer_ns();
     bool ready = true;
     if (a.io_status) {
         const uint32_t s = *a.io_status;
@@ -619,7 +588,6 @@ __global__ void __launch_bounds__(kRouterWarps * 32) route_fused_kernel(const Ro
         a.counts[0] = n_pairs - s_miss;
         a.counts[1] = s_miss;
     }
-    if (a.trace) ts[5] = globaltimer_ns();
     // One row: every pair is its own instance; order them by cell as plan_body
     // would, with eight shuffles instead of the block-wide sort.
     bool fast = false;
@@ -655,12 +623,7 @@ __global__ void __launch_bounds__(kRouterWarps * 32) route_fused_kernel(const Ro
             }
         }
     }
-    if (!fast) plan_body(sm, n_pairs, a.T, a.with_shared, a.inst, a.n_inst, a.sorted);
-    if (a.trace && tid == 0) {
-        ts[6] = globaltimer_ns();
-        ts[7] = 1;
-        for (int i = 0; i < 8; ++i) a.trace[8 * blockIdx.x + i] = ts[i];
-    }
+    if (!fast) plan_body(sm, n_pairs, a.T, a.with_shared, a.inst, a.n_inst, a.sorted, a.max_inst, a.status);
 }
 
 // moe_classify_residency_body for T rows; one thread walks the pairs in order
@@ -766,7 +729,7 @@ cudaError_t launch_route_fused(const shrike_moe* m, cudaStream_t st, const shrik
     a.with_shared = m->cfg.has_shared; a.int4 = m->cfg.weight_bits == 4; a.group = m->cfg.group_size;
     a.xsum = m->ws.xsum;
     a.slots = slots; a.counts = counts; a.inst = m->ws.inst; a.n_inst = m->ws.n_inst; a.sorted = m->ws.sorted;
-    a.xh = m->ws.xh; a.done_counter = m->ws.done_counter; a.status = m->ws.status; a.trace = m->trace;
+    a.xh = m->ws.xh; a.done_counter = m->ws.done_counter; a.status = m->ws.status; a.max_inst = max_instances(m->cfg, T);
     const uint32_t rows = a.ne + (a.gate_row ? 1u : 0u);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((rows + kRouterWarps - 1) / kRouterWarps);
@@ -868,6 +831,10 @@ extern "C" int shrike_encode_router_static(const shrike_moe_config* config, void
         return bad(SHRIKE_EINVAL, "static router: affine weights need scales and biases");
     if (hidden_stride_elements < c.d || hidden_stride_elements % 4 != 0)
         return bad(SHRIKE_EINVAL, "static router: hidden stride must be >= d and a multiple of 4 elements");
+    if (c.shared_gated && (!ops->shared_gate || !out_shared_gate))
+        return bad(SHRIKE_EINVAL, "static router: a shared_gated config needs shared_gate and out_shared_gate");
+    const char* why = nullptr;
+    if (!router_operands_aligned(c, *ops, hidden, &why)) return bad(SHRIKE_EINVAL, why);
     float* logits = nullptr;
     cudaError_t e = static_logits_for_current_device(&logits);
     if (e != cudaSuccess) return bad(SHRIKE_EIO, cudaGetErrorString(e));

@@ -45,13 +45,25 @@ __host__ __device__ __forceinline__ float exp_det(float x) {
 
 __device__ __forceinline__ float sigmoid_det(float x) { return __fdiv_rn(1.0f, __fadd_rn(1.0f, exp_det(-x))); }
 
-// Order-preserving key of expert e's selection score (0 = not a candidate); the same
-// arithmetic as select_row.
-template <class A>
-__device__ __forceinline__ uint32_t selection_key_of(float raw, float bias, const A& a) {
-    const float s = __fadd_rn(__fadd_rn(a.sigmoid_scores ? sigmoid_det(raw) : raw, bias), 0.0f);  // -0 -> +0
+// Order-preserving key of a selection score; 0 = not a candidate. The reference's insertion scan
+// (moe.metal:436-456) never inserts a NaN score (every comparison is false) nor -inf (not greater than the
+// initial -inf, and the tie-break wants an id below 0): both map to 0 here.
+__device__ __forceinline__ uint32_t key_of_score(float s) {
+    s = __fadd_rn(s, 0.0f);  // -0 -> +0
+    if (!(s > -INFINITY)) return 0u;
     const uint32_t b = __float_as_uint(s);
     return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+// The score a key stands for; a pick that found no candidate keeps the scan's initial -inf (and id 0).
+__device__ __forceinline__ float score_of_key(uint32_t k) {
+    if (k == 0u) return -INFINITY;
+    return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k);
+}
+
+// Key of expert e's selection score; the same arithmetic as select_row.
+template <class A>
+__device__ __forceinline__ uint32_t selection_key_of(float raw, float bias, const A& a) {
+    return key_of_score(__fadd_rn(a.sigmoid_scores ? sigmoid_det(raw) : raw, bias));
 }
 
 template <bool CG, class A>
@@ -152,8 +164,7 @@ __device__ __forceinline__ void select_row_block(const float* lg, const A& a, Se
         float my_score = 0.f;
         uint32_t my_id = 0;
         if (lane < a.top_k) {
-            const uint32_t k = ss.sel_key[lane];
-            my_score = __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k);
+            my_score = score_of_key(ss.sel_key[lane]);
             my_id = ss.sel_id[lane];
         }
         out_w = selection_weight<true>(lg, a, lane, my_score, my_id);
@@ -162,96 +173,5 @@ __device__ __forceinline__ void select_row_block(const float* lg, const A& a, Se
     __syncthreads();   // the scratch is reused by the next row
 }
 
-
-// One decode row routed by the calling block itself (any block size >= 128): picks, weights and pool
-// cells land in shared memory. Every block of the expert kernels repeats this instead of waiting for
-// one block of a previous launch to publish the result.
-struct SelfRouteSmem {
-    SelectSmem sel;
-    uint32_t id[SHRIKE_MAX_TOP_K];
-    float w[SHRIKE_MAX_TOP_K];
-    uint32_t slot[SHRIKE_MAX_TOP_K];   // SHRIKE_SLOT_MISS: not resident, or the batch is not ready
-    uint32_t order[SHRIKE_MAX_TOP_K];  // picks with a cell, by (cell, rank): the order of the work lists
-    uint32_t n_routed;
-    uint32_t misses;
-};
-
-// table_sm: the residency row staged in shared memory by the caller, or NULL to read it from global memory.
-template <class SR>
-__device__ __forceinline__ void self_route_block(const SR& r, SelfRouteSmem& sm, uint32_t* status,
-                                                 const uint64_t* table_sm = nullptr) {
-    uint32_t id;
-    float w;
-    const uint32_t tid = threadIdx.x;
-    // requested before the selection so that its round trip overlaps it
-    uint32_t io = 1u;
-    if (tid < 32 && r.io_status) io = *(const volatile uint32_t*)r.io_status;
-    select_row_block(r.logits, r, sm.sel, id, w);
-    if (tid < 32) {
-        const bool ready = io == 1u || io == 3u;
-        uint32_t slot = SHRIKE_SLOT_MISS;
-        bool miss = false;
-        if (tid < r.top_k) {
-            const uint64_t word = (table_sm ? table_sm : r.table)[min(id, r.ne - 1u)];
-            slot = (uint32_t)(word & 0xffffffffu);
-            const bool hit = (uint32_t)(word >> 32) == 2u && slot != SHRIKE_SLOT_MISS;
-            if (!hit) { slot = SHRIKE_SLOT_MISS; miss = true; }
-            sm.id[tid] = id;
-            sm.w[tid] = w;
-        }
-        const uint32_t misses = __popc(__ballot_sync(0xffffffffu, miss));
-        if (tid < r.top_k) {
-            // what the host reads back is the table's answer; what the kernels follow is range-checked
-            if (r.publish && r.out_slots) r.out_slots[tid] = slot;
-            if (slot != SHRIKE_SLOT_MISS && slot >= r.pool_cells) {
-                report_status(status, kStatusBadIndex);
-                slot = SHRIKE_SLOT_MISS;
-            }
-            slot = ready ? slot : SHRIKE_SLOT_MISS;
-            sm.slot[tid] = slot;
-            if (r.publish) {
-                r.out_ids[tid] = id;
-                r.out_w[tid] = w;
-            }
-        }
-        // instances in cell order, as the route kernel's work lists have them
-        const uint32_t mine = tid < r.top_k ? slot : SHRIKE_SLOT_MISS;
-        uint32_t pos = 0;
-        for (uint32_t j = 0; j < r.top_k; ++j) {
-            const uint32_t o = __shfl_sync(0xffffffffu, mine, j);
-            if (mine != SHRIKE_SLOT_MISS && o != SHRIKE_SLOT_MISS) pos += (o < mine || (o == mine && j < tid)) ? 1u : 0u;
-        }
-        if (mine != SHRIKE_SLOT_MISS) sm.order[pos] = tid;
-        const uint32_t n_routed = __popc(__ballot_sync(0xffffffffu, mine != SHRIKE_SLOT_MISS));
-        if (r.publish && r.pub) {
-            // what phase 2 needs, in one place: [0..7] cell, [8..15] order, [16..23] weight bits, [24] count
-            if (tid < SHRIKE_MAX_TOP_K) {
-                r.pub[tid] = tid < r.top_k ? slot : SHRIKE_SLOT_MISS;
-                r.pub[16 + tid] = tid < r.top_k ? __float_as_uint(w) : 0u;
-            }
-            if (mine != SHRIKE_SLOT_MISS) r.pub[8 + pos] = tid;
-            if (tid == 0) r.pub[24] = n_routed;
-        }
-        if (tid == 0) {
-            sm.n_routed = n_routed;
-            sm.misses = misses;
-            if (r.publish && r.out_counts) { r.out_counts[0] = r.top_k - misses; r.out_counts[1] = misses; }
-        }
-    }
-    __syncthreads();
-}
-
-// Phase 2 reads what phase 1's publishing block left (complete and visible once phase 1 is).
-template <class SR>
-__device__ __forceinline__ void self_route_read(const SR& r, SelfRouteSmem& sm) {
-    const uint32_t tid = threadIdx.x;
-    if (tid < SHRIKE_MAX_TOP_K) {
-        sm.slot[tid] = __ldcg(r.pub + tid);
-        sm.order[tid] = __ldcg(r.pub + 8 + tid);
-        sm.w[tid] = __uint_as_float(__ldcg(r.pub + 16 + tid));
-    }
-    if (tid == 0) sm.n_routed = __ldcg(r.pub + 24);
-    __syncthreads();
-}
 
 }  // namespace shrike

@@ -30,14 +30,15 @@
 //
 // PHASE 0: tile 0 = 128 gate rows, tile 1 = the matching 128 up rows; epilogue
 //          GLU -> fp16 activations in operand layout, one row per sorted pair.
-// PHASE 1: tiles = 256 consecutive down rows; epilogue (+ additive bias) -> one
-//          fp32 partial row per (row, rank) pair for the weighted combine.
+// PHASE 1: tiles = 256 consecutive down rows; epilogue (+ additive bias) x route
+//          weight -> red.global.add into the token's fp32 accumulator row (the
+//          weighted reduce, with no per-(row, rank) partial rows in between).
 //
 // Every wait is bounded; a wait that gives up sets the status word and the
 // block falls through to the TMEM release.
 #include <cuda.h>
-// -DSHRIKE_UMMA_TRACE: every block records entry / set-up / accumulators-ready / exit timestamps
-// in the handle's trace buffer (shrike_debug_set_trace); off in the shipped library.
+// -DSHRIKE_TRACE: every block records entry / set-up / accumulators-ready / exit timestamps
+// in the handle's trace buffer (shrike_debug_set_trace, debug builds only); compiled out of the shipped library.
 
 #include "internal.h"
 
@@ -58,7 +59,7 @@ constexpr uint32_t kOffPk = kOffA + kAStages * kAStageBytes;
 constexpr uint32_t kOffSc = kOffPk + kPkSlots * kPkSlotBytes;
 constexpr uint32_t kOffBar = kOffSc + 2 * kScHalfBytes;
 constexpr uint32_t kNumBars = 2 * kAStages + 2 * kBStages + 2 * kPkSlots + 3;
-constexpr uint32_t kUmmaSmemBytes = kOffBar + kNumBars * 8 + kUmmaMaxN * 4 + 16 + 1024 /*alignment slack*/;
+constexpr uint32_t kUmmaSmemBytes = kOffBar + kNumBars * 8 + 2 * kUmmaMaxN * 4 + 16 + 1024 /*alignment slack*/;
 
 struct WeightMaps {       // TMA descriptors of the two 128-row tiles of a block
     CUtensorMap w[2];     // packed weights   [cells][rows][row bytes]
@@ -213,7 +214,6 @@ struct ChunkInstance {  // up to 256 rows that share one expert block
 template <int BITS, int GROUP, int META, int PHASE>
 __global__ void __launch_bounds__(kUmmaThreads, 1)
 umma_expert_kernel(const ExpertArgs a, const ChunkInstance* __restrict__ inst, const uint32_t* __restrict__ n_inst,
-                   float* __restrict__ partials, float* __restrict__ partial_shared,
                    const __grid_constant__ UmmaMaps maps) {
     constexpr uint32_t kRowBlockBytes = 64 * BITS / 8;  // packed bytes of one row per K block (32 or 64)
     constexpr uint32_t kWordsPerBlock = kRowBlockBytes / 4;
@@ -222,7 +222,7 @@ umma_expert_kernel(const ExpertArgs a, const ChunkInstance* __restrict__ inst, c
     constexpr uint32_t kKbPerSc = 8 / kGroupsPerBlock;  // K blocks per scale copy (8 or 4)
     constexpr float kZero = BITS == 4 ? 8.0f : 128.0f;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
-#ifdef SHRIKE_UMMA_TRACE
+#ifdef SHRIKE_TRACE
     const uint64_t t_entry = globaltimer_ns();
 #endif
     const uint32_t ii = blockIdx.y;
@@ -257,8 +257,9 @@ umma_expert_kernel(const ExpertArgs a, const ChunkInstance* __restrict__ inst, c
     uint64_t* sc_full = pk_empty + kPkSlots;
     uint64_t* sc_empty = sc_full + 1;
     uint64_t* accum = sc_empty + 1;
-    uint32_t* rowid = (uint32_t*)(bars + kNumBars);   // output row of column n: pair id (routed) or row (shared)
-    uint32_t* tmem_slot = rowid + kUmmaMaxN;
+    uint32_t* rowid = (uint32_t*)(bars + kNumBars);   // token of column n
+    float* roww = (float*)(rowid + kUmmaMaxN);        // route weight (routed) or gate (shared) of column n
+    uint32_t* tmem_slot = (uint32_t*)(roww + kUmmaMaxN);
     __shared__ uint32_t s_failed;
 
     if (tid == 0) {
@@ -274,7 +275,14 @@ umma_expert_kernel(const ExpertArgs a, const ChunkInstance* __restrict__ inst, c
     if (PHASE == 1) {
         for (uint32_t n = tid; n < kUmmaMaxN; n += kUmmaThreads) {
             const uint32_t src = n < in.count ? n : 0;
-            rowid[n] = shared ? in.first + src : a.sorted[in.first + src];
+            if (shared) {
+                rowid[n] = in.first + src;
+                roww[n] = a.shared_gate ? a.shared_gate[in.first + src] : 1.0f;
+            } else {
+                const uint32_t pair = a.sorted[in.first + src];
+                rowid[n] = pair / a.top_k;
+                roww[n] = a.route_w[pair];
+            }
         }
     }
     if (warp == kConvWarps) tmem_alloc(smem_u32(tmem_slot), 2 * ncols);
@@ -282,7 +290,7 @@ umma_expert_kernel(const ExpertArgs a, const ChunkInstance* __restrict__ inst, c
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-#ifdef SHRIKE_UMMA_TRACE
+#ifdef SHRIKE_TRACE
     uint64_t* const tr = a.trace ? a.trace + 8 * ((size_t)(PHASE * 4096 + blockIdx.y) * 8 + blockIdx.x) : nullptr;
     if (tr && tid == 0) { tr[0] = t_entry; tr[1] = globaltimer_ns(); tr[7] = ((uint64_t)N << 32) | KB; }
 #endif
@@ -453,7 +461,7 @@ umma_expert_kernel(const ExpertArgs a, const ChunkInstance* __restrict__ inst, c
         if (!ok) report_status(a.status, kStatusWaitTimeout);
         if (*(volatile uint32_t*)&s_failed) ok = false;
         tc_fence_after();
-#ifdef SHRIKE_UMMA_TRACE
+#ifdef SHRIKE_TRACE
         if (tr && tid == 0) tr[5] = globaltimer_ns();
 #endif
         const uint32_t q = warp & 3, h = warp >> 2;
@@ -491,7 +499,6 @@ umma_expert_kernel(const ExpertArgs a, const ChunkInstance* __restrict__ inst, c
                 if (d0 < a.d) ab0 = bf16_bits_to_f32(dab[d0]);
                 if (d1 < a.d) ab1 = bf16_bits_to_f32(dab[d1]);
             }
-            float* out = shared ? partial_shared : partials;
             const bool ok0 = ok && d0 < a.d, ok1 = ok && d1 < a.d;
             for (uint32_t c0 = h * 16; c0 < N; c0 += kColStep) {
                 uint32_t v0[16], v1[16];
@@ -502,15 +509,17 @@ umma_expert_kernel(const ExpertArgs a, const ChunkInstance* __restrict__ inst, c
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
                     if ((uint32_t)j < live) {
-                        float* o = out + (size_t)rowid[c0 + j] * a.d + d0;
-                        if (ok0) o[0] = __uint_as_float(v0[j]) + ab0;
-                        if (ok1) o[128] = __uint_as_float(v1[j]) + ab1;
+                        // lanes hold consecutive output rows: one 128-byte reduction per warp and column
+                        float* o = a.yacc + (size_t)rowid[c0 + j] * a.d + d0;
+                        const float w = roww[c0 + j];
+                        if (ok0) atomicAdd(o, w * (__uint_as_float(v0[j]) + ab0));
+                        if (ok1) atomicAdd(o + 128, w * (__uint_as_float(v1[j]) + ab1));
                     }
                 }
             }
         }
     }
-#ifdef SHRIKE_UMMA_TRACE
+#ifdef SHRIKE_TRACE
     if (tr && tid == 0) tr[6] = globaltimer_ns();
 #endif
     if (*(volatile uint32_t*)&s_failed && lane == 0 && warp > kConvWarps) {
@@ -679,8 +688,7 @@ cudaError_t umma_prepare(shrike_moe* m) {
 
 template <int BITS, int GROUP, int META>
 static cudaError_t launch_umma_t(cudaStream_t st, const ExpertArgs& a, const ChunkInstance* inst,
-                                 const uint32_t* n_inst, uint32_t max_inst, float* partials, float* partial_shared,
-                                 const UmmaMaps& m0, const UmmaMaps& m1) {
+                                 const uint32_t* n_inst, uint32_t max_inst, const UmmaMaps& m0, const UmmaMaps& m1) {
     auto k0 = umma_expert_kernel<BITS, GROUP, META, 0>;
     auto k1 = umma_expert_kernel<BITS, GROUP, META, 1>;
     cudaError_t e = cudaFuncSetAttribute(k0, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kUmmaSmemBytes);
@@ -688,12 +696,10 @@ static cudaError_t launch_umma_t(cudaStream_t st, const ExpertArgs& a, const Chu
     e = cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kUmmaSmemBytes);
     if (e != cudaSuccess) return e;
     const uint32_t fmax = a.f_shared > a.f ? a.f_shared : a.f;
-    k0<<<dim3((fmax + 127) / 128, max_inst), kUmmaThreads, kUmmaSmemBytes, st>>>(a, inst, n_inst, partials,
-                                                                               partial_shared, m0);
+    k0<<<dim3((fmax + 127) / 128, max_inst), kUmmaThreads, kUmmaSmemBytes, st>>>(a, inst, n_inst, m0);
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;
-    k1<<<dim3((a.d + 255) / 256, max_inst), kUmmaThreads, kUmmaSmemBytes, st>>>(a, inst, n_inst, partials,
-                                                                              partial_shared, m1);
+    k1<<<dim3((a.d + 255) / 256, max_inst), kUmmaThreads, kUmmaSmemBytes, st>>>(a, inst, n_inst, m1);
     return cudaGetLastError();
 }
 
@@ -710,7 +716,7 @@ size_t umma_tensor_map_bytes() { return 16 * sizeof(CUtensorMap); }
 // Gate/up + GLU, then down, for the instances built from the grouping the
 // prefill plan left in the workspace.
 cudaError_t launch_umma_prefill(const shrike_moe* m, cudaStream_t st, const ExpertArgs& a, uint32_t T,
-                                uint32_t pool_cells, float* partials, float* partial_shared) {
+                                uint32_t pool_cells) {
     const shrike_moe_config& c = m->cfg;
     const Workspace& ws = m->ws;
     const CUtensorMap* am = (const CUtensorMap*)ws.tensor_maps;
@@ -753,7 +759,7 @@ cudaError_t launch_umma_prefill(const shrike_moe* m, cudaStream_t st, const Expe
     const uint32_t bits = c.weight_bits, grp = c.group_size;
     const bool f16 = c.meta_dtype == SHRIKE_DTYPE_FP16;
 #define SHRIKE_UMMA(B, G, M) \
-    return launch_umma_t<B, G, M>(st, a, inst, ws.n_chunk_inst, max_inst, partials, partial_shared, maps[0], maps[1])
+    return launch_umma_t<B, G, M>(st, a, inst, ws.n_chunk_inst, max_inst, maps[0], maps[1])
     if (bits == 4 && grp == 64 && !f16) SHRIKE_UMMA(4, 64, SHRIKE_DTYPE_BF16);
     if (bits == 4 && grp == 64 && f16) SHRIKE_UMMA(4, 64, SHRIKE_DTYPE_FP16);
     if (bits == 4 && grp == 32 && !f16) SHRIKE_UMMA(4, 32, SHRIKE_DTYPE_BF16);

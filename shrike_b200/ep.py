@@ -51,7 +51,7 @@ class ExpertParallelLayer:
         self.routed.residency_set_layer_identity(0, 0)
         self.shared: Optional[capi.SharedExpert] = None
         k, d = config.top_k, config.d
-        act = config.torch_act_dtype
+        act, yt = config.torch_act_dtype, config.torch_y_dtype
         T, G, cap = rows_per_rank, world, self.cap
         z = lambda *shape, dtype: torch.zeros(shape, dtype=dtype, device=self.dev)
         self.ids, self.w = z(T, k, dtype=torch.int32), z(T, k, dtype=torch.float32)
@@ -63,8 +63,8 @@ class ExpertParallelLayer:
         self.send_counts = z(G, dtype=torch.int32)
         self.row_of = z(T, G, dtype=torch.int32)
         self.slots = z(G * cap, k, dtype=torch.int32)
-        self.y_part, self.y_back = z(G * cap, d, dtype=act), z(G, cap, d, dtype=act)
-        self.y_home = z(T, d, dtype=act) if config.has_shared else None
+        self.y_part, self.y_back = z(G * cap, d, dtype=yt), z(G, cap, d, dtype=yt)
+        self.y_home = z(T, d, dtype=yt) if config.has_shared else None
 
     def close(self):
         self.pool.close()

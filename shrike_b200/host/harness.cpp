@@ -29,7 +29,7 @@ int main(int argc, char** argv) {
     const uint32_t rows = (uint32_t)std::atoi(argv[2]);
     shrike_moe_config cfg{};
     cfg.d = 512; cfg.f = 256; cfg.num_experts = 32; cfg.top_k = 8; cfg.weight_bits = 4; cfg.group_size = 64;
-    cfg.meta_dtype = SHRIKE_DTYPE_BF16; cfg.act_dtype = SHRIKE_DTYPE_FP32; cfg.activation = SHRIKE_ACT_SILU;
+    cfg.meta_dtype = SHRIKE_DTYPE_BF16; cfg.act_dtype = SHRIKE_DTYPE_FP32; cfg.y_dtype = SHRIKE_DTYPE_FP32; cfg.activation = SHRIKE_ACT_SILU;
     cfg.router_kind = SHRIKE_ROUTER_SOFTMAX; cfg.routed_scaling = 1.0f; cfg.round_route_weights_f16 = 1;
     cfg.has_shared = 1; cfg.shared_gated = 1; cfg.shared_f = 256; cfg.max_tokens = 16;
     try {

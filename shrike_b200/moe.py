@@ -48,6 +48,11 @@ class MoEConfig:
     shared_gated: bool = False
     shared_f: int = 0
     max_tokens: int = 16
+    y_dtype: Optional[int] = None   # dtype of y; None = the activation dtype
+
+    @property
+    def out_dtype(self) -> int:
+        return self.act_dtype if self.y_dtype is None else self.y_dtype
 
     def to_c(self) -> capi.MoEConfig:
         return capi.MoEConfig(
@@ -55,11 +60,15 @@ class MoEConfig:
             self.meta_dtype, self.act_dtype, self.activation, int(self.expert_bias), self.router_kind,
             float(self.routed_scaling), self.router_weight_bits, int(self.round_route_weights_f16),
             int(self.has_shared), int(self.shared_gated), self.shared_f if self.has_shared else 0,
-            self.max_tokens)
+            self.max_tokens, self.out_dtype)
 
     @property
     def torch_act_dtype(self) -> torch.dtype:
         return _TORCH_ACT[self.act_dtype]
+
+    @property
+    def torch_y_dtype(self) -> torch.dtype:
+        return _TORCH_ACT[self.out_dtype]
 
 
 def expert_offsets(config: MoEConfig, shared: bool = False) -> tuple[capi.ExpertOffsets, int]:

@@ -4,14 +4,16 @@ Mirrors the reference's fixture helpers: SplitMix64 / SeedTree
 (sources/ShrikeValidation/Support/PRNG), bf16 helpers and the min/max affine
 quantisers (sources/Shrike/Infrastructure/ModelIO/Quantization.swift:16-191),
 and the packed expert block order (RepackPlanner.swift:735-826). The shapes of
-the five benchmark workloads live here too.
+the five benchmark workloads live here too: activations bf16 (the default of
+MoEConfig) in, fp32 y out, which is the configuration the 1e-3 parity bar is
+stated for.
 """
 from __future__ import annotations
 
 import numpy as np
 
-from . import capi
-from .moe import MoEConfig
+from shrike_b200 import capi
+from shrike_b200.moe import MoEConfig
 
 MASK64 = (1 << 64) - 1
 GOLDEN = 0x9E3779B97F4A7C15
@@ -200,7 +202,7 @@ def qwen_config(max_tokens: int = 16, **kw) -> MoEConfig:
     """Qwen3.5-35B-A3B MoE layer: D 2048, 256 experts top-8, F 512, int4 g64, gated shared expert."""
     base = dict(d=2048, f=512, num_experts=256, top_k=8, weight_bits=4, group_size=64,
                 activation=capi.ACT_SILU, has_shared=True, shared_gated=True, shared_f=512,
-                max_tokens=max_tokens)
+                max_tokens=max_tokens, y_dtype=capi.DTYPE_FP32)
     base.update(kw)
     return MoEConfig(**base)
 
@@ -209,7 +211,7 @@ def gpt_oss_config(max_tokens: int = 64, group_size: int = 32, **kw) -> MoEConfi
     """gpt-oss-20B MoE layer: D = F = 2880, 32 experts top-4, additive biases, clamped SwiGLU, no shared expert."""
     base = dict(d=2880, f=2880, num_experts=32, top_k=4, weight_bits=4, group_size=group_size,
                 activation=capi.ACT_CLAMPED_SWIGLU, expert_bias=True, has_shared=False,
-                max_tokens=max_tokens)
+                max_tokens=max_tokens, y_dtype=capi.DTYPE_FP32)
     base.update(kw)
     return MoEConfig(**base)
 
@@ -218,7 +220,8 @@ def kimi_config(max_tokens: int = 2064, **kw) -> MoEConfig:
     """Kimi-Linear-48B MoE layer: D 2304, 256 experts top-8 sigmoid x2.446, F 1024, int8 g64, ungated shared."""
     base = dict(d=2304, f=1024, num_experts=256, top_k=8, weight_bits=8, group_size=64,
                 activation=capi.ACT_SILU, router_kind=capi.ROUTER_SIGMOID, routed_scaling=2.446,
-                has_shared=True, shared_gated=False, shared_f=1024, max_tokens=max_tokens)
+                has_shared=True, shared_gated=False, shared_f=1024, max_tokens=max_tokens,
+                y_dtype=capi.DTYPE_FP32)
     base.update(kw)
     return MoEConfig(**base)
 

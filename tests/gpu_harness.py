@@ -3,12 +3,14 @@ layer for the CPU oracle, so that parity tests read: run both, compare."""
 from __future__ import annotations
 
 import ctypes as C
+import os
 
 import numpy as np
 import torch
 
 import oracle_lib as O
-from shrike_b200 import capi, fixtures as fx
+from shrike_b200 import capi
+import fixtures as fx
 from shrike_b200.moe import ExpertCellArena, MoE, MoEConfig, RouterOperands, expert_offsets, round_up
 
 
@@ -123,7 +125,7 @@ class Layer:
         if fused:
             ids = torch.empty((T, cfg.top_k), dtype=torch.int32, device=self.device)
             w = torch.empty((T, cfg.top_k), dtype=torch.float32, device=self.device)
-            y = torch.empty_like(x_dev)
+            y = torch.empty(x_dev.shape, dtype=cfg.torch_y_dtype, device=self.device)
             h = None if hidden is None else to_act_tensor(hidden, cfg.act_dtype, self.device)
             st = None if io_status is None else torch.tensor([io_status], dtype=torch.int32, device=self.device)
             self.moe.encode_decode_layer(self.pool, self.offsets, self.layer, self.router_ops, x_dev, y, h,
@@ -133,7 +135,7 @@ class Layer:
                     None if h is None else h.float().cpu().numpy())
         ids, w, gate = self.route(x_dev)
         slots, _ = self.classify(ids)
-        y = torch.empty_like(x_dev)
+        y = torch.empty(x_dev.shape, dtype=cfg.torch_y_dtype, device=self.device)
         h = None if hidden is None else to_act_tensor(hidden, cfg.act_dtype, self.device)
         if prefill is None:
             prefill = T > capi.MAX_DECODE_TOKENS
@@ -176,12 +178,17 @@ class Layer:
         return ids, w, np.stack(logits_all)
 
     def oracle_forward(self, x: np.ndarray, ids: np.ndarray | None = None, weights: np.ndarray | None = None,
-                       threads: int = 8, skip_experts: set | None = None):
+                       threads: int | None = None, skip_experts: set | None = None, rows: np.ndarray | None = None):
+        """The oracle's y for all rows, or for the sample `rows` (full-size workloads: the CPU FFN costs
+        about 10 ms per row at the Qwen shape)."""
         cfg = self.cfg
+        threads = threads or min(32, os.cpu_count() or 8)
         xr = self.act_round(x)
         if ids is None:
             ids, weights, _ = self.oracle_route(x)
         weights = np.array(weights, dtype=np.float32)
+        if rows is not None:
+            xr, ids, weights = xr[rows], ids[rows], weights[rows]
         if skip_experts:
             weights = np.where(np.isin(ids, list(skip_experts)), np.float32(0), weights)
         needed = sorted(set(int(e) for e in ids.ravel()))

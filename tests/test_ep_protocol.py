@@ -18,7 +18,7 @@ def _free_port():
 
 def _layer_inputs():
     import oracle_lib as O
-    from shrike_b200 import fixtures as fx
+    import fixtures as fx
     d, f, ne, k, T = 128, 64, 8, 2, 12
     rng = np.random.default_rng(3)
     x = fx.round_bf16(rng.normal(0, 1, (T, d)).astype(np.float32))

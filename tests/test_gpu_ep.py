@@ -26,7 +26,7 @@ def _config(ne=16, act=None):
 
 
 def _problem(T, cfg, seed=5):
-    from shrike_b200 import fixtures as fx
+    import fixtures as fx
     rng = np.random.default_rng(seed)
     x = fx.round_bf16(rng.normal(0, 1, (T, cfg.d)).astype(np.float32))
     router = rng.normal(0, 0.05, (cfg.num_experts, cfg.d)).astype(np.float32)
@@ -35,7 +35,7 @@ def _problem(T, cfg, seed=5):
 
 def _oracle(cfg, x, router, seed):
     import oracle_lib as O
-    from shrike_b200 import fixtures as fx
+    import fixtures as fx
     T = x.shape[0]
     ids = np.zeros((T, cfg.top_k), np.uint32)
     w = np.zeros((T, cfg.top_k), np.float32)
@@ -51,7 +51,8 @@ def _oracle(cfg, x, router, seed):
 def _run_rank(rank, world, port, T, seed, out_path):
     """One EP rank: builds its shard, runs the layer on its rows, saves y."""
     import torch.distributed as dist
-    from shrike_b200 import capi, fixtures as fx
+    from shrike_b200 import capi
+    import fixtures as fx
     from shrike_b200.ep import ExpertParallelLayer
     from shrike_b200.moe import RouterOperands, expert_offsets
     cfg = _config()

@@ -4,7 +4,8 @@ import numpy as np
 import pytest
 
 from gpu_harness import Layer, inputs, rel_l2
-from shrike_b200 import capi, fixtures as fx
+from shrike_b200 import capi
+import fixtures as fx
 
 pytestmark = pytest.mark.gpu
 
@@ -36,10 +37,21 @@ def test_qwen_layer_decode(cuda_device, T):
     layer.close()
 
 
-def test_qwen_layer_bf16_io_and_fp16_meta(cuda_device):
-    cfg = fx.qwen_config(max_tokens=16, act_dtype=capi.DTYPE_BF16, meta_dtype=capi.DTYPE_FP16)
+@pytest.mark.parametrize("T", [1, 4])
+def test_qwen_layer_bf16_in_fp32_out(cuda_device, T):
+    """The benchmarked configuration: bf16 x in, fp32 accumulate, fp32 y out, at the stated 1e-3 bar."""
+    cfg = fx.qwen_config(max_tokens=16)
+    assert cfg.act_dtype == capi.DTYPE_BF16 and cfg.out_dtype == capi.DTYPE_FP32
     layer = Layer(cfg, seed=102, device_fill=True)
-    run(layer, inputs(2, cfg.d, seed=9), tol=4e-3)  # bf16 store of y: 8 significant bits
+    run(layer, inputs(T, cfg.d, seed=9))
+    run(layer, inputs(T, cfg.d, seed=9), fused=True)
+    layer.close()
+
+
+def test_qwen_layer_fp16_meta(cuda_device):
+    cfg = fx.qwen_config(max_tokens=16, meta_dtype=capi.DTYPE_FP16)
+    layer = Layer(cfg, seed=102, device_fill=True)
+    run(layer, inputs(2, cfg.d, seed=9))
     layer.close()
 
 
@@ -75,6 +87,44 @@ def test_qwen_prefill_zipf_chunk(cuda_device):
     counts = np.bincount(ids.ravel(), minlength=256)
     assert counts.max() >= 20 * max(1, np.median(counts[counts > 0]))
     run(layer, inputs(160, cfg.d, seed=3), prefill=True)
+    layer.close()
+
+
+def sample_rows(T: int, n: int, seed: int) -> np.ndarray:
+    return np.sort(np.random.default_rng(seed).choice(T, size=min(n, T), replace=False))
+
+
+def test_qwen_prefill_full_chunk_4096_rows(cuda_device):
+    """The ragged prefill workload at its full size: 4096 bf16 rows, Zipf(1.1) prior, top-8 of 256, on the
+    tcgen05 path. Routing of every row is checked bit for bit; y against the oracle on a seeded sample of
+    512 rows (the CPU FFN costs about 10 ms per row) plus the 16 rows routed to the most loaded expert."""
+    T = 4096
+    cfg = fx.qwen_config(max_tokens=T)
+    layer = Layer(cfg, seed=107, device_fill=True, logit_bias=fx.zipf_logit_bias(256, 1.1))
+    x = inputs(T, cfg.d, seed=41)
+    y, ids, w, _ = layer.forward(x, prefill=True)
+    ids_ref, w_ref, _ = layer.oracle_route(x)
+    assert (ids == ids_ref).all() and (w == w_ref).all()
+    counts = np.bincount(ids.ravel(), minlength=256)
+    assert counts.max() > 1500 and (counts > 0).sum() > 100   # a few experts take thousands of rows
+    busiest = np.where((ids == counts.argmax()).any(axis=1))[0][:16]
+    rows = np.unique(np.concatenate([sample_rows(T, 512, 7), busiest]))
+    y_ref = layer.oracle_forward(x, ids_ref, w_ref, rows=rows)
+    err = rel_l2(y[rows], y_ref)
+    assert err <= TOL, f"relative L2 {err:.3e}"
+    assert np.isfinite(y).all() and np.abs(y).max() < 1e3
+    print(f"qwen prefill 4096 rows: rel L2 {err:.2e} on {rows.size} sampled rows, busiest expert {counts.max()} rows")
+    layer.close()
+
+
+def test_gpt_oss_64_rows_on_the_expert_grouped_path(cuda_device):
+    """gpt-oss shape, g32, 64 rows on a handle that owns the prefill operands (max_tokens = 128): the layer
+    call takes the tcgen05 path with scale rows of 90 groups (not whole 16-byte units: read by the converter
+    threads) at D = F = 2880."""
+    cfg = fx.gpt_oss_config(max_tokens=128, group_size=32)
+    layer = Layer(cfg, seed=108, device_fill=True)
+    err, gap = run(layer, inputs(64, cfg.d, seed=43), fused=True)
+    print(f"gpt-oss g32 64 rows, grouped path: rel L2 {err:.2e}, min top-k gap {gap:.2e}")
     layer.close()
 
 

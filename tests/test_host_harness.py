@@ -21,7 +21,8 @@ def test_cpp_host_mirror_compiles_and_links():
 @pytest.mark.gpu
 def test_cpp_host_runs_the_layer_like_the_oracle(cuda_device):
     import oracle_lib as O
-    from shrike_b200 import capi, fixtures as fx
+    from shrike_b200 import capi
+    import fixtures as fx
     from shrike_b200.moe import MoEConfig
 
     exe = build.build_harness()

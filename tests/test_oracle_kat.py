@@ -7,7 +7,8 @@ import numpy as np
 import pytest
 
 import oracle_lib as O
-from shrike_b200 import capi, fixtures as fx
+from shrike_b200 import capi
+import fixtures as fx
 from shrike_b200.moe import MoEConfig
 
 
@@ -110,6 +111,61 @@ def test_k4_constant_block(bits):
     w = np.full((1, 8), 0.125, dtype=np.float32)
     y = O.moe_layer(cfg, {e: blob for e in range(8)}, None, None, x, ids, w)
     assert np.abs(y - 2 / (1 + math.exp(-2))).max() < 0.01
+
+
+# K5 -- MoEFusedFFNTests.productionRoutedPipelineSpecHitsAndFixupMissesMatchReference: eight int4 experts
+# drawn from SeedTree(0x2D3)/"production-routed-moe" (weights U(-0.4, 0.4) quantised by the fixture
+# quantiser, x and residual U(-0.5, 0.5) rounded to fp16, route weights fp16(0.04 + 0.015 k)), the
+# routed-only pipeline y = residual + sum_k w_k * down_k(gelu_tanh(gate_k x) * up_k x) of
+# MoeRef.applyStreamedRouted, at the reference's chained-reduction tolerance 1e-2 (max abs / max abs ref).
+def k5_fixture():
+    d, f, k = 128, 64, 8
+    rng = fx.SeedTree(0x2D3).key("production-routed-moe")
+    def mat(rows, cols):
+        return np.array([[rng.uniform(-0.4, 0.4) for _ in range(cols)] for _ in range(rows)], dtype=np.float32)
+    experts = []
+    for _ in range(k):
+        g, u, dn = mat(f, d), mat(f, d), mat(d, f)
+        experts.append(tuple(fx.quantize_affine(m, 4) for m in (g, u, dn)))
+    x = np.array([rng.uniform(-0.5, 0.5) for _ in range(d)], np.float32).astype(np.float16).astype(np.float32)
+    residual = np.array([rng.uniform(-0.5, 0.5) for _ in range(d)], np.float32).astype(np.float16).astype(np.float32)
+    w = np.array([0.04 + 0.015 * i for i in range(k)], np.float32).astype(np.float16).astype(np.float32)
+    expected = residual.astype(np.float64)
+    for (gate, up, down), wk in zip(experts, w):
+        gv = dequant_then_dot(*gate, x).astype(np.float64)
+        uv = dequant_then_dot(*up, x).astype(np.float64)
+        act = 0.5 * gv * (1 + np.tanh(0.7978845608028654 * (gv + 0.044715 * gv ** 3))) * uv
+        expected = expected + float(wk) * dequant_then_dot(*down, act.astype(np.float32))
+    blobs = [fx.pack_expert_block(*e) for e in experts]
+    return d, f, k, blobs, x, residual, w, expected.astype(np.float32)
+
+
+def test_k5_routed_pipeline_matches_the_streamed_reference():
+    d, f, k, blobs, x, residual, w, expected = k5_fixture()
+    out = residual.copy()
+    cfg = O.expert_cfg(d, f, activation=capi.ACT_GELU_TANH)
+    for blob, wk in zip(blobs, w):
+        O.expert_ffn_accumulate(blob, cfg, x, float(wk), out)
+    assert np.abs(out - expected).max() / np.abs(expected).max() < 1e-2
+    # far inside it: the oracle is fp32 throughout, the reference's own kernels round to fp16
+    assert np.abs(out - expected).max() / np.abs(expected).max() < 1e-4
+
+
+def test_router_never_selects_nan_or_minus_infinity():
+    """router_topk_select_body's insertion scan (moe.metal:436-456): a NaN score fails every comparison and
+    -inf is not greater than the initial -inf, so neither is ever inserted; with fewer candidates than top_k
+    the remaining picks keep the initial id 0 and, under softmax, weight exp(-inf - max) = 0."""
+    logits = np.linspace(1.0, 2.0, 16, dtype=np.float32)
+    bias = np.zeros(16, np.float32)
+    bias[15] = -np.inf      # the best score, masked
+    bias[14] = np.nan
+    ids, w = O.router_select(logits, 4, bias=bias, round_f16=False)
+    assert list(ids) == [13, 12, 11, 10] and abs(float(w.sum()) - 1) < 1e-6
+    bias[:] = -np.inf
+    bias[3] = 0.0
+    bias[9] = 0.0
+    ids, w = O.router_select(logits, 4, bias=bias, round_f16=False)
+    assert list(ids) == [9, 3, 0, 0] and w[2] < 1e-30 and w[3] < 1e-30 and abs(float(w[:2].sum()) - 1) < 1e-6
 
 
 # K6 -- gpt-oss expert: additive biases + clamped SwiGLU (MoeRef.runFFNGptOss)

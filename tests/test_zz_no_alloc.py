@@ -49,6 +49,47 @@ def test_static_router_equals_the_handle_router_twice_in_a_row(cuda_device, kw, 
     layer.close()
 
 
+def test_static_router_matches_the_oracle_and_leaves_free_memory_alone(cuda_device):
+    """The property in the entry point's name: repeated calls change neither the device's free memory
+    (cudaMemGetInfo) nor torch's allocator statistics, and the answers are the oracle's, bit for bit."""
+    layer = Layer(small_config(d=256, num_experts=64, top_k=8))
+    cfg = layer.cfg
+    x = inputs(32, cfg.d, seed=7)
+    x_dev = to_act_tensor(x, cfg.act_dtype, layer.device)
+    ids = torch.zeros((32, 8), dtype=torch.int32, device=layer.device)
+    w = torch.zeros((32, 8), dtype=torch.float32, device=layer.device)
+    g = torch.zeros(32, dtype=torch.float32, device=layer.device)
+    encode_router_static(cfg, layer.router_ops, x_dev, ids, w, g)   # the first call looks the array's address up
+    torch.cuda.synchronize()
+    free0, _ = torch.cuda.mem_get_info()
+    reserved0 = torch.cuda.memory_reserved()
+    for _ in range(5):
+        encode_router_static(cfg, layer.router_ops, x_dev, ids, w, g)
+    torch.cuda.synchronize()
+    free1, _ = torch.cuda.mem_get_info()
+    assert free1 == free0 and torch.cuda.memory_reserved() == reserved0
+    ids_ref, w_ref, _ = layer.oracle_route(x)
+    assert (ids.cpu().numpy().astype(np.uint32) == ids_ref).all()
+    assert (w.cpu().numpy() == w_ref).all()
+    layer.close()
+
+
+def test_static_router_asks_for_the_gate_operands_like_the_handle_call(cuda_device):
+    layer = Layer(small_config())   # shared_gated
+    x_dev = to_act_tensor(inputs(2, 128, seed=1), layer.cfg.act_dtype, layer.device)
+    ids = torch.zeros((2, 4), dtype=torch.int32, device=layer.device)
+    w = torch.zeros((2, 4), dtype=torch.float32, device=layer.device)
+    with pytest.raises(ShrikeError) as e:
+        encode_router_static(layer.cfg, layer.router_ops, x_dev, ids, w, None)
+    assert e.value.code == capi.EINVAL and "shared_gate" in str(e.value)
+    with pytest.raises(ShrikeError) as e:   # an offset view: 4-byte aligned only
+        base = torch.zeros(2 * 128 + 4, dtype=torch.float32, device=layer.device)
+        g = torch.zeros(2, dtype=torch.float32, device=layer.device)
+        encode_router_static(layer.cfg, layer.router_ops, base[1:1 + 256].view(2, 128), ids, w, g)
+    assert e.value.code == capi.EINVAL and "aligned" in str(e.value)
+    layer.close()
+
+
 def test_static_router_refuses_what_its_array_cannot_hold(cuda_device):
     layer = Layer(small_config(max_tokens=128))
     x_dev = to_act_tensor(inputs(65, 128, seed=1), layer.cfg.act_dtype, layer.device)
