@@ -5,10 +5,15 @@
   python bench.py [--gpus N] [--steps K] [--warmup W] [--tokens T] [--impl ours|reference]
 
 A step is one pass of T tokens (default 1) through all layers: router -> top-8 ->
-residency lookup -> shared + routed expert FFN -> combine, hidden += y feeding the
-next layer. Prints ONE JSON line. With N > 1 (torchrun) every rank runs an
-independent replica of the workload on its own GPU (the single-GPU workloads do
-not shard; no collective on the data path) and the value is the aggregate.
+residency lookup -> shared + routed expert FFN -> combine; the output joins the residual stream that feeds the
+next layer (stream_rows). Prints ONE JSON line.
+
+N = 1: the line also carries compact blocks for the other workloads -- `sweep` (batch 4 and 16),
+`prefill` (4096 ragged rows on the tensor cores), `gptoss` (1 and 64 rows) -- and the CPU baseline.
+N > 1 (torchrun): `value` is N independent replicas of the decode sweep (the single-GPU workloads do
+not shard; no collective on their data path), and the `ep` block is the expert-parallel workload
+(Kimi-Linear shape, experts sharded over the N ranks, rows dispatched and combined over NVLink)
+measured in the same job, with the same rank's one-GPU time measured first.
 """
 from __future__ import annotations
 
@@ -31,6 +36,9 @@ sys.path.insert(1, str(ROOT / "tests"))   # fixtures, the oracle bindings and th
 SEED = 20240
 LAYERS = 40
 METRIC = "MoE-FFN tokens/s and HBM GB/s vs 8 TB/s peak at 1/2/4/8 B200"
+# dram__bytes_read.sum + dram__bytes_write.sum of one decode_layer_kernel launch over its algorithmic bytes,
+# from the ncu capture summarised in profiles/decode_layer_kernel_qwen_batch1.md
+TRAFFIC_RATIO = None
 
 
 def parse_args():
@@ -41,10 +49,10 @@ def parse_args():
     ap.add_argument("--tokens", type=int, default=1, help="decode batch: 1, 4 or 16")
     ap.add_argument("--layers", type=int, default=LAYERS)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--workload", choices=["decode", "prefill", "ep", "gptoss"], default="decode",
-                    help="decode: the 40-layer sweep (headline); prefill: one layer, 4096 rows, Zipf(1.1)-skewed routing")
+    ap.add_argument("--workload", choices=["all", "decode", "prefill", "ep", "gptoss"], default="all",
+                    help="all: the headline decode sweep plus the compact blocks of the other workloads; "
+                         "one name: that workload alone (decode = the headline line without the extra blocks)")
     ap.add_argument("--rows", type=int, default=4096, help="rows of the prefill workload")
-    ap.add_argument("--no-sweep", action="store_true", help="skip the T=4 / T=16 lines of the sweep")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     return ap.parse_args()
 
@@ -53,8 +61,8 @@ def measured_peaks():
     p = ROOT / "MEASURED_PEAKS.json"
     if p.exists():
         d = json.loads(p.read_text())
-        return float(d["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
-    return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+        return float(d["hbm_gbs"]), float(d["bf16_tflops"]), "measured (MEASURED_PEAKS.json: hbm_gbs, bf16_tflops burst)"
+    return 6650.0, 1590.0, "fallback (6.65 TB/s, 1.59 PFLOP/s: earlier measurements on this pool)"
 
 
 def router_weights(layer: int, ne: int, d: int) -> np.ndarray:
@@ -65,9 +73,18 @@ def gate_weights(layer: int, d: int) -> np.ndarray:
     return np.random.default_rng(SEED * 1000 + 500 + layer).normal(0, 0.02, d).astype(np.float32)
 
 
-def input_tokens(T: int, d: int) -> np.ndarray:
+def input_tokens(T: int, d: int, seed: int = SEED) -> np.ndarray:
     import fixtures as fx
-    return fx.round_bf16(np.random.default_rng(SEED).normal(0, 1, (T, d)).astype(np.float32))
+    return fx.round_bf16(np.random.default_rng(seed).normal(0, 1, (T, d)).astype(np.float32))
+
+
+def stream_rows(L: int, T: int, d: int) -> np.ndarray:
+    """The residual stream of the stacked workload, [(L + 1) x T x d] bf16 N(0,1): block 0 enters layer 0, block
+    l stands for what the rest of transformer block l (attention + normalisation, not part of this path) adds
+    between MoE layer l-1 and MoE layer l. Layer l's input is block l + y of layer l-1, so every layer's routing
+    depends on the layer before it, and the stream keeps unit scale (fed back unnormalised, the quadratic
+    SwiGLU of 40 synthetic layers overflows fp16 within 8 layers)."""
+    return np.stack([input_tokens(T, d, SEED + 17 * l) for l in range(L + 1)])
 
 
 # ------------------------------------------------------------------ clocks
@@ -121,7 +138,6 @@ class ClockSampler:
 def cpu_reference_run(T: int, layers: int, steps: int, warmup: int, budget_s: float):
     """The reference's CPU implementation of the path on the host cores: its own compiled
     int4 GEMV (oracle/_ref) under the restated expert FFN, router and combine (oracle/)."""
-    sys.path.insert(0, str(ROOT / "tests"))
     import oracle_lib as O
     import fixtures as fx
 
@@ -130,7 +146,7 @@ def cpu_reference_run(T: int, layers: int, steps: int, warmup: int, budget_s: fl
     cores = os.cpu_count() or 1
     ecfg = O.expert_cfg(cfg.d, cfg.f)
     lcfg = O.layer_cfg(ecfg, O.expert_cfg(cfg.d, cfg.shared_f), True)
-    x0 = input_tokens(T, cfg.d)
+    rows = stream_rows(layers, T, cfg.d)
     routers = [router_weights(l, cfg.num_experts, cfg.d) for l in range(layers)]
     gates = [gate_weights(l, cfg.d) for l in range(layers)]
     shared = [O.synth_block(O.expert_cfg(cfg.d, cfg.shared_f), SEED, l, 100000) for l in range(layers)]
@@ -142,7 +158,7 @@ def cpu_reference_run(T: int, layers: int, steps: int, warmup: int, budget_s: fl
         return cache[(l, e)]
 
     def step():
-        h = x0.copy()
+        h = rows[0].copy()
         for l in range(layers):
             ids = np.zeros((T, cfg.top_k), np.uint32)
             w = np.zeros((T, cfg.top_k), np.float32)
@@ -150,7 +166,7 @@ def cpu_reference_run(T: int, layers: int, steps: int, warmup: int, budget_s: fl
                 ids[t], w[t] = O.router_select(O.router_logits_f32(routers[l], h[t]), cfg.top_k, round_f16=True)
             blocks = {int(e): block(l, int(e)) for e in np.unique(ids)}
             y = O.moe_layer(lcfg, blocks, shared[l], gates[l], h, ids, w, threads=cores)
-            h = fx.round_bf16(h + fx.round_bf16(y))
+            h = fx.round_bf16(rows[l + 1] + y)
         return h
 
     step()  # generates and caches the blocks the routing touches; not timed
@@ -166,12 +182,14 @@ def cpu_reference_run(T: int, layers: int, steps: int, warmup: int, budget_s: fl
             break
     O.use_reference_gemv(False)
     ms = 1e3 * sum(times) / len(times)
+    tasks = T * cfg.top_k + T
     return {"value": T / (ms / 1e3), "unit": "tokens/s", "cores": cores, "kind": kind,
-            "sample": f"{len(times)} steps of {T} token(s) x {layers} layers (router + 8 routed + 1 shared expert per layer), "
-                      f"{cores} threads over experts", "ms_per_step": ms, "steps": len(times)}
+            "sample": f"{len(times)} steps of {T} token(s) x {layers} layers (router + 8 routed + 1 shared expert per layer); "
+                      f"one thread per expert task: {min(tasks, cores)} of {cores} host threads busy, "
+                      f"{max(0, cores - tasks)} idle", "ms_per_step": ms, "steps": len(times)}
 
 
-# ------------------------------------------------------------------ our arm
+# ------------------------------------------------------------------ the decode stack
 
 class Workload:
     """All layers resident on one GPU; per-layer handles so that every layer keeps its own work lists."""
@@ -180,7 +198,7 @@ class Workload:
         import torch
         from shrike_b200 import capi
         import fixtures as fx
-        from shrike_b200.moe import ExpertCellArena, MoE, RouterOperands, expert_offsets, round_up
+        from shrike_b200.moe import DecodeStack, ExpertCellArena, MoE, RouterOperands, expert_offsets, round_up
 
         self.torch = torch
         self.T, self.L = T, layers
@@ -209,48 +227,29 @@ class Workload:
                                if cfg.has_shared else None)
         k = cfg.top_k
         self.ids = [torch.zeros((T, k), dtype=torch.int32, device=self.dev) for _ in range(layers)]
-        self.slots = [torch.zeros((T, k), dtype=torch.int32, device=self.dev) for _ in range(layers)]
         self.w = [torch.zeros((T, k), dtype=torch.float32, device=self.dev) for _ in range(layers)]
-        self.gate = [torch.zeros(T, dtype=torch.float32, device=self.dev) for _ in range(layers)]
-        self.x_host = torch.from_numpy(input_tokens(T, cfg.d)).to(torch.bfloat16).pin_memory()
-        self.out_host = torch.empty_like(self.x_host).pin_memory()
-        self.x0 = self.x_host.to(self.dev)
-        self.hidden = torch.zeros_like(self.x0)
-        self.y = torch.zeros_like(self.x0)
-        self.launches_per_step = layers * 3
+        self.rows_host = torch.from_numpy(stream_rows(layers, T, cfg.d)).to(torch.bfloat16).pin_memory()
+        self.out_host = torch.empty((T, cfg.d), dtype=torch.bfloat16).pin_memory()
+        self.rows0 = self.rows_host.to(self.dev)
+        self.stream = torch.zeros_like(self.rows0)
+        self.y = torch.zeros((T, cfg.d), dtype=cfg.torch_y_dtype, device=self.dev)
+        self.stack = DecodeStack([(self.moes[l], self.pool, self.off, 0, self.routers[l], self.shared[l])
+                                  for l in range(layers)], T)
+        # kernels of this library per layer call: one row = the single fused launch; up to 16 rows = route +
+        # phase 1 + phase 2; more (on a handle that owns the prefill operands) = the expert-grouped path
+        self.launches_per_step = layers * (1 if T == 1 else 3 if T <= 16 else 14)
         torch.cuda.synchronize()
 
-    def layers_on_device(self):
-        """router -> classification -> plan -> phase 1 -> phase 2 for every layer; hidden carries on."""
-        for l in range(self.L):
-            self.moes[l].encode_decode_layer(self.pool, self.off, 0, self.routers[l], self.hidden, self.y,
-                                             self.hidden, self.shared[l], self.ids[l], self.w[l])
-
     def step_resident(self):
-        self.hidden.copy_(self.x0)
-        self.layers_on_device()
-
-    def step_e2e(self):
-        self.hidden.copy_(self.x_host, non_blocking=True)
-        self.layers_on_device()
-        self.out_host.copy_(self.hidden, non_blocking=True)
-
-    def build_work_lists(self):
-        """The per-phase graphs run the expert kernels from work lists; the one-row layer call routes inside the
-        expert kernels and leaves none, so the route kernel builds them here (outside any timed region)."""
+        """Inputs already in HBM: one device copy re-arms the residual stream, then every layer call."""
+        self.stream.copy_(self.rows0)
         for l in range(self.L):
-            self.moes[l].encode_route_decode(self.routers[l], 0, self.pool, self.hidden, self.ids[l], self.w[l],
-                                             self.gate[l] if self.cfg.shared_gated else None)
-        self.torch.cuda.synchronize()
+            self.moes[l].encode_decode_layer(self.pool, self.off, 0, self.routers[l], self.stream[l], self.y,
+                                             self.stream[l + 1], self.shared[l], self.ids[l], self.w[l])
 
-    def phase1_only(self):
-        for l in range(self.L):
-            self.moes[l].encode_phase1(self.pool, self.off, self.T, self.shared[l])
-
-    def phase2_only(self):
-        for l in range(self.L):
-            self.moes[l].encode_phase2_reduce(self.pool, self.off, self.w[l], self.y, self.T, None, self.shared[l],
-                                              self.gate[l] if self.cfg.shared_gated else None)
+    def step_host(self):
+        """One step through the C-ABI entry point for host buffers: H2D of the rows, every layer, D2H, sync."""
+        self.stack.forward_host(self.rows_host, self.out_host)
 
     def capture(self, fn):
         torch = self.torch
@@ -279,6 +278,15 @@ class Workload:
         torch.cuda.synchronize()
         return e0.elapsed_time(e1) / steps
 
+    def time_host(self, steps: int, warmup: int) -> float:
+        """Mean ms per host-buffer step (every call ends with a stream synchronise)."""
+        for _ in range(warmup):
+            self.step_host()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            self.step_host()
+        return 1e3 * (time.perf_counter() - t0) / steps
+
     def distinct_experts(self):
         return [int(self.torch.unique(self.ids[l]).numel()) for l in range(self.L)]
 
@@ -287,19 +295,19 @@ class Workload:
             m.status()
 
     def close(self):
+        self.stack.close()
         self.pool.close()
         for m in self.moes:
             m.close()
 
 
-def run_ours(args, rank: int, world: int, local_rank: int):
+def run_decode(T: int, L: int, K: int, W: int, rank: int, world: int, local_rank: int, cfg=None):
+    """The stacked decode sweep on this rank's GPU: (ms per device-resident step, ms per host-buffer step,
+    bytes of distinct expert blocks a layer streams, the workload)."""
     import torch
     import torch.distributed as dist
-
-    T, L, K, W = args.tokens, args.layers, args.steps, max(3, args.warmup)
-    wl = Workload(T, L, local_rank)
+    wl = Workload(T, L, local_rank, cfg)
     g_step = wl.capture(wl.step_resident)
-    g_e2e = wl.capture(wl.step_e2e)
     wl.check_status()
 
     def barrier():
@@ -307,88 +315,92 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             dist.barrier()
         torch.cuda.synchronize()
 
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
     barrier()
     ms = wl.time_graph(g_step, K, W)
     barrier()
-    ms_e2e = wl.time_graph(g_e2e, K, W)
+    ms_host = wl.time_host(K, W)
     barrier()
-    clocks = sampler.stop() if rank == 0 else None
     if world > 1:
-        t = torch.tensor([ms, ms_e2e], dtype=torch.float64, device=wl.dev)
+        t = torch.tensor([ms, ms_host], dtype=torch.float64, device=wl.dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, ms_e2e = float(t[0]), float(t[1])
+        ms, ms_host = float(t[0]), float(t[1])
     wl.check_status()
+    units = [u + (1 if wl.cfg.has_shared else 0) for u in wl.distinct_experts()]
+    return ms, ms_host, sum(units) / L * wl.block_bytes, wl
 
-    # roofline of the dominant kernel (phase 1: gate/up dequant-GEMV + GLU), timed alone:
-    # one launch per layer, each on a different layer's cold expert blocks
+
+def decode_line(args, rank: int, world: int, local_rank: int):
+    T, L, K, W = args.tokens, args.layers, args.steps, max(3, args.warmup)
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ms, ms_host, layer_bytes, wl = run_decode(T, L, K, W, rank, world, local_rank)
+    clocks = sampler.stop() if rank == 0 else None
     cfg = wl.cfg
-    o = wl.off
-    gate_up_bytes = o.down_w                      # gate + up sub-tensors of one block
-    down_bytes = wl.block_bytes - o.down_w
-    distinct = wl.distinct_experts()
-    wl.build_work_lists()
-    g_p1 = wl.capture(wl.phase1_only)
-    g_p2 = wl.capture(wl.phase2_only)
-    ms_p1 = wl.time_graph(g_p1, max(10, K // 2), 3) / L
-    ms_p2 = wl.time_graph(g_p2, max(10, K // 2), 3) / L
-    units = [u + 1 for u in distinct]             # + the shared expert
-    mean_units = sum(units) / L
-    peak, peak_src = measured_peaks()
-    # dram__bytes_read + dram__bytes_write of one phase-1 launch from the ncu capture summarised in
-    # profiles/phase1_kernel_qwen_batch1.md: 10,654,848 B for 9 experts, i.e. 1.0036 x the algorithmic bytes;
-    # traffic grows with the experts a launch touches, so it is scaled by the units of this run.
-    traffic = mean_units * 10_654_848 / 9.0
-    p1_gbs = mean_units * gate_up_bytes / (ms_p1 * 1e-3) / 1e9
-    p2_gbs = mean_units * down_bytes / (ms_p2 * 1e-3) / 1e9
-    layer_gbs = mean_units * wl.block_bytes / (ms / L * 1e-3) / 1e9
-
+    hbm, _, src = measured_peaks()
+    gbs = layer_bytes / (ms / L * 1e-3) / 1e9
+    kernel = ("decode_layer_kernel<4,64,bf16> (router + top-8 + lookup + gate/up + GLU + down + combine of one row, one launch)"
+              if T == 1 else "route_fused_kernel + phase1_kernel<4,64,bf16> + phase2_kernel<4,64,bf16>")
     line = None
     if rank == 0:
         tokens = T * world
         line = {
             "metric": METRIC, "value": tokens / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": K,
             "warmup": W, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "int4 weights x fp16 operands, fp32 accumulate", "data": "synthetic",
+            "dtype": "int4 weights x fp16 operands, fp32 accumulate; bf16 x in, fp32 y out", "data": "synthetic",
             "config": {
                 "workload": f"qwen3.5-35b-a3b expert shape, {L}-layer decode sweep, batch {T} "
                             f"(D 2048, 256 experts top-8 + gated shared, F 512, int4 g64 bf16 meta)",
                 "tokens_per_step_per_gpu": T, "layers": L, "parallelism": "replicas" if world > 1 else "single",
-                "l2": "inputs larger than L2: every step streams "
-                      f"{mean_units * wl.block_bytes * L / 1e6:.0f} MB of distinct expert blocks (L2 126 MB)",
-                "pool_gb": wl.pool.cells * wl.pool.cell_stride / 1e9,
+                "l2": f"inputs larger than L2: every step streams {layer_bytes * L / 1e6:.0f} MB of distinct expert "
+                      "blocks (L2 126 MB)",
+                "stream": "layer l's input = seeded N(0,1) row l (standing for attention + norm) + y of layer l-1",
+                "pool_gb": round(wl.pool.cells * wl.pool.cell_stride / 1e9, 2),
             },
-            "hbm_gbs_per_layer": layer_gbs,
-            "roofline": {"bound": "hbm", "kernel": "phase1_kernel<4,64,bf16>", "achieved": p1_gbs, "peak": peak,
-                         "unit": "GB/s", "frac": p1_gbs / peak, "peak_source": peak_src, "traffic": traffic,
-                         "algorithmic_bytes_per_launch": mean_units * gate_up_bytes, "us_per_launch": ms_p1 * 1e3,
-                         "phase2": {"achieved": p2_gbs, "frac": p2_gbs / peak, "us_per_launch": ms_p2 * 1e3,
-                                    "algorithmic_bytes_per_launch": mean_units * down_bytes},
-                         "whole_layer": {"achieved": layer_gbs, "frac": layer_gbs / peak,
-                                         "us_per_layer": ms / L * 1e3}},
-            "e2e": {"value": tokens / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e,
-                    "h2d_bytes_per_step": T * cfg.d * 2, "d2h_bytes_per_step": T * cfg.d * 2},
+            "roofline": {"bound": "hbm", "kernel": kernel, "achieved": gbs, "peak": hbm, "unit": "GB/s",
+                         "frac": gbs / hbm, "whole_layer_frac": gbs / hbm, "peak_source": src,
+                         "traffic": layer_bytes * TRAFFIC_RATIO if (TRAFFIC_RATIO and T == 1) else None,
+                         "algorithmic_bytes_per_launch": layer_bytes, "us_per_launch": ms / L * 1e3,
+                         "note": "a launch is a whole layer; its time is the step's CUDA-event time / layers, "
+                                 "launch hand-over included"},
+            "e2e": {"value": tokens / (ms_host * 1e-3), "unit": "tokens/s", "ms_per_step": ms_host,
+                    "h2d_bytes_per_step": (L + 1) * T * cfg.d * 2, "d2h_bytes_per_step": T * cfg.d * 2,
+                    "api": "shrike_decode_stack_forward_host (pinned host rows in, every layer call, host rows out, sync)"},
             "gpu_launches": wl.launches_per_step * K,
-            "distinct_experts_per_layer": sum(distinct) / L,
+            "distinct_experts_per_layer": layer_bytes / wl.block_bytes - 1,
             "clocks": clocks,
         }
     wl.close()
     return line
 
 
-def run_prefill(args, local_rank: int):
+# ------------------------------------------------------------------ compact blocks of the other workloads
+
+def sweep_block(args, local_rank: int) -> dict:
+    out = {}
+    hbm, _, _ = measured_peaks()
+    for T in (4, 16):
+        K = max(10, args.steps // 4)
+        ms, ms_host, layer_bytes, wl = run_decode(T, args.layers, K, 3, 0, 1, local_rank)
+        L = args.layers
+        gbs = layer_bytes / (ms / L * 1e-3) / 1e9
+        out[f"batch_{T}"] = {"tokens_per_s": round(T / (ms * 1e-3), 1), "e2e_tokens_per_s": round(T / (ms_host * 1e-3), 1),
+                             "us_per_layer": round(ms / L * 1e3, 2), "hbm_gbs": round(gbs, 1), "frac": round(gbs / hbm, 4),
+                             "distinct_experts_per_layer": round(layer_bytes / wl.block_bytes - 1, 1)}
+        wl.close()
+    return out
+
+
+def prefill_block(args, local_rank: int) -> dict:
     """Ragged prefill through one Qwen-shape int4 layer: rows routed top-8 of 256 with a Zipf(1.1) prior on the
     expert ids, permuted by expert on the device, expert-grouped GEMM on the tcgen05 tensor cores."""
     import torch
     from shrike_b200 import capi
     import fixtures as fx
     from shrike_b200.moe import ExpertCellArena, MoE, RouterOperands, expert_offsets, round_up
-    sys.path.insert(0, str(ROOT / "tests"))
     from gpu_harness import bf16_tensor
 
-    T, K, W = args.rows, args.steps, max(3, args.warmup)
+    T, K, W = args.rows, max(10, args.steps // 4), 3
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     cfg = fx.qwen_config(max_tokens=T)
@@ -405,9 +417,9 @@ def run_prefill(args, local_rank: int):
                          shared_gate=torch.from_numpy(gate_weights(0, cfg.d)).to(dev),
                          logit_bias=bf16_tensor(fx.zipf_logit_bias(cfg.num_experts, 1.1), dev))
     x_host = torch.from_numpy(input_tokens(T, cfg.d)).to(torch.bfloat16).pin_memory()
-    y_host = torch.empty_like(x_host).pin_memory()
+    y_host = torch.empty(x_host.shape, dtype=cfg.torch_y_dtype).pin_memory()
     x = x_host.to(dev)
-    y = torch.empty_like(x)
+    y = torch.empty(x.shape, dtype=cfg.torch_y_dtype, device=dev)
     ids = torch.zeros((T, cfg.top_k), dtype=torch.int32, device=dev)
     slots = torch.zeros_like(ids)
     w = torch.zeros((T, cfg.top_k), dtype=torch.float32, device=dev)
@@ -424,11 +436,6 @@ def run_prefill(args, local_rank: int):
         route()
         experts()
 
-    def step_e2e():
-        x.copy_(x_host, non_blocking=True)
-        step()
-        y_host.copy_(y, non_blocking=True)
-
     def timed(fn, steps, warm):
         for _ in range(warm):
             fn()
@@ -441,170 +448,143 @@ def run_prefill(args, local_rank: int):
         torch.cuda.synchronize()
         return e0.elapsed_time(e1) / steps
 
-    sampler = ClockSampler(local_rank)
-    sampler.start()
     ms = timed(step, K, W)
+    ms_router = timed(route, K, 2)
     ms_experts = timed(experts, K, 2)
-    ms_e2e = timed(step_e2e, K, 2)
-    clocks = sampler.stop()
+    # end to end through the host-buffer entry point: H2D of the rows, router, classification, experts, D2H, sync
+    for _ in range(2):
+        moe.layer_forward_host(pool, off, 0, ops, x_host, y_host, shared)
+    t0 = time.perf_counter()
+    for _ in range(K):
+        moe.layer_forward_host(pool, off, 0, ops, x_host, y_host, shared)
+    ms_e2e = 1e3 * (time.perf_counter() - t0) / K
     moe.status()
     counts = torch.bincount(ids.flatten().long(), minlength=cfg.num_experts).cpu().numpy()
     flops = 6.0 * cfg.d * cfg.f * T * cfg.top_k + 6.0 * cfg.d * cfg.shared_f * T
-    peak = 1590.0
-    src = "fallback (1.59 PFLOP/s)"
-    pk = ROOT / "MEASURED_PEAKS.json"
-    if pk.exists():
-        peak = float(json.loads(pk.read_text())["bf16_tflops"])
-        src = "measured (MEASURED_PEAKS.json bf16_tflops, burst)"
+    _, peak, src = measured_peaks()
     tf = flops / (ms_experts * 1e-3) / 1e12
-    line = {
-        "metric": METRIC, "value": T / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
-        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "int4 weights dequantised to fp16 operands, fp32 accumulate (TMEM)", "data": "synthetic",
-        "config": {"workload": f"ragged prefill, one qwen3.5-35b-a3b-shape int4 layer, {T} rows, top-8 of 256, "
-                               "Zipf(1.1) prior on the router logits, gated shared expert",
-                   "rows_per_expert_max": int(counts.max()), "rows_per_expert_median": float(np.median(counts)),
-                   "experts_hit": int((counts > 0).sum()),
-                   "l2": "inputs larger than L2: 453 MB of expert blocks + 268 MB of per-pair rows per step"},
-        "roofline": {"bound": "tensor", "kernel": "umma_expert_kernel<4,64,bf16,{0,1}> (+ plan, combine)",
-                     "achieved": tf, "peak": peak, "unit": "TFLOP/s", "frac": tf / peak, "peak_source": src,
-                     "traffic": None, "algorithmic_flops": flops, "ms_experts": ms_experts},
-        "e2e": {"value": T / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e,
-                "h2d_bytes_per_step": T * cfg.d * 2, "d2h_bytes_per_step": T * cfg.d * 2},
-        "gpu_launches": K * 12, "clocks": clocks,
-    }
+    out = {"workload": f"ragged prefill, one qwen-shape int4 layer, {T} rows, top-8 of 256, Zipf(1.1) router prior",
+           "rows_per_s": round(T / (ms * 1e-3)), "ms_per_step": round(ms, 4), "ms_router": round(ms_router, 4),
+           "ms_experts": round(ms_experts, 4), "tflops": round(tf, 1), "peak_tflops": peak, "frac": round(tf / peak, 4),
+           "bound": "tensor", "kernel": "umma_expert_kernel<4,64,bf16,{0,1}> (+ plan, combine)",
+           "e2e_rows_per_s": round(T / (ms_e2e * 1e-3)), "h2d_bytes": T * cfg.d * 2, "d2h_bytes": T * cfg.d * 4,
+           "experts_hit": int((counts > 0).sum()), "rows_per_expert_max": int(counts.max())}
     pool.close()
     moe.close()
-    return line
+    return out
 
 
-
-def run_gptoss(args, local_rank: int):
+def gptoss_block(args, local_rank: int) -> dict:
     """gpt-oss-20B-shape layers (D = F = 2880, 32 experts top-4, int4 g32, additive biases, clamped SwiGLU, no
-    shared expert) at --tokens rows (1 or 64): 8 independently seeded layers chained like the decode sweep, so
-    every layer call streams its own cold expert blocks."""
-    import torch
+    shared expert) at 1 and 64 rows: 8 independently seeded layers chained like the decode sweep."""
     import fixtures as fx
-    T, L, K, W = args.tokens, min(args.layers, 8), args.steps, max(3, args.warmup)
-    cfg = fx.gpt_oss_config(max_tokens=128)
-    wl = Workload(T, L, local_rank, cfg)
-    g_step = wl.capture(wl.step_resident)
-    g_e2e = wl.capture(wl.step_e2e)
-    sampler = ClockSampler(local_rank)
-    sampler.start()
-    ms = wl.time_graph(g_step, K, W)
-    ms_e2e = wl.time_graph(g_e2e, K, W)
-    clocks = sampler.stop()
-    wl.check_status()
-    distinct = wl.distinct_experts()
-    mean_units = sum(distinct) / L
-    peak, peak_src = measured_peaks()
-    gbs = mean_units * wl.block_bytes / (ms / L * 1e-3) / 1e9
-    line = {
-        "metric": METRIC, "value": T / (ms / 1e3) , "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
-        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "int4 weights x fp16 operands, fp32 accumulate", "data": "synthetic",
-        "config": {"workload": f"gpt-oss-20b expert shape, {L} chained layers, batch {T} (D 2880, F 2880, 32 experts top-4, "
-                               "int4 g32, bf16 additive biases, clamped SwiGLU)",
-                   "layers": L, "distinct_experts_per_layer": mean_units,
-                   "l2": f"inputs larger than L2: {mean_units * L * wl.block_bytes / 1e6:.0f} MB of distinct expert "
-                         "blocks per step"},
-        "roofline": {"bound": "hbm", "kernel": "whole layer call (one row: route + phase 1 + phase 2; more than 16 rows: router + expert-grouped tcgen05 path)", "achieved": gbs, "peak": peak,
-                     "unit": "GB/s", "frac": gbs / peak, "peak_source": peak_src, "traffic": None,
-                     "us_per_layer": ms / L * 1e3},
-        "e2e": {"value": T / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e,
-                "h2d_bytes_per_step": wl.x_host.numel() * 2, "d2h_bytes_per_step": wl.out_host.numel() * 2},
-        "gpu_launches": (K + W) * wl.launches_per_step, "clocks": clocks,
-    }
-    wl.close()
-    return line
+    hbm, _, _ = measured_peaks()
+    out = {"workload": "gpt-oss-20b expert shape, 8 chained layers (D 2880, F 2880, 32 experts top-4, int4 g32, "
+                       "bf16 additive biases, clamped SwiGLU)"}
+    for T in (1, 64):
+        cfg = fx.gpt_oss_config(max_tokens=128)
+        K = max(10, args.steps // 4)
+        ms, ms_host, layer_bytes, wl = run_decode(T, 8, K, 3, 0, 1, local_rank, cfg)
+        gbs = layer_bytes / (ms / 8 * 1e-3) / 1e9
+        out[f"rows_{T}"] = {"tokens_per_s": round(T / (ms * 1e-3), 1), "e2e_tokens_per_s": round(T / (ms_host * 1e-3), 1),
+                            "us_per_layer": round(ms / 8 * 1e3, 2), "hbm_gbs": round(gbs, 1), "frac": round(gbs / hbm, 4),
+                            "distinct_experts_per_layer": round(layer_bytes / wl.block_bytes, 1)}
+        wl.close()
+    return out
 
 
-def run_ep(args, rank: int, world: int, local_rank: int):
+def ep_block(args, rank: int, world: int, local_rank: int) -> dict:
     """Expert-parallel Kimi-Linear-shape layer (int8 g64, 256 experts top-8 sigmoid, shared expert): every rank
-    holds 256/N experts and its own mixed batch of 16 decode rows + one 2048-row prefill chunk; rows are
-    dispatched and combined with all-to-all over NCCL. Weak scaling: N x 2064 rows per step."""
+    brings its own mixed batch of 16 decode rows + one 2048-row prefill chunk (weak scaling: N x 2064 rows per
+    step). Measured twice in this process: with all 256 experts on this rank alone (world 1, no exchange), then
+    with the experts sharded over the N ranks and the rows dispatched and combined over NVLink."""
     import torch
     import torch.distributed as dist
     from shrike_b200 import capi
     import fixtures as fx
     from shrike_b200.ep import ExpertParallelLayer
     from shrike_b200.moe import RouterOperands, expert_offsets
+    from gpu_harness import bf16_tensor
 
-    rows, K, W = 16 + 2048, args.steps, max(3, args.warmup)
+    rows, K, W = 16 + 2048, max(10, args.steps // 4), 3
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     cfg = fx.kimi_config(max_tokens=rows)
-    group = None
-    layer = ExpertParallelLayer(cfg, rank, world, local_rank, rows, group)
-    layer.pool.fill_synthetic(0, layer.epr, SEED, 0, first_expert=layer.lo)
-    soff, sbytes = expert_offsets(cfg, shared=True)
+    soff, _ = expert_offsets(cfg, shared=True)
     sh = torch.from_numpy(fx.synth_block(cfg, SEED, 0, 100000, shared=True).copy()).to(dev)
-    layer.set_shared(capi.SharedExpert(sh.data_ptr(), soff))
-    sys.path.insert(0, str(ROOT / "tests"))
-    from gpu_harness import bf16_tensor
     correction = np.random.default_rng(SEED + 7).uniform(-0.1, 0.1, cfg.num_experts).astype(np.float32)
     ops = RouterOperands(weights=torch.from_numpy(router_weights(0, cfg.num_experts, cfg.d)).to(dev),
                          logit_bias=bf16_tensor(correction, dev))
-    # every rank routes its own rows
-    xr = np.random.default_rng(SEED + 1000 + rank).normal(0, 1, (rows, cfg.d)).astype(np.float32)
-    x_host = torch.from_numpy(xr).to(torch.bfloat16).pin_memory()
-    y_host = torch.empty_like(x_host).pin_memory()
-    x = x_host.to(dev)
-    y = torch.empty_like(x)
+    xr = input_tokens(rows, cfg.d, SEED + 1000 + rank)
+    x = torch.from_numpy(xr).to(torch.bfloat16).to(dev)
+    y = torch.empty(x.shape, dtype=cfg.torch_y_dtype, device=dev)
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed(fn, n):
+    def measure(layer):
+        for _ in range(W):
+            layer.forward(ops, x, y)
+        layer.status()
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        for _ in range(n):
-            fn()
+        for _ in range(K):
+            layer.forward(ops, x, y)
         e1.record()
         barrier()
-        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
-        if world > 1:
+        ms = torch.tensor([e0.elapsed_time(e1) / K], dtype=torch.float64, device=dev)
+        if layer.world > 1:
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        layer.status()
         return float(ms.item())
 
-    def step():
-        layer.forward(ops, x, y)
+    def build(r, n):
+        layer = ExpertParallelLayer(cfg, r, n, local_rank, rows)
+        layer.pool.fill_synthetic(0, layer.epr, SEED, 0, first_expert=layer.lo)
+        layer.set_shared(capi.SharedExpert(sh.data_ptr(), soff))
+        return layer
 
-    def step_e2e():
-        x.copy_(x_host, non_blocking=True)
+    single = build(0, 1)
+    ms1 = measure(single)
+    single.close()
+    layer = build(rank, world)
+    ms_n = measure(layer)
+    stats = layer.exchange_stats(ops, x, y, K)
+    # parity of this rank's rows against the CPU oracle on a seeded sample (rank 0 only; the oracle is the checker)
+    parity = None
+    if rank == 0:
+        import oracle_lib as O
+        sample = np.sort(np.random.default_rng(3).choice(rows, 48, replace=False))
         layer.forward(ops, x, y)
-        y_host.copy_(y, non_blocking=True)
-
-    for _ in range(W):
-        step()
-    layer.home.status()
-    layer.routed.status()
-    sampler = ClockSampler(local_rank)
-    sampler.start()
-    ms = timed(step, K)
-    clocks = sampler.stop()
-    ms_e2e = timed(step_e2e, K)
-    sent = int(layer.send_counts.sum().item())
-    line = {
-        "metric": METRIC, "value": world * rows * K / (ms / 1e3), "unit": "tokens/s", "n_gpus": world, "steps": K,
-        "warmup": W, "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "int8 weights dequantised to fp16 operands, fp32 accumulate (TMEM)", "data": "synthetic",
-        "config": {"workload": "kimi-linear-48b-shape layer, expert parallel: 256 experts top-8 sigmoid + shared "
-                               "expert, D 2304, F 1024, int8 g64; 16 decode rows + one 2048-row prefill chunk per "
-                               "rank; all-to-all dispatch and combine over NCCL",
-                   "rows_per_rank": rows, "experts_per_rank": layer.epr, "parallelism": f"ep{world}",
-                   "rows_sent_by_rank0": sent,
-                   "l2": f"inputs larger than L2: {layer.epr * layer.block_bytes / 1e6:.0f} MB of expert blocks per rank"},
-        "e2e": {"value": world * rows * K / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e / K,
-                "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": y_host.numel() * 2},
-        "gpu_launches": None, "clocks": clocks,
-    }
+        torch.cuda.synchronize()
+        got = y.float().cpu().numpy()[sample]
+        ids = layer.ids.cpu().numpy().astype(np.uint32)[sample]
+        wts = layer.w.cpu().numpy()[sample]
+        ecfg = O.expert_cfg(cfg.d, cfg.f, bits=8)
+        lcfg = O.layer_cfg(ecfg, O.expert_cfg(cfg.d, cfg.shared_f, bits=8), False)
+        blocks = {int(e): fx.synth_block(cfg, SEED, 0, int(e)) for e in np.unique(ids)}
+        ref = O.moe_layer(lcfg, blocks, fx.synth_block(cfg, SEED, 0, 100000, shared=True), None, xr[sample], ids, wts,
+                          threads=os.cpu_count() or 8)
+        parity = float(np.linalg.norm(got - ref) / np.linalg.norm(ref))
+    recv = torch.tensor([stats["rows_received"]], dtype=torch.float64, device=dev)
+    recv_max, recv_sum = recv.clone(), recv.clone()
+    if world > 1:
+        dist.all_reduce(recv_max, op=dist.ReduceOp.MAX)
+        dist.all_reduce(recv_sum, op=dist.ReduceOp.SUM)
     layer.close()
-    return line
+    rows_s_1, rows_s_n = rows / (ms1 * 1e-3), world * rows / (ms_n * 1e-3)
+    return {"workload": "kimi-linear-48b-shape layer, expert parallel: 256 experts top-8 sigmoid + shared expert, D 2304, "
+                        "F 1024, int8 g64; 16 decode rows + one 2048-row prefill chunk per rank",
+            "world": world, "rows_per_rank": rows, "rows_per_s": round(rows_s_n), "ms_per_step": round(ms_n, 4),
+            "rows_per_s_one_gpu": round(rows_s_1), "ms_per_step_one_gpu": round(ms1, 4),
+            "efficiency": round(rows_s_n / (world * rows_s_1), 4),
+            "ms_dispatch": round(stats["ms_dispatch"], 4), "ms_combine": round(stats["ms_combine"], 4),
+            "bytes_sent_per_rank": stats["bytes_sent"], "rows_received_max_over_mean": round(
+                float(recv_max.item()) / (float(recv_sum.item()) / world), 4),
+            "exchange": stats["exchange"], "parity_rel_l2": parity}
 
 
 def main():
@@ -616,14 +596,14 @@ def main():
     if args.impl == "reference":
         if rank != 0:
             return
-        budget = 120.0
-        r = cpu_reference_run(args.tokens, args.layers, args.steps, args.warmup, budget)
+        r = cpu_reference_run(args.tokens, args.layers, args.steps, args.warmup, 120.0)
         print(json.dumps({
             "impl": "reference", "metric": METRIC, "value": r["value"], "unit": "tokens/s", "n_gpus": args.gpus,
             "steps": r["steps"], "warmup": args.warmup, "ms_per_step": r["ms_per_step"], "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "int4 weights, fp32 arithmetic", "data": "synthetic",
-            "config": {"workload": f"qwen3.5-35b-a3b expert shape, {args.layers}-layer decode sweep, batch {args.tokens}, "
-                                   "CPU path on the host cores"},
+            "config": {"workload": f"qwen3.5-35b-a3b expert shape, {args.layers}-layer decode sweep, batch {args.tokens} "
+                                   "(D 2048, 256 experts top-8 + gated shared, F 512, int4 g64 bf16 meta)",
+                       "arm": "the reference's CPU path on the host cores"},
             "cpu_baseline": {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")},
             "e2e": {"value": r["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         }))
@@ -633,45 +613,37 @@ def main():
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device (no CPU path in this library); "
                          "use --impl reference for the CPU arm")
-    if args.workload == "prefill":
-        if rank == 0:
-            print(json.dumps(run_prefill(args, local_rank)))
-        return
-    if args.workload == "gptoss":
-        if rank == 0:
-            print(json.dumps(run_gptoss(args, local_rank)))
-        return
-    if args.workload == "ep":
-        import torch.distributed as dist
-        if world > 1:
-            dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-        line = run_ep(args, rank, world, local_rank)
-        if rank == 0:
-            print(json.dumps(line))
-        if world > 1:
-            dist.barrier()
-            dist.destroy_process_group()
-        return
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    line = run_ours(args, rank, world, local_rank)
-    if rank == 0:
-        if world == 1 and not args.no_sweep and args.tokens == 1:
-            sweep = {}
-            for T in (4, 16):
-                a2 = argparse.Namespace(**vars(args))
-                a2.tokens, a2.steps = T, max(10, args.steps // 2)
-                l2 = run_ours(a2, 0, 1, local_rank)
-                sweep[f"batch_{T}"] = {"tokens_per_s": l2["value"], "ms_per_step": l2["ms_per_step"],
-                                       "hbm_gbs_per_layer": l2["hbm_gbs_per_layer"],
-                                       "distinct_experts_per_layer": l2["distinct_experts_per_layer"],
-                                       "phase1_gbs": l2["roofline"]["achieved"], "phase1_frac": l2["roofline"]["frac"],
-                                       "phase2_gbs": l2["roofline"]["phase2"]["achieved"]}
-            line["sweep"] = sweep
-        if world == 1 and not args.no_cpu_baseline:
+    only = args.workload
+    line = None
+    if only in ("all", "decode"):
+        line = decode_line(args, rank, world, local_rank)
+    if world == 1:
+        blocks = {}
+        if only == "all" and args.tokens == 1:
+            blocks["sweep"] = sweep_block(args, local_rank)
+        if only in ("all", "prefill"):
+            blocks["prefill"] = prefill_block(args, local_rank)
+        if only in ("all", "gptoss"):
+            blocks["gptoss"] = gptoss_block(args, local_rank)
+        if only == "ep":
+            blocks["ep"] = ep_block(args, 0, 1, local_rank)
+        if line is None:
+            line = {"metric": METRIC, "n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup)}
+        line.update(blocks)
+        if only in ("all", "decode") and not args.no_cpu_baseline:
             r = cpu_reference_run(args.tokens, args.layers, 1000, 2, 15.0)
             line["cpu_baseline"] = {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")}
+    else:
+        if only in ("all", "ep"):
+            ep = ep_block(args, rank, world, local_rank)
+            if rank == 0:
+                if line is None:
+                    line = {"metric": METRIC, "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup)}
+                line["ep"] = ep
+    if rank == 0 and line is not None:
         print(json.dumps(line))
     if world > 1:
         import torch.distributed as dist

@@ -51,6 +51,8 @@ extern "C" {
 #define SHRIKE_MAX_DECODE_TOKENS 64u /* largest query_count of the decode entry points */
 #define SHRIKE_STATIC_ROUTER_MAX_ROWS 64u /* rows the allocation-free router accepts per call */
 #define SHRIKE_SLOT_MISS 0xffffffffu /* resolved_slots sentinel, moe.metal:146 */
+#define SHRIKE_EP_MAX_WORLD 16u      /* most ranks of one expert-parallel group (the GPUs of one box) */
+#define SHRIKE_EP_HANDLE_BYTES 64u   /* size of the token a rank exports for its exchange buffer */
 
 enum { SHRIKE_DTYPE_BF16 = 0, SHRIKE_DTYPE_FP16 = 1, SHRIKE_DTYPE_FP32 = 2 };
 enum { SHRIKE_ACT_SILU = 0, SHRIKE_ACT_GELU_TANH = 1, SHRIKE_ACT_CLAMPED_SWIGLU = 2 };
@@ -323,6 +325,49 @@ int shrike_ep_encode_combine(shrike_moe* moe, void* stream, const void* recv_y, 
                              const void* y_home, uint32_t query_count, uint32_t world,
                              uint32_t capacity_rows, void* y, void* hidden);
 
+/* ---- the expert-parallel layer as one call (no counterpart in the reference) ---------------------------
+ *
+ * The exchange needs no collective library: every rank owns one exchange buffer, exports a token for it,
+ * the host hands every rank all tokens (over whatever transport it has), and from then on the kernels of
+ * shrike_ep_forward store rows straight into the destination rank's buffer over NVLink and wait on its
+ * arrival words -- plain peer loads and stores, bounded waits. Only the rows routed to a rank move.
+ *
+ *   shrike_ep_create   `home` is this rank's handle for the router and the shared expert (config of the whole
+ *                      layer, max_tokens >= rows_per_call); `routed` is the handle of its local experts
+ *                      (num_experts = experts per rank, no shared expert, max_tokens >= max(65, world *
+ *                      rows_per_call)). rows_per_call bounds query_count of every forward on every rank.
+ *   shrike_ep_export   SHRIKE_EP_HANDLE_BYTES bytes to give to the other ranks (a CUDA IPC handle).
+ *   shrike_ep_connect  all ranks' tokens, [world x SHRIKE_EP_HANDLE_BYTES], in rank order (its own is skipped).
+ *                      One process per GPU. A process that drives several GPUs itself passes the buffers'
+ *                      device addresses (shrike_ep_buffer) to shrike_ep_connect_pointers instead, with peer
+ *                      access enabled between the devices.
+ *   shrike_ep_forward  router -> dispatch -> (shared expert on a second stream meanwhile) -> local experts ->
+ *                      return -> combine for this rank's query_count rows; every rank of the group calls it
+ *                      once per layer step. The call enqueues on `stream` and on the handle's own second
+ *                      stream (joined before it returns control of `stream`'s order); it is not capturable
+ *                      in a CUDA graph (the epoch of the arrival words is a host counter).
+ *                      A rank whose peer never arrives waits about a second per exchange, then the next
+ *                      shrike_ep_status returns SHRIKE_ETIMEDOUT; the rows of that peer are missing from y.
+ *   wait_polls         0 = the default limit (about one second); tests pass a small number. */
+typedef struct shrike_ep shrike_ep;
+int shrike_ep_create(shrike_moe* home, shrike_moe* routed, uint32_t rank, uint32_t world, uint32_t rows_per_call,
+                     shrike_ep** out);
+void shrike_ep_destroy(shrike_ep* ep);
+int shrike_ep_export(shrike_ep* ep, void* handle_out);
+int shrike_ep_connect(shrike_ep* ep, const void* all_handles);
+int shrike_ep_buffer(shrike_ep* ep, void** base_out, uint64_t* bytes_out);
+int shrike_ep_connect_pointers(shrike_ep* ep, void* const* peer_bases);
+int shrike_ep_set_wait_polls(shrike_ep* ep, uint32_t wait_polls);
+int shrike_ep_forward(shrike_ep* ep, void* stream, const shrike_pool* local_pool,
+                      const shrike_expert_offsets* routed_offsets, const uint64_t* local_residency_row,
+                      const shrike_router_operands* router, const shrike_shared_expert* shared, const void* x,
+                      uint32_t query_count, void* y, void* hidden);
+/* Synchronises `stream`; SHRIKE_OK, or the first failure either handle recorded. */
+int shrike_ep_status(shrike_ep* ep, void* stream);
+/* Counters of the last forward, read after a synchronise: rows this rank sent to each rank
+ * [world], rows it received in total, bytes it stored into peers' buffers (both directions). */
+int shrike_ep_last_counts(shrike_ep* ep, uint32_t* sent_per_rank, uint32_t* rows_received, uint64_t* bytes_stored);
+
 /* The router for callers that cannot allocate. No counterpart in the reference.
  * Creating a handle sizes a workspace with cudaMalloc; a host that has already
  * given all free HBM to its expert pool, that fixes its memory plan before the
@@ -361,6 +406,37 @@ int shrike_moe_layer_forward_host(shrike_moe* moe, void* stream, const shrike_po
                                   const shrike_shared_expert* shared,
                                   const void* x_host, uint32_t query_count, void* y_host,
                                   uint32_t* ids_host, float* weights_host);
+
+/* One layer of a decode stack, as shrike_moe_decode_stack_forward_host takes them. */
+typedef struct shrike_stack_layer {
+    shrike_moe*                  moe;                 /* the layer's handle (its own work lists) */
+    const shrike_pool*           pool;
+    const shrike_expert_offsets* routed_offsets;
+    const uint64_t*              residency_table_row;
+    const shrike_router_operands* router;
+    const shrike_shared_expert*  shared;              /* NULL without a shared expert */
+} shrike_stack_layer;
+
+/* A decode step through stacked MoE layers with host activations in and out: what produceToken's per-layer
+ * encodeRoutedLayer calls (RealForwardRunner.swift:2205-2313) amount to for this path when only the MoE
+ * halves of the layers are present. The stack owns a device copy of the residual stream,
+ * [(layer_count + 1) x max_rows x d] in act_dtype.
+ *
+ *   rows_host   [(layer_count + 1) x query_count x d]: block 0 is the row set entering layer 0; block l >= 1 is
+ *               what the rest of transformer block l (attention, normalisation -- not part of this library)
+ *               contributes to the residual stream between MoE layer l-1 and MoE layer l.
+ *   forward     copies rows_host to the device (one copy), then for every layer l runs
+ *               shrike_encode_decode_layer with x = block l and hidden = block l+1, so that
+ *               block l+1 = rows_host block l+1 + y_l is the next layer's input; copies the last block
+ *               into out_host [query_count x d] and synchronises the stream.
+ * Every handle must share device, d and act_dtype; query_count <= max_rows <= SHRIKE_MAX_DECODE_TOKENS and
+ * <= every handle's max_tokens. Pinned host memory makes the copies asynchronous up to the final wait. */
+typedef struct shrike_decode_stack shrike_decode_stack;
+int shrike_decode_stack_create(const shrike_stack_layer* layers, uint32_t layer_count, uint32_t max_rows,
+                               shrike_decode_stack** out);
+void shrike_decode_stack_destroy(shrike_decode_stack* stack);
+int shrike_decode_stack_forward_host(shrike_decode_stack* stack, void* stream, const void* rows_host,
+                                     uint32_t query_count, void* out_host);
 
 #ifdef __cplusplus
 }

@@ -17,6 +17,8 @@ IO_PENDING, IO_READY, IO_FAILED = 0, 1, 2
 SLOT_MISS = 0xFFFFFFFF
 MAX_DECODE_TOKENS = 64
 STATIC_ROUTER_MAX_ROWS = 64
+EP_MAX_WORLD = 16
+EP_HANDLE_BYTES = 64
 
 OK, EINVAL, ENOMEM, ERANGE, EIO, ETIMEDOUT = 0, 22, 12, 34, 5, 110
 
@@ -49,6 +51,12 @@ class RouterOperands(C.Structure):
 
 class SharedExpert(C.Structure):
     _fields_ = [("block", C.c_void_p), ("offsets", ExpertOffsets)]
+
+
+class StackLayer(C.Structure):
+    _fields_ = [("moe", C.c_void_p), ("pool", C.c_void_p), ("routed_offsets", C.POINTER(ExpertOffsets)),
+                ("residency_table_row", C.c_void_p), ("router", C.POINTER(RouterOperands)),
+                ("shared", C.POINTER(SharedExpert))]
 
 
 _P = C.c_void_p
@@ -90,6 +98,20 @@ SIGNATURES = {
     "shrike_ep_encode_dispatch": (_INT, [_P, _P, _P, _P, _P, _U32, _U32, _U32, _U32, _P, _P, _P, _P, _P]),
     "shrike_ep_encode_local_slots": (_INT, [_P, _P, _P, _P, _U32, _P]),
     "shrike_ep_encode_combine": (_INT, [_P, _P, _P, _P, _P, _U32, _U32, _U32, _P, _P]),
+    "shrike_ep_create": (_INT, [_P, _P, _U32, _U32, _U32, C.POINTER(_P)]),
+    "shrike_ep_destroy": (None, [_P]),
+    "shrike_ep_export": (_INT, [_P, _P]),
+    "shrike_ep_connect": (_INT, [_P, _P]),
+    "shrike_ep_buffer": (_INT, [_P, C.POINTER(_P), C.POINTER(_U64)]),
+    "shrike_ep_connect_pointers": (_INT, [_P, C.POINTER(_P)]),
+    "shrike_ep_set_wait_polls": (_INT, [_P, _U32]),
+    "shrike_ep_forward": (_INT, [_P, _P, _P, C.POINTER(ExpertOffsets), _P, C.POINTER(RouterOperands),
+                                 C.POINTER(SharedExpert), _P, _U32, _P, _P]),
+    "shrike_ep_status": (_INT, [_P, _P]),
+    "shrike_ep_last_counts": (_INT, [_P, C.POINTER(_U32), C.POINTER(_U32), C.POINTER(_U64)]),
+    "shrike_decode_stack_create": (_INT, [C.POINTER(StackLayer), _U32, _U32, C.POINTER(_P)]),
+    "shrike_decode_stack_destroy": (None, [_P]),
+    "shrike_decode_stack_forward_host": (_INT, [_P, _P, _P, _U32, _P]),
     "shrike_moe_layer_forward_host": (_INT, [_P, _P, _P, C.POINTER(ExpertOffsets), _P,
                                              C.POINTER(RouterOperands), C.POINTER(SharedExpert),
                                              _P, _U32, _P, _P, _P]),

@@ -6,6 +6,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <new>
+#include <vector>
 
 #include "internal.h"
 
@@ -128,12 +129,14 @@ cudaError_t dev_alloc(P** p, size_t bytes) {
 }
 
 void free_workspace(Workspace& w) {
-    void* ptrs[] = {w.yacc, w.xs, w.chunk_inst, w.n_chunk_inst, w.done_counter, w.xsum, w.logits, w.xh, w.acts, w.acts_shared, w.sorted, w.inst, w.n_inst, w.status, w.block_hist,
+    void* ptrs[] = {w.fused_logits, w.fused_acts, w.fused_epoch, w.yacc, w.xs, w.chunk_inst, w.n_chunk_inst, w.done_counter, w.xsum, w.logits, w.xh, w.acts, w.acts_shared, w.sorted, w.inst, w.n_inst, w.status, w.block_hist,
                     w.expert_offsets, w.expert_counts, w.slot_of_expert, w.x_dev, w.y_dev,
                     w.ids_dev, w.w_dev, w.gate_dev, w.slots_dev, w.counts_dev};
     for (void* p : ptrs)
         if (p) cudaFree(p);
     free(w.tensor_maps);
+    free(w.fused_geom);
+    free(w.fused_maps);
     w = Workspace();
 }
 
@@ -288,11 +291,31 @@ int shrike_moe_create(const shrike_moe_config* config, int device, shrike_moe** 
     A(&w.gate_dev, T * 4);
     A(&w.slots_dev, T * K * 4);
     A(&w.counts_dev, 8);
+    // the one-row layer kernel: sizes of its shared-memory ring, and its hand-over buffers
+    int smem_optin = 0;
+    cudaDeviceGetAttribute(&smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device);
+    w.fused_geom = malloc(fused_geom_bytes());
+    w.fused_maps = calloc(1, fused_map_cache_bytes());
+    if (w.fused_geom && w.fused_maps && fused_geometry(c, m->sm_count, smem_optin, *(FusedGeom*)w.fused_geom)) {
+        A((uint8_t**)&w.fused_logits, fused_logits_bytes(c));
+        A(&w.fused_acts, fused_acts_bytes(c));
+        A(&w.fused_epoch, 4);
+    } else {
+        free(w.fused_geom);
+    free(w.fused_maps);
+        w.fused_geom = nullptr;
+    }
     if (!ok) {
         free_workspace(w);
         delete m;
         cudaGetLastError();
         return fail(nullptr, SHRIKE_ENOMEM, "device allocation of the workspace failed");
+    }
+    if (w.fused_geom) {
+        // no logit carries the first epoch's tag, no activation has been published
+        cudaMemset(w.fused_logits, 0xff, fused_logits_bytes(c));
+        cudaMemset(w.fused_acts, 0xff, fused_acts_bytes(c));
+        cudaMemset(w.fused_epoch, 0, 4);
     }
     if (T <= SHRIKE_MAX_DECODE_TOKENS) {   // decode-only handle: no prefill operands
         cudaFree(w.xs);
@@ -638,6 +661,23 @@ int shrike_encode_decode_layer(shrike_moe* m, void* stream, const shrike_pool* p
         return encode_prefill(m, stream, pool, routed_offsets, ids, w.slots_dev, wt, x, query_count, shared, gate,
                               io_status, y, hidden);
     }
+    if (query_count == 1 && w.fused_geom) {
+        // one row: router, selection, lookup, both projections and the combine in ONE launch (fused_layer.cu)
+        if (!residency_table_row || !pool) return fail(m, SHRIKE_EINVAL, "decode_layer: null operand");
+        int rcf = check_router_call(m, router, x, 1, 1, m->cfg.d, false, nullptr);
+        if (rcf) return rcf;
+        if (!aligned_to(y, 16) || (hidden && !aligned_to(hidden, 16)))
+            return fail(m, SHRIKE_EINVAL, "decode_layer: y and hidden must be 16-byte aligned");
+        ExpertArgs ea;
+        rcf = fill_expert_args(m, pool, routed_offsets, shared, wt, gate, ea);
+        if (rcf) return rcf;
+        if ((rcf = check_device(m))) return rcf;
+        const cudaError_t fe = launch_fused_layer(m, (cudaStream_t)stream, ea, *router, residency_table_row,
+                                                  pool->view.cells, io_status, x, ids, wt, w.slots_dev, gate, y, hidden);
+        if (fe == cudaSuccess) return SHRIKE_OK;
+        if (fe != cudaErrorNotSupported) return cuda_fail(m, fe, "launch_fused_layer");
+        // a block layout the tiled copies cannot describe: the three launches below
+    }
     int rc = shrike_encode_route_decode(m, stream, router, residency_table_row, pool, x, query_count, m->cfg.d,
                                         io_status, ids, wt, gate, w.slots_dev, nullptr);
     if (rc) return rc;
@@ -748,6 +788,327 @@ int shrike_moe_layer_forward_host(shrike_moe* m, void* stream, const shrike_pool
     if (ids_host) CU(cudaMemcpyAsync(ids_host, w.ids_dev, (size_t)query_count * c.top_k * 4, cudaMemcpyDeviceToHost, st));
     if (weights_host) CU(cudaMemcpyAsync(weights_host, w.w_dev, (size_t)query_count * c.top_k * 4, cudaMemcpyDeviceToHost, st));
     return shrike_moe_status(m, stream);
+}
+
+// ---- expert parallelism over peer memory ---------------------------------------------------------------
+
+struct shrike_ep {
+    shrike_moe* home;
+    shrike_moe* routed;
+    uint32_t rank, world, cap, epr, t_max;
+    EpLayout lay;
+    uint8_t* mine = nullptr;
+    uint8_t* peer[SHRIKE_EP_MAX_WORLD] = {};
+    bool opened[SHRIKE_EP_MAX_WORLD] = {};
+    bool connected = false;
+    // local scratch
+    uint32_t* ids = nullptr; float* w = nullptr; float* gate = nullptr; int32_t* row_of = nullptr;
+    uint32_t* send_counts = nullptr; uint32_t* miss_slots = nullptr;
+    uint32_t* c_ids = nullptr; float* c_w = nullptr; uint32_t* c_slots = nullptr; uint32_t* row_map = nullptr;
+    uint32_t* prefix = nullptr; uint32_t* n_rows = nullptr;
+    void* y_home = nullptr;
+    cudaStream_t side = nullptr;
+    cudaEvent_t ev_routed = nullptr, ev_shared = nullptr;
+    uint32_t epoch = 0;
+    uint32_t max_polls = 1000000;   // ~1 us per poll
+};
+
+static void ep_free(shrike_ep* ep) {
+    for (uint32_t g = 0; g < SHRIKE_EP_MAX_WORLD; ++g)
+        if (ep->opened[g] && ep->peer[g]) cudaIpcCloseMemHandle(ep->peer[g]);
+    void* ptrs[] = {ep->mine, ep->ids, ep->w, ep->gate, ep->row_of, ep->send_counts, ep->miss_slots, ep->c_ids, ep->c_w,
+                    ep->c_slots, ep->row_map, ep->prefix, ep->n_rows, ep->y_home};
+    for (void* p : ptrs)
+        if (p) cudaFree(p);
+    if (ep->side) cudaStreamDestroy(ep->side);
+    if (ep->ev_routed) cudaEventDestroy(ep->ev_routed);
+    if (ep->ev_shared) cudaEventDestroy(ep->ev_shared);
+    delete ep;
+}
+
+int shrike_ep_create(shrike_moe* home, shrike_moe* routed, uint32_t rank, uint32_t world, uint32_t rows_per_call,
+                     shrike_ep** out) {
+    if (!home || !routed || !out) return SHRIKE_EINVAL;
+    shrike_moe* m = home;
+    *out = nullptr;
+    const shrike_moe_config& c = home->cfg;
+    const shrike_moe_config& r = routed->cfg;
+    if (world == 0 || world > SHRIKE_EP_MAX_WORLD || rank >= world)
+        return fail(m, SHRIKE_EINVAL, "ep: world must be 1..%u and rank below it", SHRIKE_EP_MAX_WORLD);
+    if (c.num_experts % world != 0 || r.num_experts != c.num_experts / world)
+        return fail(m, SHRIKE_EINVAL, "ep: the routed handle must hold num_experts / world experts");
+    if (r.d != c.d || r.f != c.f || r.top_k != c.top_k || r.weight_bits != c.weight_bits || r.group_size != c.group_size ||
+        r.meta_dtype != c.meta_dtype || r.act_dtype != c.act_dtype || r.y_dtype != c.y_dtype ||
+        r.activation != c.activation || r.expert_bias != c.expert_bias || r.has_shared || home->device != routed->device)
+        return fail(m, SHRIKE_EINVAL, "ep: the routed handle must share the layer's shape, dtypes and device and have no shared expert");
+    if (rows_per_call == 0 || rows_per_call > c.max_tokens)
+        return fail(m, SHRIKE_ERANGE, "ep: rows_per_call must be 1..max_tokens of the home handle");
+    const uint32_t t_max = world * rows_per_call;
+    if (r.max_tokens < t_max || r.max_tokens <= SHRIKE_MAX_DECODE_TOKENS)
+        return fail(m, SHRIKE_ERANGE, "ep: the routed handle needs max_tokens >= max(65, world * rows_per_call)");
+    DeviceGuard guard(home->device);
+    shrike_ep* ep = new (std::nothrow) shrike_ep();
+    if (!ep) return fail(m, SHRIKE_ENOMEM, "host allocation failed");
+    ep->home = home; ep->routed = routed; ep->rank = rank; ep->world = world; ep->cap = rows_per_call;
+    ep->epr = r.num_experts; ep->t_max = t_max;
+    ep->lay = ep_layout(c, world, rows_per_call);
+    const size_t T = rows_per_call, K = c.top_k;
+    bool ok = true;
+    auto A = [&](auto** p, size_t bytes) { if (ok && dev_alloc(p, bytes) != cudaSuccess) ok = false; };
+    A(&ep->mine, ep->lay.bytes);
+    A(&ep->ids, T * K * 4); A(&ep->w, T * K * 4); A(&ep->gate, T * 4); A(&ep->row_of, T * world * 4);
+    A(&ep->send_counts, SHRIKE_EP_MAX_WORLD * 4); A(&ep->miss_slots, T * K * 4);
+    A(&ep->c_ids, (size_t)t_max * K * 4); A(&ep->c_w, (size_t)t_max * K * 4); A(&ep->c_slots, (size_t)t_max * K * 4);
+    A(&ep->row_map, (size_t)t_max * 4); A(&ep->prefix, (SHRIKE_EP_MAX_WORLD + 1) * 4); A(&ep->n_rows, 4);
+    A((uint8_t**)&ep->y_home, c.has_shared ? T * c.d * act_bytes(c.y_dtype) : 0);
+    if (ok && (cudaStreamCreateWithFlags(&ep->side, cudaStreamNonBlocking) != cudaSuccess ||
+               cudaEventCreateWithFlags(&ep->ev_routed, cudaEventDisableTiming) != cudaSuccess ||
+               cudaEventCreateWithFlags(&ep->ev_shared, cudaEventDisableTiming) != cudaSuccess))
+        ok = false;
+    if (!ok) {
+        ep_free(ep);
+        cudaGetLastError();
+        return fail(m, SHRIKE_ENOMEM, "ep: allocation of the exchange buffers failed");
+    }
+    // no arrival word carries the first epoch's tag; the shared-only call of the home rows sees every pick miss
+    cudaMemset(ep->mine, 0, ep->lay.bytes);
+    cudaMemset(ep->miss_slots, 0xff, T * K * 4);
+    ep->peer[rank] = ep->mine;
+    ep->connected = world == 1;
+    *out = ep;
+    return SHRIKE_OK;
+}
+
+void shrike_ep_destroy(shrike_ep* ep) {
+    if (!ep) return;
+    DeviceGuard guard(ep->home->device);
+    cudaDeviceSynchronize();
+    ep_free(ep);
+}
+
+int shrike_ep_export(shrike_ep* ep, void* handle_out) {
+    if (!ep || !handle_out) return SHRIKE_EINVAL;
+    shrike_moe* m = ep->home;
+    static_assert(sizeof(cudaIpcMemHandle_t) == SHRIKE_EP_HANDLE_BYTES, "token size");
+    DeviceGuard guard(m->device);
+    cudaIpcMemHandle_t h;
+    CU(cudaIpcGetMemHandle(&h, ep->mine));
+    memcpy(handle_out, &h, sizeof h);
+    return SHRIKE_OK;
+}
+
+int shrike_ep_connect(shrike_ep* ep, const void* all_handles) {
+    if (!ep || !all_handles) return SHRIKE_EINVAL;
+    shrike_moe* m = ep->home;
+    DeviceGuard guard(m->device);
+    for (uint32_t g = 0; g < ep->world; ++g) {
+        if (g == ep->rank || ep->peer[g]) continue;
+        cudaIpcMemHandle_t h;
+        memcpy(&h, (const uint8_t*)all_handles + (size_t)g * SHRIKE_EP_HANDLE_BYTES, sizeof h);
+        void* p = nullptr;
+        CU(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+        ep->peer[g] = (uint8_t*)p;
+        ep->opened[g] = true;
+    }
+    ep->connected = true;
+    return SHRIKE_OK;
+}
+
+int shrike_ep_buffer(shrike_ep* ep, void** base_out, uint64_t* bytes_out) {
+    if (!ep || !base_out) return SHRIKE_EINVAL;
+    *base_out = ep->mine;
+    if (bytes_out) *bytes_out = ep->lay.bytes;
+    return SHRIKE_OK;
+}
+
+int shrike_ep_connect_pointers(shrike_ep* ep, void* const* peer_bases) {
+    if (!ep || !peer_bases) return SHRIKE_EINVAL;
+    for (uint32_t g = 0; g < ep->world; ++g) {
+        if (g == ep->rank) continue;
+        if (!peer_bases[g]) return fail(ep->home, SHRIKE_EINVAL, "ep: peer %u has no buffer", g);
+        ep->peer[g] = (uint8_t*)peer_bases[g];
+    }
+    ep->connected = true;
+    return SHRIKE_OK;
+}
+
+int shrike_ep_set_wait_polls(shrike_ep* ep, uint32_t wait_polls) {
+    if (!ep) return SHRIKE_EINVAL;
+    ep->max_polls = wait_polls ? wait_polls : 1000000;
+    return SHRIKE_OK;
+}
+
+int shrike_ep_forward(shrike_ep* ep, void* stream, const shrike_pool* local_pool,
+                      const shrike_expert_offsets* routed_offsets, const uint64_t* local_residency_row,
+                      const shrike_router_operands* router, const shrike_shared_expert* shared, const void* x,
+                      uint32_t query_count, void* y, void* hidden) {
+    if (!ep) return SHRIKE_EINVAL;
+    shrike_moe* m = ep->home;
+    shrike_moe* r = ep->routed;
+    if (!ep->connected) return fail(m, SHRIKE_EINVAL, "ep: connect the ranks' buffers first");
+    if (!local_pool || !routed_offsets || !local_residency_row || !router || !y || (query_count && !x))
+        return fail(m, SHRIKE_EINVAL, "ep forward: null operand");
+    if (query_count > ep->cap) return fail(m, SHRIKE_ERANGE, "ep forward: query_count exceeds rows_per_call");
+    const shrike_moe_config& c = m->cfg;
+    cudaStream_t st = (cudaStream_t)stream;
+    int rc;
+    if ((rc = check_device(m))) return rc;
+    const uint32_t epoch = ++ep->epoch;
+    const uint32_t T = query_count;
+    float* gate = c.shared_gated ? ep->gate : nullptr;
+    if (T) {
+        rc = shrike_encode_router(m, stream, router, x, T, c.d, ep->ids, ep->w, gate);
+        if (rc) return rc;
+    }
+    // the shared expert of the home rows depends on the router's gate only: second stream, beside the exchange
+    const bool with_shared = c.has_shared && T > 0;
+    if (with_shared) {
+        CU(cudaEventRecord(ep->ev_routed, st));
+        CU(cudaStreamWaitEvent(ep->side, ep->ev_routed, 0));
+        if (T <= SHRIKE_MAX_DECODE_TOKENS)
+            rc = shrike_encode_moe_decode(m, ep->side, local_pool, routed_offsets, ep->miss_slots, ep->w, x, T, shared, gate,
+                                          nullptr, ep->y_home, nullptr);
+        else
+            rc = encode_prefill(m, ep->side, local_pool, routed_offsets, ep->ids, ep->miss_slots, ep->w, x, T, shared, gate,
+                                nullptr, ep->y_home, nullptr);
+        if (rc) return rc;
+        CU(cudaEventRecord(ep->ev_shared, ep->side));
+    }
+    CU(launch_ep_dispatch_peer(m, st, x, ep->ids, ep->w, T, ep->world, ep->rank, ep->epr, ep->cap, ep->peer, ep->lay, epoch,
+                               ep->send_counts, ep->row_of));
+    CU(launch_ep_receive(r, st, ep->mine, ep->lay, ep->world, ep->cap, epoch, local_residency_row, ep->t_max, ep->prefix,
+                         ep->n_rows, ep->c_ids, ep->c_w, ep->c_slots, ep->row_map, ep->max_polls));
+    {   // local experts on the received rows (read in place through the row map), accumulated per row
+        ExpertArgs a;
+        rc = fill_expert_args(r, local_pool, routed_offsets, nullptr, ep->c_w, nullptr, a);
+        if (rc) { m->err = r->err; return rc; }
+        const bool warp_mma = r->force_warp_mma || !umma_supported(r->cfg);
+        CU(launch_prefill_plan(r, st, ep->c_ids, ep->c_slots, ep->mine + ep->lay.off_recv_x, ep->t_max, false,
+                               local_pool->view.cells, warp_mma, nullptr, ep->row_map, ep->n_rows));
+        if (warp_mma) {
+            const uint32_t mi = max_instances(r->cfg, ep->t_max);
+            CU(launch_phase1(r, st, a, mi, false));
+            CU(launch_phase2_accumulate(r, st, a, mi));
+        } else {
+            CU(launch_umma_prefill(r, st, a, ep->t_max, local_pool->view.cells));
+        }
+    }
+    CU(launch_ep_return(r, st, ep->row_map, ep->n_rows, ep->t_max, ep->world, ep->rank, ep->cap, ep->peer, ep->lay, epoch));
+    CU(launch_ep_wait_returns(m, st, ep->mine, ep->lay, ep->world, ep->cap, epoch, ep->max_polls));
+    if (with_shared) CU(cudaStreamWaitEvent(st, ep->ev_shared, 0));
+    if (T)
+        CU(launch_ep_combine(m, st, ep->mine + ep->lay.off_ret, ep->row_of, with_shared ? ep->y_home : nullptr, T, ep->world,
+                             ep->cap, y, hidden));
+    return SHRIKE_OK;
+}
+
+int shrike_ep_status(shrike_ep* ep, void* stream) {
+    if (!ep) return SHRIKE_EINVAL;
+    int rc = shrike_moe_status(ep->home, stream);
+    const int rc2 = shrike_moe_status(ep->routed, stream);
+    if (!rc && rc2) {
+        ep->home->err = ep->routed->err;
+        rc = rc2;
+    }
+    return rc;
+}
+
+int shrike_ep_last_counts(shrike_ep* ep, uint32_t* sent_per_rank, uint32_t* rows_received, uint64_t* bytes_stored) {
+    if (!ep) return SHRIKE_EINVAL;
+    shrike_moe* m = ep->home;
+    uint32_t sent[SHRIKE_EP_MAX_WORLD] = {};
+    uint32_t n = 0;
+    CU(cudaMemcpy(sent, ep->send_counts, ep->world * 4, cudaMemcpyDeviceToHost));
+    CU(cudaMemcpy(&n, ep->n_rows, 4, cudaMemcpyDeviceToHost));
+    uint64_t rows_out = 0;
+    for (uint32_t g = 0; g < ep->world; ++g) {
+        if (sent_per_rank) sent_per_rank[g] = sent[g];
+        if (g != ep->rank) rows_out += sent[g];
+    }
+    if (rows_received) *rows_received = n;
+    if (bytes_stored) {
+        const shrike_moe_config& c = m->cfg;
+        // rows + ids + weights out, partial rows back (the rows this rank received from others), 8-byte words
+        uint32_t own = 0;
+        uint32_t pre[SHRIKE_EP_MAX_WORLD + 1] = {};
+        CU(cudaMemcpy(pre, ep->prefix, (ep->world + 1) * 4, cudaMemcpyDeviceToHost));
+        own = pre[ep->rank + 1] - pre[ep->rank];
+        *bytes_stored = rows_out * ((uint64_t)c.d * act_bytes(c.act_dtype) + (uint64_t)c.top_k * 8) +
+                        (uint64_t)(n - own) * c.d * act_bytes(c.y_dtype) + (uint64_t)(ep->world - 1) * 16;
+    }
+    return SHRIKE_OK;
+}
+
+struct shrike_decode_stack {
+    std::vector<shrike_stack_layer> layers;
+    uint32_t max_rows;
+    void* stream_dev = nullptr;   // [(layers + 1) x max_rows x d]
+};
+
+int shrike_decode_stack_create(const shrike_stack_layer* layers, uint32_t layer_count, uint32_t max_rows,
+                               shrike_decode_stack** out) {
+    if (!layers || layer_count == 0 || !layers[0].moe || !out) return SHRIKE_EINVAL;
+    *out = nullptr;
+    shrike_moe* m = layers[0].moe;
+    const shrike_moe_config& c = m->cfg;
+    if (max_rows == 0 || max_rows > SHRIKE_MAX_DECODE_TOKENS)
+        return fail(m, SHRIKE_ERANGE, "decode_stack: max_rows must be 1..%u", SHRIKE_MAX_DECODE_TOKENS);
+    for (uint32_t l = 0; l < layer_count; ++l) {
+        const shrike_moe* ml = layers[l].moe;
+        if (!ml || ml->device != m->device || ml->cfg.d != c.d || ml->cfg.act_dtype != c.act_dtype)
+            return fail(m, SHRIKE_EINVAL, "decode_stack: layer %u does not share device, d and act_dtype with layer 0", l);
+        if (max_rows > ml->cfg.max_tokens) return fail(m, SHRIKE_ERANGE, "decode_stack: max_rows exceeds layer %u's max_tokens", l);
+        if (!layers[l].pool || !layers[l].routed_offsets || !layers[l].residency_table_row || !layers[l].router)
+            return fail(m, SHRIKE_EINVAL, "decode_stack: layer %u has a null operand", l);
+    }
+    DeviceGuard guard(m->device);
+    shrike_decode_stack* s = new (std::nothrow) shrike_decode_stack();
+    if (!s) return fail(m, SHRIKE_ENOMEM, "host allocation failed");
+    s->layers.assign(layers, layers + layer_count);
+    s->max_rows = max_rows;
+    const size_t bytes = (size_t)(layer_count + 1) * max_rows * c.d * act_bytes(c.act_dtype);
+    if (cudaMalloc(&s->stream_dev, bytes) != cudaSuccess) {
+        delete s;
+        cudaGetLastError();
+        return fail(m, SHRIKE_ENOMEM, "decode_stack: residual stream of %zu bytes", bytes);
+    }
+    *out = s;
+    return SHRIKE_OK;
+}
+
+void shrike_decode_stack_destroy(shrike_decode_stack* stack) {
+    if (!stack) return;
+    DeviceGuard guard(stack->layers[0].moe->device);
+    cudaFree(stack->stream_dev);
+    delete stack;
+}
+
+int shrike_decode_stack_forward_host(shrike_decode_stack* stack, void* stream, const void* rows_host,
+                                     uint32_t query_count, void* out_host) {
+    if (!stack) return SHRIKE_EINVAL;
+    shrike_moe* m = stack->layers[0].moe;
+    if (!rows_host || !out_host) return fail(m, SHRIKE_EINVAL, "decode_stack: null operand");
+    if (query_count == 0) return SHRIKE_OK;
+    if (query_count > stack->max_rows) return fail(m, SHRIKE_ERANGE, "decode_stack: query_count exceeds max_rows");
+    const shrike_moe_config& c = m->cfg;
+    cudaStream_t st = (cudaStream_t)stream;
+    const uint32_t L = (uint32_t)stack->layers.size();
+    const size_t block = (size_t)query_count * c.d * act_bytes(c.act_dtype);
+    uint8_t* dev = (uint8_t*)stack->stream_dev;
+    CU(cudaMemcpyAsync(dev, rows_host, (size_t)(L + 1) * block, cudaMemcpyHostToDevice, st));
+    for (uint32_t l = 0; l < L; ++l) {
+        const shrike_stack_layer& ly = stack->layers[l];
+        const int rc = shrike_encode_decode_layer(ly.moe, stream, ly.pool, ly.routed_offsets, ly.residency_table_row,
+                                                  ly.router, ly.shared, dev + (size_t)l * block, query_count, nullptr, nullptr,
+                                                  nullptr, ly.moe->ws.y_dev, dev + (size_t)(l + 1) * block);
+        if (rc) {
+            if (ly.moe != m) m->err = ly.moe->err;
+            return rc;
+        }
+    }
+    CU(cudaMemcpyAsync(out_host, dev + (size_t)L * block, block, cudaMemcpyDeviceToHost, st));
+    CU(cudaStreamSynchronize(st));
+    return SHRIKE_OK;
 }
 
 }  // extern "C"

@@ -196,6 +196,16 @@ __host__ __device__ __forceinline__ uint32_t perm_index(uint32_t i, bool int4) {
 // into an infinity.
 constexpr float kHalfMax = 65504.0f;
 
+// fp16 bits of an inter-phase activation (the reference keeps them in fp16 too, moe.metal:829): a magnitude
+// beyond the fp16 range saturates and is reported like an out-of-range input.
+__device__ __forceinline__ uint16_t act_to_half_bits(float v, uint32_t* status) {
+    if (fabsf(v) > kHalfMax) {
+        report_status(status, kStatusOperandRange);
+        v = copysignf(kHalfMax, v);
+    }
+    return __half_as_ushort(__float2half_rn(v));
+}
+
 __device__ __forceinline__ float xprep_block8(const void* xrow, uint32_t blk, uint32_t dt, bool int4,
                                               uint16_t* xh_row, uint32_t* status) {
     float v[8];
@@ -234,14 +244,20 @@ __device__ __forceinline__ float xprep_block8(const void* xrow, uint32_t blk, ui
 // shuffles. Every lane of a warp must call this together.
 __device__ __forceinline__ void xprep_item(const void* x, size_t row_stride_bytes, uint32_t d, uint32_t group,
                                            uint32_t dt, bool int4, uint32_t item, bool valid, uint16_t* xh,
-                                           float* xsum, uint32_t* status) {
+                                           float* xsum, uint32_t* status, const uint32_t* row_map = nullptr,
+                                           uint32_t n_rows = 0xffffffffu) {
+    // row_map: row r of the call is row row_map[r] of x; rows from n_rows on carry no work
     const uint32_t per_row = d / 8;
     float sum = 0.f;
     uint32_t row = 0, blk = 0;
     if (valid) {
         row = item / per_row;
         blk = item - row * per_row;
-        sum = xprep_block8((const uint8_t*)x + (size_t)row * row_stride_bytes, blk, dt, int4, xh + (size_t)row * d,
+        valid = row < n_rows;
+    }
+    if (valid) {
+        const uint32_t src = row_map ? row_map[row] : row;
+        sum = xprep_block8((const uint8_t*)x + (size_t)src * row_stride_bytes, blk, dt, int4, xh + (size_t)row * d,
                            status);
     }
     const uint32_t lanes = group / 8;  // 8 or 4 lanes per group

@@ -328,7 +328,7 @@ __global__ void __launch_bounds__(kP1Warps * 32) phase1_kernel(const ExpertArgs 
             const float act = glu(gate, up, a.activation);
             const uint32_t fi = perm_index(f0 + row, BITS == 4);
             uint16_t* dst = shared ? a.acts_shared : a.acts;
-            dst[(size_t)pick(in.pair, c) * F + fi] = __half_as_ushort(__float2half_rn(act));
+            dst[(size_t)pick(in.pair, c) * F + fi] = act_to_half_bits(act, a.status);
         }
     }
 }

@@ -87,6 +87,12 @@ struct Workspace {
     uint32_t* n_chunk_inst = nullptr; // [0] instances, [1] sorted rows
     uint16_t* xs = nullptr;         // prefill: fp16 activation rows in expert-sorted order [max_tokens x top_k x d]
     void* tensor_maps = nullptr;    // host: the TMA descriptors of xs, acts, xh, acts_shared
+    // one-row decode layer in one launch (fused_layer.cu)
+    void* fused_geom = nullptr;       // host: sizes of the shared-memory ring, or NULL when the shape does not fit
+    void* fused_maps = nullptr;       // host: cached tensor maps of the last call's pool and shared block
+    void* fused_logits = nullptr;     // [num_experts + 1] {epoch, logit} words
+    uint16_t* fused_acts = nullptr;   // two activation hand-over buffers
+    uint32_t* fused_epoch = nullptr;
     // forward_host staging
     void* x_dev = nullptr; void* y_dev = nullptr;
     uint32_t* ids_dev = nullptr; float* w_dev = nullptr; float* gate_dev = nullptr;
@@ -176,12 +182,30 @@ cudaError_t launch_phase2_accumulate(const shrike_moe* m, cudaStream_t st, const
 // prefill.cu
 cudaError_t launch_prefill_plan(const shrike_moe* m, cudaStream_t st, const uint32_t* ids,
                                 const uint32_t* slots, const void* x, uint32_t T, bool with_shared,
-                                uint32_t pool_cells, bool warp_mma_instances, const uint32_t* io_status);
+                                uint32_t pool_cells, bool warp_mma_instances, const uint32_t* io_status,
+                                const uint32_t* row_map = nullptr, const uint32_t* n_rows = nullptr);
 cudaError_t launch_prefill_combine(const shrike_moe* m, cudaStream_t st, uint32_t T, void* y, void* hidden);
 }  // namespace shrike
 
 namespace shrike {
 // ep.cu
+struct EpLayout {   // byte offsets inside a rank's exchange buffer
+    size_t off_recv_x, off_recv_ids, off_recv_w, off_ret, off_arrive, off_ret_arrive, bytes;
+};
+EpLayout ep_layout(const shrike_moe_config& c, uint32_t world, uint32_t cap);
+cudaError_t launch_ep_dispatch_peer(const shrike_moe* m, cudaStream_t st, const void* x, const uint32_t* ids,
+                                    const float* weights, uint32_t T, uint32_t world, uint32_t rank,
+                                    uint32_t experts_per_rank, uint32_t cap, uint8_t* const* peer_base,
+                                    const EpLayout& lay, uint32_t epoch, uint32_t* send_counts, int32_t* row_of);
+cudaError_t launch_ep_receive(const shrike_moe* routed, cudaStream_t st, const uint8_t* mine, const EpLayout& lay,
+                              uint32_t world, uint32_t cap, uint32_t epoch, const uint64_t* table, uint32_t t_max,
+                              uint32_t* prefix, uint32_t* n_rows, uint32_t* c_ids, float* c_w, uint32_t* c_slots,
+                              uint32_t* row_map, uint32_t max_polls);
+cudaError_t launch_ep_return(const shrike_moe* routed, cudaStream_t st, const uint32_t* row_map, const uint32_t* n_rows,
+                             uint32_t t_max, uint32_t world, uint32_t rank, uint32_t cap, uint8_t* const* peer_base,
+                             const EpLayout& lay, uint32_t epoch);
+cudaError_t launch_ep_wait_returns(const shrike_moe* home, cudaStream_t st, const uint8_t* mine, const EpLayout& lay,
+                                   uint32_t world, uint32_t cap, uint32_t epoch, uint32_t max_polls);
 cudaError_t launch_ep_dispatch(const shrike_moe* m, cudaStream_t st, const void* x, const uint32_t* ids,
                                const float* weights, uint32_t T, uint32_t world, uint32_t experts_per_rank,
                                uint32_t cap, void* send_x, uint32_t* send_ids, float* send_w,
@@ -190,6 +214,20 @@ cudaError_t launch_ep_local_slots(const shrike_moe* m, cudaStream_t st, const ui
                                   const uint64_t* table, uint32_t rows, uint32_t* slots);
 cudaError_t launch_ep_combine(const shrike_moe* m, cudaStream_t st, const void* recv_y, const int32_t* row_of,
                               const void* y_home, uint32_t T, uint32_t world, uint32_t cap, void* y, void* hidden);
+}  // namespace shrike
+
+namespace shrike {
+// fused_layer.cu
+struct FusedGeom;
+bool fused_geometry(const shrike_moe_config& c, int sm_count, int max_smem_optin, FusedGeom& g);
+size_t fused_geom_bytes();
+size_t fused_map_cache_bytes();
+size_t fused_logits_bytes(const shrike_moe_config& c);
+size_t fused_acts_bytes(const shrike_moe_config& c);
+cudaError_t launch_fused_layer(const shrike_moe* m, cudaStream_t st, const ExpertArgs& ea,
+                               const shrike_router_operands& ops, const uint64_t* table, uint32_t pool_cells,
+                               const uint32_t* io_status, const void* x, uint32_t* ids, float* weights,
+                               uint32_t* slots, float* gate, void* y, void* hidden);
 }  // namespace shrike
 
 namespace shrike {

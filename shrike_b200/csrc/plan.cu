@@ -104,8 +104,10 @@ group_hist_kernel(const uint32_t* __restrict__ ids, uint32_t T, uint32_t top_k, 
                 // a row that names one expert twice (no top-k router does) is counted once and reported
                 const uint32_t bit = 1u << (tl & 31);
                 if (atomicOr(&bits[e][tl >> 5], bit) & bit) report_status(status, kStatusBadIndex);
-            } else {
-                report_status(status, kStatusBadIndex);   // expert id out of range: the pair is dropped
+            } else if (e != 0xffffffffu) {
+                // out of range: the pair is dropped and reported (0xffffffff is the expert-parallel layer's
+                // "this pick lives on another rank" and is dropped silently)
+                report_status(status, kStatusBadIndex);
             }
         }
     }

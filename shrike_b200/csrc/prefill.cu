@@ -64,12 +64,14 @@ prefill_instances_kernel(const uint32_t* __restrict__ offsets, const uint32_t* _
 // x -> fp16 operand layout and per-group sums, all rows.
 __global__ void __launch_bounds__(256)
 prefill_xprep_kernel(const void* __restrict__ x, uint32_t T, uint32_t d, uint32_t group, uint32_t act_dtype,
-                     uint32_t int4, uint16_t* __restrict__ xh, float* __restrict__ xsum, uint32_t* status) {
+                     uint32_t int4, uint16_t* __restrict__ xh, float* __restrict__ xsum, uint32_t* status,
+                     const uint32_t* __restrict__ row_map, const uint32_t* __restrict__ n_rows_dev) {
     const uint32_t items = T * (d / 8);
     const size_t row_bytes = (size_t)d * (act_dtype == SHRIKE_DTYPE_FP32 ? 4 : 2);
+    const uint32_t n_rows = n_rows_dev ? *n_rows_dev : T;
     for (uint32_t i0 = blockIdx.x * blockDim.x; i0 < items; i0 += gridDim.x * blockDim.x)
         xprep_item(x, row_bytes, d, group, act_dtype, int4 != 0, i0 + threadIdx.x, i0 + threadIdx.x < items, xh,
-                   xsum, status);
+                   xsum, status, row_map, n_rows);
 }
 
 // slot_of_expert[e] = the cell every pair of expert e resolved to.
@@ -106,7 +108,8 @@ prefill_combine_kernel(const float* __restrict__ yacc, uint32_t n, uint32_t act_
 
 cudaError_t launch_prefill_plan(const shrike_moe* m, cudaStream_t st, const uint32_t* ids,
                                 const uint32_t* slots, const void* x, uint32_t T, bool with_shared,
-                                uint32_t pool_cells, bool warp_mma_instances, const uint32_t* io_status) {
+                                uint32_t pool_cells, bool warp_mma_instances, const uint32_t* io_status,
+                                const uint32_t* row_map, const uint32_t* n_rows) {
     const shrike_moe_config& c = m->cfg;
     const Workspace& ws = m->ws;
     cudaError_t e = cudaMemsetAsync(ws.slot_of_expert, 0xff, c.num_experts * 4, st);
@@ -124,7 +127,7 @@ cudaError_t launch_prefill_plan(const shrike_moe* m, cudaStream_t st, const uint
                                                     ws.inst, ws.n_inst, ws.status);
     const uint32_t items = T * (c.d / 8);
     prefill_xprep_kernel<<<min(2048u, (items + 255) / 256), 256, 0, st>>>(
-        x, T, c.d, c.group_size, c.act_dtype, c.weight_bits == 4 ? 1u : 0u, ws.xh, ws.xsum, ws.status);
+        x, T, c.d, c.group_size, c.act_dtype, c.weight_bits == 4 ? 1u : 0u, ws.xh, ws.xsum, ws.status, row_map, n_rows);
     return cudaGetLastError();
 }
 

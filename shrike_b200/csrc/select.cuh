@@ -107,7 +107,9 @@ struct alignas(16) SelectSmem {
 // rounds: every expert counts the experts that beat it ((score desc, id asc) is a total order, so
 // the count is its rank). Warp w ranks its 64 experts among themselves and keeps the best 8;
 // warp 0 ranks the 32 survivors. Lane r of warp 0 returns the r-th pick; call from all threads.
-template <class A>
+// CG: read the logits past L1 (they were written by other blocks of this launch); false for a
+// copy that already sits in shared memory.
+template <bool CG = true, class A>
 __device__ __forceinline__ void select_row_block(const float* lg, const A& a, SelectSmem& ss, uint32_t& out_id,
                                                  float& out_w) {
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -115,7 +117,8 @@ __device__ __forceinline__ void select_row_block(const float* lg, const A& a, Se
     if (tid < 128) {
         // both logits (and biases) are requested before either is used: one L2 round trip, not two
         const uint32_t e0 = tid, e1 = tid + 128;
-        const float raw0 = e0 < a.ne ? __ldcg(lg + e0) : 0.f, raw1 = e1 < a.ne ? __ldcg(lg + e1) : 0.f;
+        const float raw0 = e0 < a.ne ? (CG ? __ldcg(lg + e0) : lg[e0]) : 0.f;
+        const float raw1 = e1 < a.ne ? (CG ? __ldcg(lg + e1) : lg[e1]) : 0.f;
         uint16_t lb0 = 0, lb1 = 0;
         if (a.logit_bias) {
             if (e0 < a.ne) lb0 = a.logit_bias[e0];
@@ -167,7 +170,7 @@ __device__ __forceinline__ void select_row_block(const float* lg, const A& a, Se
             my_score = score_of_key(ss.sel_key[lane]);
             my_id = ss.sel_id[lane];
         }
-        out_w = selection_weight<true>(lg, a, lane, my_score, my_id);
+        out_w = selection_weight<CG>(lg, a, lane, my_score, my_id);
         out_id = my_id;
     }
     __syncthreads();   // the scratch is reused by the next row

@@ -487,7 +487,7 @@ umma_expert_kernel(const ExpertArgs a, const ChunkInstance* __restrict__ inst, c
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
                     const float v = glu_epilogue(__uint_as_float(g[j]) + gab, __uint_as_float(u[j]) + uab, a.activation);
-                    if ((uint32_t)j < live) *p = __half_as_ushort(__float2half_rn(v));
+                    if ((uint32_t)j < live) *p = act_to_half_bits(v, a.status);
                     p += F;
                 }
             }

@@ -287,6 +287,39 @@ class MoE:
             weights_host.data_ptr() if weights_host is not None else None))
 
 
+class DecodeStack:
+    """Stacked MoE layers behind `shrike_decode_stack_forward_host`: one decode step with host activations in
+    and out (copies inside the call). `layers`: (moe, pool, routed_offsets, layer index, router, shared)."""
+
+    def __init__(self, layers, max_rows: int):
+        self._lib = capi.load()
+        self._keep = []
+        arr = (capi.StackLayer * len(layers))()
+        for i, (moe, pool, off, layer, router, shared) in enumerate(layers):
+            ops = router.to_c()
+            self._keep += [ops, off, shared, router]
+            arr[i] = capi.StackLayer(moe._h, pool._h, C.pointer(off), moe.residency_row(layer), C.pointer(ops),
+                                     C.pointer(shared) if shared is not None else None)
+        self._first = layers[0][0]
+        h = C.c_void_p()
+        self._first._check(self._lib.shrike_decode_stack_create(arr, len(layers), max_rows, C.byref(h)))
+        self._h = h
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            self._lib.shrike_decode_stack_destroy(self._h)
+            self._h = None
+
+    def forward_host(self, rows_host: torch.Tensor, out_host: torch.Tensor) -> None:
+        """rows_host [(layers + 1), T, d]: block 0 enters layer 0, block l is added to the residual stream
+        before layer l; out_host [T, d] receives the stream after the last layer."""
+        for t in (rows_host, out_host):
+            if t.is_cuda or not t.is_contiguous():
+                raise ValueError("host operands must be contiguous CPU tensors")
+        self._first._check(self._lib.shrike_decode_stack_forward_host(
+            self._h, _stream(), rows_host.data_ptr(), rows_host.shape[1], out_host.data_ptr()))
+
+
 def encode_router_static(config: MoEConfig, operands: RouterOperands, hidden: torch.Tensor,
                          out_indices: torch.Tensor, out_weights: torch.Tensor,
                          out_shared_gate: Optional[torch.Tensor] = None, query_count: Optional[int] = None,

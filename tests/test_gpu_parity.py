@@ -78,27 +78,28 @@ def test_decode_half_precision_in(cuda_device, act_dtype, y_dtype):
     layer.close()
 
 
-def ulps_bf16(a: np.ndarray, b: np.ndarray) -> np.ndarray:
-    """Distance between two bf16-representable arrays in units of the last place (sign-magnitude order)."""
-    def key(v):
-        bits = (np.asarray(v, np.float32).view(np.uint32) >> 16).astype(np.int64)
-        return np.where(bits & 0x8000, -(bits & 0x7FFF), bits)
-    return np.abs(key(a) - key(b))
+def bf16_ulp(v: np.ndarray) -> np.ndarray:
+    """Spacing of bf16 values at |v| (8 significant bits)."""
+    e = np.floor(np.log2(np.maximum(np.abs(v).astype(np.float64), 2.0 ** -126)))
+    return 2.0 ** (e - 7)
 
 
 @pytest.mark.parametrize("prefill", [False, True])
 def test_bf16_output_is_the_oracle_output_rounded_once(cuda_device, prefill):
-    """y_dtype = bf16 rounds the fp32 sums once on store: every element is within one bf16 unit in the last
-    place of the oracle's y rounded to bf16 (not a loosened L2 bound), except where the fp32 values sit
-    closer to a rounding boundary than the 1e-3 parity error; those may move by one more."""
+    """y_dtype = bf16 rounds the fp32 sums once on store. Per element (not a loosened L2 bound): the stored
+    value is within one bf16 unit in the last place of the oracle's y rounded to bf16, plus the absolute
+    error the 1e-3 relative-L2 bar allows before rounding (which decides elements close to zero)."""
     cfg = small_config(act_dtype=capi.DTYPE_BF16, y_dtype=capi.DTYPE_BF16, d=256, f=128, shared_f=128,
                        max_tokens=128)
     layer = Layer(cfg)
     x = inputs(70 if prefill else 6, 256, seed=17)
     y, ids, w, _ = layer.forward(x, prefill=prefill)
     y_ref = layer.oracle_forward(x, ids, w)
-    d = ulps_bf16(y, fx.round_bf16(y_ref))
-    assert d.max() <= 2 and (d <= 1).mean() > 0.999, f"max {d.max()} ulp, {(d > 1).sum()} elements beyond 1 ulp"
+    assert (fx.round_bf16(y) == y).all()
+    rms = float(np.sqrt(np.mean(y_ref.astype(np.float64) ** 2)))
+    excess = np.abs(y.astype(np.float64) - fx.round_bf16(y_ref)) - bf16_ulp(y_ref) - 3e-3 * rms
+    assert excess.max() <= 0, f"{(excess > 0).sum()} elements beyond one bf16 ulp + the parity error"
+    # and the rounding is the only loss: the same call with fp32 y meets the 1e-3 bar (test_decode_half_precision_in)
     layer.close()
 
 
