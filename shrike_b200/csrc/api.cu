@@ -257,6 +257,7 @@ int shrike_moe_create(const shrike_moe_config* config, int device, shrike_moe** 
     cudaDeviceGetAttribute(&m->sm_count, cudaDevAttrMultiProcessorCount, device);
     // switches for tests and diagnostics, read once here and never on the per-layer path
     m->no_pdl = getenv("SHRIKE_NO_PDL") != nullptr;
+    m->cooperative = getenv("SHRIKE_COOPERATIVE") != nullptr;
     const char* path = getenv("SHRIKE_PREFILL_PATH");
     m->force_warp_mma = path && strcmp(path, "mma") == 0;
     const shrike_moe_config& c = m->cfg;
@@ -302,8 +303,9 @@ int shrike_moe_create(const shrike_moe_config* config, int device, shrike_moe** 
         A(&w.fused_epoch, 4);
     } else {
         free(w.fused_geom);
-    free(w.fused_maps);
+        free(w.fused_maps);
         w.fused_geom = nullptr;
+        w.fused_maps = nullptr;
     }
     if (!ok) {
         free_workspace(w);

@@ -7,14 +7,17 @@
 //   moe_phase2_down_reduce_spec_k8 / phase2_finish  moe.metal:889-893, 1008-1057
 //   shared expert (SharedExpertRuntime)             SharedExpertInt4.swift:251-342
 //
-// One persistent block per SM. A layer's bytes (nine 1.7 MB expert blocks at the Qwen shape) are
-// about as large as the chip's shared memory, so after the selection every block asks for ALL of
-// its share at once: one producer lane issues a few large tiled TMA copies (cp.async.bulk.tensor,
-// no multicast) into a ring of shared-memory slots, each slot completing on an mbarrier, and eight
-// consumer warps walk the slots with the dequant-fused skinny tiles (packed words -> exact fp16
-// integers with one logic op per register, mma.sync m16n8k16, fp32 accumulate, one fused
-// multiply-add per group with the scale and one with the zero-point bias). HBM streams the whole
-// layer in one burst instead of one load-then-compute pass per block and per launch.
+// One persistent block per SM: a producer warp and sixteen consumer warps. A layer's bytes (nine 1.7 MB
+// expert blocks at the Qwen shape) are about as large as the chip's shared memory, so as soon as the
+// instance list is known every block asks for ALL of its share: the lanes of the producer warp each
+// issue one unit's tiled TMA copies (cp.async.bulk.tensor, no multicast; the lanes run copy by copy,
+// so the copy engine's queue holds the small scale/bias boxes first and the weight boxes in unit
+// order) into a ring of shared-memory slots, each slot completing on an mbarrier. The consumers walk
+// the slots with the dequant-fused skinny tiles (packed words -> exact fp16 integers with one logic
+// op per register, mma.sync m16n8k16, fp32 accumulate, one fused multiply-add per group with the
+// scale and one with the zero-point bias): gate/up units by groups of four warps, a unit per group
+// at a time; the down tile of a block by all sixteen warps, one meeting per tile. What a block does
+// is a closed form of its index (BlockPlan), so no warp walks a list to find its work.
 //
 // The tensor maps describe a weight matrix as (bytes of one group of a row, rows, groups along the
 // row [, gate/up], cells): a box of 8 or 16 rows lands in shared memory as [group][row][group
@@ -25,14 +28,26 @@
 // warps: 3.5 TB/s, and per-unit mbarrier arrivals serialise the units.)
 //
 // What used to be launch boundaries are data hand-overs through L2, with no barrier object:
-//   logits   every block computes its expert rows and publishes {epoch, value} as one 64-bit word
-//            per expert; every block gathers all words and repeats the (cheap) selection itself;
-//   acts     a phase-1 unit (8 gate rows + 8 up rows of one expert) publishes its 8 fp16
+//   logits   every block computes its expert rows (fp32 rows were bulk-copied to shared memory
+//            before the dependency wait) and publishes {epoch, value} as one 64-bit word per expert;
+//   route    the last eight blocks (they have the fewest router rows) gather all words, rank them
+//            (comparison counting, no serial rounds), look the picks up in the residency table and
+//            publish the instance list as 16-byte entries that each carry the epoch; every other
+//            block's producer warp reads one of the eight copies;
+//   acts     a gate/up unit (8 gate rows + 8 up rows of one expert) publishes its 8 fp16
 //            activations as 16 bytes whose halves are never the sentinel 0xFFFF; the blocks that
 //            own a tile of output rows poll until no half is the sentinel. The buffer of the
 //            previous call (other parity of the epoch) is reset by this call.
 // Every wait -- mbarrier or global poll -- is bounded: it gives up, reports through the status
-// word and the block runs on to its end. The launch is cooperative (all blocks resident).
+// word and the block runs on to its end.
+//
+// What bounds the kernel (measured with per-warp cycle stamps): not HBM. A warp of this code issues
+// an instruction every 5 to 10 cycles (dependent shared-memory loads, logic ops and tiles; four warps
+// share an issue port), so the serial chain router row -> gather -> rank -> publish -> read ->
+// request -> first bytes -> gate/up -> exchange -> down costs about 18 us at the Qwen shape, of which
+// the bytes need 2.4. Code that runs once per launch also pays for its instruction fetches (a body
+// beyond about 32 KB streams at 6 bytes a cycle), which is why the waits, the walkers and the tile
+// bodies are out of line and shared.
 //
 // MMA row slot s of a unit is row s of its box: rows 0..7 gate and 8..15 up in phase 1 (GLU partners
 // in one thread), 16 consecutive down rows in phase 2.
@@ -47,9 +62,13 @@ namespace shrike {
 
 namespace {
 
-constexpr uint32_t kPW = 1;                          // producer warps (one lane issues the copies)
-constexpr uint32_t kCW = 8;                          // consumer warps
-constexpr uint32_t kFusedThreads = (kPW + kCW + 1) * 32;   // + epilogue warp
+constexpr uint32_t kGroups = 4;                      // consumer groups: each takes every fourth unit of the block
+constexpr uint32_t kGroupWarps = 4;                  // warps of a group: they split a unit's columns
+constexpr uint32_t kCW = kGroups * kGroupWarps;      // consumer warps
+constexpr uint32_t kSelWarps = 8;                    // consumer warps that take part in the selection (32 experts each)
+constexpr uint32_t kFusedThreads = (1 + kCW) * 32;   // + the producer warp (its lanes issue the copies)
+constexpr uint32_t kMaxUnits = 64;                   // units of one block
+constexpr uint32_t kSelectors = 8;                   // blocks that select and publish the instance list
 constexpr uint32_t kMaxInst = SHRIKE_MAX_TOP_K + 1;  // picks + shared expert
 constexpr uint32_t kMaxSlots = 16;
 constexpr uint32_t kMaxRouterRowsPerBlock = 2;
@@ -128,6 +147,21 @@ struct FQ {
     static constexpr float kOffOdd = BITS == 4 ? 64.0f : 1024.0f;
 };
 
+// One unit of work of a block, as every warp reads it from the block's table (8 bytes).
+//   bits 0     kind: 0 phase 1 (8 gate + 8 up rows of one instance), 1 phase 2 (16 output rows x a pack)
+//   bit  1     the shared expert's geometry
+//   bits 4-7   first instance          bits 8-11  instances in the pack (0: the layer has no expert work at all)
+//   bits 20-24 ring slot               bit 25     parity of the slot's round
+struct alignas(8) UnitRec {
+    uint32_t bits, r0;
+    __device__ uint32_t kind() const { return bits & 1u; }
+    __device__ uint32_t sh() const { return (bits >> 1) & 1u; }
+    __device__ uint32_t inst() const { return (bits >> 4) & 15u; }
+    __device__ uint32_t count() const { return (bits >> 8) & 15u; }
+    __device__ uint32_t slot() const { return (bits >> 20) & 31u; }
+    __device__ uint32_t parity() const { return (bits >> 25) & 1u; }
+};
+
 struct RouteSmem {
     uint32_t cell[kMaxInst];    // per instance (shared expert first when there is one)
     float w[kMaxInst];          // route weight, or the shared expert's gate
@@ -135,32 +169,46 @@ struct RouteSmem {
 };
 
 struct FusedStatic {
-    uint64_t table[SHRIKE_MAX_EXPERTS];
+    alignas(16) uint64_t table[SHRIKE_MAX_EXPERTS];
     float logits[SHRIKE_MAX_EXPERTS + 1];
-    uint32_t cand_key[kCW * 8], cand_id[kCW * 8];   // every consumer warp's best picks
+    // selection: {key, ~expert id} of every expert, every selecting warp's best eight, the picks in rank order
+    alignas(16) unsigned long long ckeys[SHRIKE_MAX_EXPERTS], cand[kSelWarps * 8], sel[SHRIKE_MAX_TOP_K];
     RouteSmem route;
-    float red[2][kCW][16];
-    alignas(16) uint16_t act_stage[8];
-    uint64_t full[kMaxSlots], empty[kMaxSlots], red_full[2], red_empty[2], rw_bar;
+    UnitRec units[kMaxUnits];                      // UnitRec, in the order the block takes them
+    float red[kGroups][2][kGroupWarps][16];        // a group's partial sums, two units deep
+    float red2[2][kCW][16];                        // every consumer warp's sums of a down tile, two tiles deep
+    alignas(16) uint16_t act_stage[kGroups][8];
+    uint64_t full[kMaxSlots], empty[kMaxSlots], rw_bar, tab_bar;
     uint32_t epoch, failed;
 };
 
-__device__ __forceinline__ bool wait_bar(uint64_t* bar, uint32_t parity) {
-    const uint32_t addr = smem_u32(bar);
-    for (uint32_t it = 0; it < (1u << 21); ++it) {
-        uint32_t ok;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
-        if (ok) return true;
+__device__ __forceinline__ bool try_wait_bar(uint32_t addr, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
+    return ok != 0;
+}
+// The bounded part of a wait, out of line: the kernel's instruction stream holds one copy of it.
+__device__ __noinline__ bool wait_bar_slow(uint32_t addr, uint32_t parity) {
+#pragma unroll 1
+    for (uint32_t it = 0; it < (1u << 17); ++it) {
+        if (try_wait_bar(addr, parity)) return true;
         if (it > 128) __nanosleep(32);
     }
     return false;
 }
+__device__ __forceinline__ bool wait_bar(uint64_t* bar, uint32_t parity) {
+    const uint32_t addr = smem_u32(bar);
+    return try_wait_bar(addr, parity) || wait_bar_slow(addr, parity);
+}
 __device__ __forceinline__ void bar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void bar_arrive_n(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
 }
 __device__ __forceinline__ unsigned long long ld_relaxed_u64(const unsigned long long* p) {
     unsigned long long v;
@@ -180,26 +228,24 @@ __device__ __forceinline__ void st_relaxed_v4(void* p, uint4 v) {
     asm volatile("st.relaxed.gpu.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
                  : "memory");
 }
-__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kCW * 32) : "memory"); }
+// Named barriers: 1 the selecting warps, 2 all consumer warps, 3.. one per consumer group.
+__device__ __forceinline__ void select_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kSelWarps * 32) : "memory"); }
+__device__ __forceinline__ void consumers_sync() { asm volatile("bar.sync 2, %0;" ::"n"(kCW * 32) : "memory"); }
+__device__ __forceinline__ void group_sync(uint32_t group) {
+    asm volatile("bar.sync %0, %1;" ::"r"(3u + group), "n"(kGroupWarps * 32) : "memory");
+}
 
 __device__ __forceinline__ bool has_sentinel(uint4 v) {
     auto bad = [](uint32_t w) { return (w & 0xffffu) == 0xffffu || (w >> 16) == 0xffffu; };
     return bad(v.x) || bad(v.y) || bad(v.z) || bad(v.w);
 }
 
-// One unit of work of a block. The producer, the consumers and the epilogue warp walk the same sequence.
-struct Unit {
-    uint32_t kind;    // 0: phase 1 (8 gate + 8 up rows of one instance); 1: phase 2 (16 output rows x a pack)
-    uint32_t inst;    // first instance
-    uint32_t count;   // phase 2: instances in the pack (0: the layer has no expert work at all)
-    uint32_t r0;      // first weight row
-    uint32_t sh;      // the shared expert's geometry
-    uint32_t last;    // phase 2: last pack of its tile
-};
-
-struct Walker {
-    uint32_t n_blk, blk, su, upe, n_routed, has_shared, tiles, epp;
-    uint32_t phase, idx, pack;
+// What a block does, in closed form (every lane can work out any unit on its own): phase-1 units blk, blk +
+// n_blk, ... of the sequence [shared expert's units | first pick's | second pick's ...], then the packs of the
+// output tiles n_blk - 1 - blk, + n_blk, ... (blocks that are light in one phase are heavy in the other).
+struct BlockPlan {
+    uint32_t n_blk, blk, su, upe, has_shared, tiles, epp, n_slots;
+    uint32_t n_routed, n1, n_tiles, packs, packs_eff, n_units;
 
     __device__ void init(const FusedArgs& a) {
         n_blk = gridDim.x; blk = blockIdx.x;
@@ -208,43 +254,48 @@ struct Walker {
         upe = a.f / 8;
         tiles = a.d / 16;
         epp = a.g.experts_per_pack;
-        n_routed = 0;
-        phase = 0; idx = blk; pack = 0;
+        n_slots = a.g.n_slots;
+        const uint32_t t0 = n_blk - 1u - blk;
+        n_tiles = t0 < tiles ? (tiles - t0 + n_blk - 1u) / n_blk : 0u;
     }
-    // Next unit; false when exhausted, or when the next one needs the routing result and `routed` is false.
-    __device__ __noinline__ bool next(Unit& u, bool routed) {
-        if (phase == 0) {
-            if (idx < su) {
-                u = Unit{0u, 0u, 1u, idx * 8u, 1u, 0u};
-                idx += n_blk;
-                return true;
-            }
-            if (!routed) return false;
-            const uint32_t k = idx - su;
-            if (k < n_routed * upe) {
-                u = Unit{0u, has_shared + k / upe, 1u, (k % upe) * 8u, 0u, 0u};
-                idx += n_blk;
-                return true;
-            }
-            phase = 1; idx = n_blk - 1u - blk; pack = 0;
-        }
-        if (!routed) return false;
-        if (idx >= tiles) return false;
-        const uint32_t routed_packs = (n_routed + epp - 1u) / epp;
-        const uint32_t packs = has_shared + routed_packs;
-        if (packs == 0) {
-            u = Unit{1u, 0u, 0u, idx * 16u, 0u, 1u};
-            idx += n_blk;
-            return true;
-        }
-        if (has_shared && pack == 0) {
-            u = Unit{1u, 0u, 1u, idx * 16u, 1u, packs == 1u ? 1u : 0u};
+    // phase-1 units of the shared expert: they do not depend on the routing
+    __device__ uint32_t shared_units() const { return blk < su ? (su - blk + n_blk - 1u) / n_blk : 0u; }
+    __device__ void route(uint32_t routed) {
+        n_routed = routed;
+        const uint32_t total1 = su + n_routed * upe;
+        n1 = blk < total1 ? (total1 - blk + n_blk - 1u) / n_blk : 0u;
+        packs = has_shared + (n_routed + epp - 1u) / epp;
+        packs_eff = packs ? packs : 1u;
+        n_units = n1 + n_tiles * packs_eff;
+    }
+    __device__ UnitRec phase1(uint32_t i) const {
+        const uint32_t idx = blk + i * n_blk;
+        UnitRec u;
+        if (idx < su) {
+            u.bits = 0u | 2u | (1u << 8);
+            u.r0 = idx * 8u;
         } else {
-            const uint32_t p = pack - has_shared;
-            u = Unit{1u, has_shared + p * epp, min(epp, n_routed - p * epp), idx * 16u, 0u, pack + 1u == packs ? 1u : 0u};
+            const uint32_t k = idx - su, e = k / upe;
+            u.bits = ((has_shared + e) << 4) | (1u << 8);
+            u.r0 = (k - e * upe) * 8u;
         }
-        if (++pack == packs) { pack = 0; idx += n_blk; }
-        return true;
+        u.bits |= ((i % n_slots) << 20) | (((i / n_slots) & 1u) << 25);
+        return u;
+    }
+    __device__ UnitRec unit(uint32_t i) const {
+        if (i < n1) return phase1(i);
+        const uint32_t j = i - n1, m = j / packs_eff, p = j - m * packs_eff;
+        UnitRec u;
+        u.r0 = (n_blk - 1u - blk + m * n_blk) * 16u;
+        u.bits = 1u | ((i % n_slots) << 20) | (((i / n_slots) & 1u) << 25);
+        if (packs == 0u) return u;   // count 0
+        if (has_shared && p == 0u) {
+            u.bits |= 2u | (1u << 8);
+        } else {
+            const uint32_t q = p - has_shared;
+            u.bits |= ((has_shared + q * epp) << 4) | (min(epp, n_routed - q * epp) << 8);
+        }
+        return u;
     }
 };
 
@@ -383,7 +434,9 @@ __device__ __noinline__ float2 group_sums(const uint16_t* row, uint32_t grp) {
 }
 
 #ifdef SHRIKE_TRACE
-#define FUSED_TS(slot) do { if (a.trace && lane == 0) a.trace[(size_t)blockIdx.x * 16 + (slot)] = globaltimer_ns(); } while (0)
+// the SM's cycle counter: cheap to read (the global timer was measured to hold a warp for about 2 us per read).
+// Every warp keeps 32 stamps.
+#define FUSED_TS(slot) do { if (a.trace && lane == 0) a.trace[((size_t)blockIdx.x * (kFusedThreads / 32) + warp) * 32 + (slot)] = (uint64_t)clock64(); } while (0)
 #else
 #define FUSED_TS(slot) do { } while (0)
 #endif
@@ -395,11 +448,6 @@ __device__ __forceinline__ void prefetch_map(const CUtensorMap* map) {
 }
 
 // Tiled TMA loads (no multicast): the box lands densely, innermost dimension first.
-__device__ __forceinline__ void tma_3d(uint32_t dst, const CUtensorMap* map, int32_t c0, int32_t c1, int32_t c2, uint64_t* bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
-        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(smem_u32(bar)) : "memory");
-}
 __device__ __forceinline__ void tma_4d(uint32_t dst, const CUtensorMap* map, int32_t c0, int32_t c1, int32_t c2, int32_t c3,
                                        uint64_t* bar) {
     asm volatile(
@@ -413,55 +461,54 @@ __device__ __forceinline__ void tma_5d(uint32_t dst, const CUtensorMap* map, int
         ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4), "r"(smem_u32(bar)) : "memory");
 }
 
-// Top-k of the logits in shared memory by the eight consumer warps, then a merge by the first of them: warp w
-// holds experts 32w..32w+31 one per lane and takes its best top_k by rounds of a warp-wide maximum (equal keys:
-// the lowest lane, i.e. the lowest expert id); the candidates are merged the same way. The picks and their
-// order are those of router_topk_select_body's insertion scan (moe.metal:436-456). Lane r of the merging warp
-// returns the r-th pick. `cw`: consumer warp index; all consumer warps call it.
-template <class A>
-__device__ __forceinline__ void select_warps(const float* lg, const A& a, uint32_t* cand_key, uint32_t* cand_id,
-                                             uint32_t cw, uint32_t lane, uint32_t& out_id, float& out_w) {
+// Top-k of the logits in shared memory by the first kSelWarps consumer warps, without serial rounds: (score
+// descending, expert id ascending) is a total order, so the number of experts that beat one is its rank.
+// An expert's key and the complement of its id make one 64-bit word whose unsigned order is that order.
+// Warp w ranks experts 32w..32w+31 among themselves and keeps the best eight; two warps rank the 64
+// survivors. The picks and their order are those of router_topk_select_body's insertion scan
+// (moe.metal:436-456). Lane r of warp 0 returns the r-th pick. All kSelWarps warps call it.
+template <class A, class S>
+__device__ __forceinline__ void select_ranked(const float* lg, const A& a, S& st, uint32_t cw, uint32_t lane,
+                                              uint32_t& out_id, float& out_w) {
     const uint32_t e = cw * 32 + lane;
     uint32_t key = 0;
     if (e < a.ne) key = selection_key_of(lg[e], a.logit_bias ? bf16_bits_to_f32(a.logit_bias[e]) : 0.0f, a);
-    for (uint32_t r = 0; r < a.top_k; ++r) {
-        const uint32_t best = __reduce_max_sync(0xffffffffu, key);
-        const uint32_t who = __ffs(__ballot_sync(0xffffffffu, key == best && best != 0u));   // 0: nobody left
-        if (lane == 0) {
-            cand_key[cw * 8 + r] = who ? best : 0u;
-            cand_id[cw * 8 + r] = who ? cw * 32 + who - 1 : 0u;
+    const unsigned long long mine = ((unsigned long long)key << 32) | (unsigned long long)(0xffffffffu - e);
+    st.ckeys[e] = mine;
+    __syncwarp();
+    {
+        const ulonglong2* kv = (const ulonglong2*)(st.ckeys + cw * 32);
+        uint32_t rank = 0;
+#pragma unroll
+        for (uint32_t j = 0; j < 16; ++j) {
+            const ulonglong2 v = kv[j];
+            rank += (v.x > mine ? 1u : 0u) + (v.y > mine ? 1u : 0u);
         }
-        if (who && lane == who - 1) key = 0u;
+        if (rank < 8) st.cand[cw * 8 + rank] = mine;   // the words are distinct: one lane per rank
     }
-    consumer_sync();
+    select_sync();
+    if (cw < 2) {
+        const unsigned long long c = st.cand[cw * 32 + lane];
+        const ulonglong2* cv = (const ulonglong2*)st.cand;
+        uint32_t rank = 0;
+#pragma unroll
+        for (uint32_t j = 0; j < kSelWarps * 4; ++j) {
+            const ulonglong2 v = cv[j];
+            rank += (v.x > c ? 1u : 0u) + (v.y > c ? 1u : 0u);
+        }
+        if (rank < SHRIKE_MAX_TOP_K) st.sel[rank] = c;
+    }
+    select_sync();
     out_id = 0;
     out_w = 0.f;
     if (cw == 0) {
-        // 64 candidates (8 warps x 8, unused entries 0), two per lane: lane l holds warp l/4's entries 2(l%4), +1
-        uint32_t k0 = 0, k1 = 0, i0 = 0, i1 = 0;
-        {
-            const uint32_t w = lane >> 2, q = (lane & 3) * 2;
-            if (q < a.top_k) { k0 = cand_key[w * 8 + q]; i0 = cand_id[w * 8 + q]; }
-            if (q + 1 < a.top_k) { k1 = cand_key[w * 8 + q + 1]; i1 = cand_id[w * 8 + q + 1]; }
-        }
         float my_score = -INFINITY;
         uint32_t my_id = 0;
-        for (uint32_t r = 0; r < a.top_k; ++r) {
-            const uint32_t best = __reduce_max_sync(0xffffffffu, max(k0, k1));
-            uint32_t cand = 0xffffffffu;
-            if (best != 0u) {
-                if (k1 == best) cand = i1;
-                if (k0 == best) cand = min(cand, i0);
-            }
-            const uint32_t win = __reduce_min_sync(0xffffffffu, cand);   // equal keys: the lower expert id
-            if (win != 0xffffffffu) {
-                if (k0 == best && i0 == win) k0 = 0u;
-                else if (k1 == best && i1 == win) k1 = 0u;
-            }
-            if (lane == r) {
-                my_score = score_of_key(win == 0xffffffffu ? 0u : best);
-                my_id = win == 0xffffffffu ? 0u : min(win, a.ne - 1u);
-            }
+        if (lane < a.top_k) {
+            const unsigned long long c = st.sel[lane];
+            const uint32_t k = (uint32_t)(c >> 32);
+            my_score = score_of_key(k);   // key 0: no candidate, the scan's initial -inf and id 0
+            my_id = k ? min(0xffffffffu - (uint32_t)c, a.ne - 1u) : 0u;
         }
         out_w = selection_weight<false>(lg, a, lane, my_score, my_id);
         out_id = my_id;
@@ -492,23 +539,21 @@ __global__ void __launch_bounds__(kFusedThreads, 1) decode_layer_kernel(const __
     const uint32_t ring_smem = smem_u32(ring);
     const uint32_t has_shared = a.shared_block ? 1u : 0u;
     const uint32_t gmax2 = G.acts_stride / GROUP;
-    const bool is_producer = warp < kPW, is_consumer = warp >= kPW && warp < kPW + kCW;
-    const uint32_t cw = warp - kPW;    // consumer index of the consumer warps
+    const bool is_producer = warp == 0;
+    const uint32_t cw = warp - 1u;     // consumer index of the consumer warps
 
-    if (warp == 0) FUSED_TS(0);
-    Walker prod;   // the producers' position survives the routing
-    prod.init(a);
-    uint32_t prod_n = 0;
+    FUSED_TS(0);
+    BlockPlan plan;
+    plan.init(a);
 
     // ---- before the previous kernel in the stream is known to be complete: nothing that it produces ----
-    if (tid == 0) {
-        for (uint32_t s = 0; s < G.n_slots; ++s) { mbar_init(&st.full[s], 1); mbar_init(&st.empty[s], kCW); }
-        for (uint32_t s = 0; s < 2; ++s) { mbar_init(&st.red_full[s], kCW); mbar_init(&st.red_empty[s], 1); }
-        mbar_init(&st.rw_bar, 1);
-        fence_mbar_init();
-        st.failed = 0;
+    if (tid < G.n_slots) {
+        mbar_init(&st.full[tid], 1);
+        mbar_init(&st.empty[tid], kGroupWarps);
     }
-    for (uint32_t e = tid; e < a.ne; e += kFusedThreads) st.table[e] = a.table[e];
+    if (tid == 32) { mbar_init(&st.rw_bar, 1); mbar_init(&st.tab_bar, 1); }
+    if (tid <= 32) fence_mbar_init();
+    if (tid == 0) st.failed = 0;
     {   // the descriptors this block may use: the shared expert's, and every pool chunk's
         const uint32_t n_chunks = (a.pool.cells + a.pool.cells_per_chunk - 1) / a.pool.cells_per_chunk;
         const uint32_t which = tid >> 2, kind = tid & 3;
@@ -516,14 +561,13 @@ __global__ void __launch_bounds__(kFusedThreads, 1) decode_layer_kernel(const __
         if (tid < 4 * (SHRIKE_MAX_POOL_CHUNKS + 1) && wanted)
             prefetch_map(kind == 0 ? &a.maps.w1[which] : kind == 1 ? &a.maps.m1[which] : kind == 2 ? &a.maps.w2[which] : &a.maps.m2[which]);
     }
-    // this block's router rows (fp32 rows are fetched into registers now, used after the wait)
     const uint32_t router_rows = a.ne + (a.gate_row ? 1u : 0u);
     const uint32_t my_row = blockIdx.x + cw * gridDim.x;
-    const bool routes = is_consumer && cw < G.router_rows_per_block && my_row < router_rows;
+    const bool routes = !is_producer && cw < G.router_rows_per_block && my_row < router_rows;
     const bool row_is_gate = routes && a.gate_row && my_row == a.ne;
     const bool row_f32 = a.rbits == 0 || row_is_gate;
     __syncthreads();   // barriers initialised
-    if (tid == 0) {
+    if (tid == 32) {
         // fp32 router rows (and the gate row) of this block -> shared memory, one bulk copy each
         uint32_t bytes = 0;
         for (uint32_t k = 0; k < G.router_rows_per_block; ++k) {
@@ -541,68 +585,141 @@ __global__ void __launch_bounds__(kFusedThreads, 1) decode_layer_kernel(const __
         }
     }
 
-    auto issue = [&](const Unit& u, uint32_t n) {
-        // lane 0 of the producer warp: a unit is one to four tiled copies that complete on the slot's barrier
-        const uint32_t slot = n % G.n_slots, round = n / G.n_slots;
-        if (round > 0 && !wait_bar(&st.empty[slot], (round - 1) & 1)) {
-            report_status(a.status, kStatusWaitTimeout);
-            st.failed = 1;
-        }
+    // One lane asks for one unit: one to four tiled copies that complete on the slot's barrier.
+    auto issue = [&](const UnitRec u) {
+        const uint32_t slot = u.slot();
         const uint32_t stage = ring_smem + slot * G.slot_bytes;
         uint64_t* bar = &st.full[slot];
-        if (u.kind == 0) {
-            const uint32_t cell = u.sh ? 0u : st.route.cell[u.inst];
-            const uint32_t mi = u.sh ? SHRIKE_MAX_POOL_CHUNKS : cell / a.pool.cells_per_chunk;
-            const int32_t cc = u.sh ? 0 : (int32_t)(cell % a.pool.cells_per_chunk);
+        const uint32_t sh = u.sh();
+        if (u.kind() == 0) {
+            const uint32_t cell = sh ? 0u : st.route.cell[u.inst()];
+            const uint32_t mi = sh ? SHRIKE_MAX_POOL_CHUNKS : cell / a.pool.cells_per_chunk;
+            const int32_t cc = sh ? 0 : (int32_t)(cell % a.pool.cells_per_chunk);
             mbar_expect_tx(bar, 16 * rb1 + 64 * GD + (a.expert_bias ? 32u : 0u));
+            tma_5d(stage + G.p1_meta_off, &a.maps.m1[mi], 0, (int32_t)(u.r0 / 8), 0, 0, cc, bar);   // the small one first
             tma_5d(stage, &a.maps.w1[mi], 0, (int32_t)u.r0, 0, 0, cc, bar);
-            tma_5d(stage + G.p1_meta_off, &a.maps.m1[mi], 0, (int32_t)(u.r0 / 8), 0, 0, cc, bar);
             if (a.expert_bias) {
-                const uint8_t* base = u.sh ? a.shared_block : pool_cell_base(a.pool, cell);
-                const Offsets3& off = u.sh ? a.shared : a.routed;
+                const uint8_t* base = sh ? a.shared_block : pool_cell_base(a.pool, cell);
+                const Offsets3& off = sh ? a.shared : a.routed;
                 bulk_g2s(ring + (size_t)slot * G.slot_bytes + G.p1_ab_off, base + off.ab[0] + (size_t)u.r0 * 2, 16, bar);
                 bulk_g2s(ring + (size_t)slot * G.slot_bytes + G.p1_ab_off + 16, base + off.ab[1] + (size_t)u.r0 * 2, 16, bar);
             }
         } else {
-            const uint32_t F = u.sh ? a.f_shared : a.f, G2 = F / GROUP, rb2 = F * BITS / 8;
-            mbar_expect_tx(bar, u.count * (16 * rb2 + 64 * G2 + (a.expert_bias ? 32u : 0u)));   // count 0: the arrival alone
-            for (uint32_t q = 0; q < u.count; ++q) {
-                const uint32_t cell = u.sh ? 0u : st.route.cell[u.inst + q];
-                const uint32_t mi = u.sh ? SHRIKE_MAX_POOL_CHUNKS : cell / a.pool.cells_per_chunk;
-                const int32_t cc = u.sh ? 0 : (int32_t)(cell % a.pool.cells_per_chunk);
-                const uint32_t eb = stage + q * G.p2_expert_bytes[u.sh];
+            const uint32_t F = sh ? a.f_shared : a.f, G2 = F / GROUP, rb2 = F * BITS / 8;
+            const uint32_t count = u.count();
+            mbar_expect_tx(bar, count * (16 * rb2 + 64 * G2 + (a.expert_bias ? 32u : 0u)));   // count 0: the arrival alone
+            for (uint32_t q = 0; q < count; ++q) {
+                const uint32_t cell = sh ? 0u : st.route.cell[u.inst() + q];
+                const uint32_t mi = sh ? SHRIKE_MAX_POOL_CHUNKS : cell / a.pool.cells_per_chunk;
+                const int32_t cc = sh ? 0 : (int32_t)(cell % a.pool.cells_per_chunk);
+                const uint32_t eb = stage + q * G.p2_expert_bytes[sh];
+                tma_4d(eb + G.p2_meta_off[sh], &a.maps.m2[mi], 0, (int32_t)(u.r0 / 8), 0, cc, bar);
                 tma_4d(eb, &a.maps.w2[mi], 0, (int32_t)u.r0, 0, cc, bar);
-                tma_4d(eb + G.p2_meta_off[u.sh], &a.maps.m2[mi], 0, (int32_t)(u.r0 / 8), 0, cc, bar);
                 if (a.expert_bias) {
-                    const uint8_t* base = u.sh ? a.shared_block : pool_cell_base(a.pool, cell);
-                    const Offsets3& off = u.sh ? a.shared : a.routed;
-                    bulk_g2s(ring + (size_t)slot * G.slot_bytes + q * G.p2_expert_bytes[u.sh] + G.p2_ab_off[u.sh],
+                    const uint8_t* base = sh ? a.shared_block : pool_cell_base(a.pool, cell);
+                    const Offsets3& off = sh ? a.shared : a.routed;
+                    bulk_g2s(ring + (size_t)slot * G.slot_bytes + q * G.p2_expert_bytes[sh] + G.p2_ab_off[sh],
                              base + off.ab[2] + (size_t)u.r0 * 2, 32, bar);
                 }
             }
         }
     };
 
-    // the shared expert's gate/up units do not depend on the routing (nor on the previous kernel): ask now
-    if (tid == 0) {
-        Unit u;
-        while (prod_n < G.n_slots && prod.next(u, false)) issue(u, prod_n++);
-    }
+    // the shared expert's gate/up units do not depend on the routing (nor on the previous kernel): the lanes
+    // of the producer warp ask for one each, now
+    const uint32_t n_pre = min(plan.shared_units(), G.n_slots);
+    if (is_producer && lane < n_pre) issue(plan.phase1(lane));
 
-    if (warp == 0) FUSED_TS(1);
+    FUSED_TS(1);
     pdl_wait();
-    if (warp == 0) FUSED_TS(2);
+    FUSED_TS(2);
 
-    // ---- the activation row, as it is, into shared memory (one round trip, every thread a piece; the epoch
-    // word travels in the same round trip); then this block's router rows from there ----
+    // ---- the activation row: every thread takes 8 elements in one round trip and leaves the fp16 operand
+    // copy (permuted for the tiles, clamped to the fp16 range), the fp32 copy the router multiplies, and --
+    // with the lanes that share a group -- the group's {sum x, sum offset*x} ----
     {
-        const uint32_t n16 = D * (a.act_dtype == SHRIKE_DTYPE_FP32 ? 4u : 2u) / 16;
-        uint4* xr = (uint4*)(dsm + G.off_xraw);
-        if (tid == 0) st.epoch = *(volatile const uint32_t*)a.epoch;
-        for (uint32_t c = tid; c < n16; c += kFusedThreads) xr[c] = __ldg((const uint4*)a.x + c);
+        if (tid == kFusedThreads - 1) st.epoch = *(volatile const uint32_t*)a.epoch;
+        float* xf_sm = (float*)(dsm + G.off_xraw);
+        constexpr uint32_t kLanes = GROUP / 8;   // lanes of a group
+        for (uint32_t base = warp * 32; base < D / 8; base += kFusedThreads) {
+            const uint32_t blk = base + lane;
+            const bool valid = blk < D / 8;
+            float v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = 0.f;
+            if (valid) {
+                if (a.act_dtype == SHRIKE_DTYPE_FP32) {
+                    const float4 lo = __ldg((const float4*)a.x + 2 * blk), hi = __ldg((const float4*)a.x + 2 * blk + 1);
+                    v[0] = lo.x; v[1] = lo.y; v[2] = lo.z; v[3] = lo.w; v[4] = hi.x; v[5] = hi.y; v[6] = hi.z; v[7] = hi.w;
+                } else {
+                    const uint4 raw = __ldg((const uint4*)a.x + blk);
+                    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        if (a.act_dtype == SHRIKE_DTYPE_FP16) {
+                            v[2 * j] = f16_bits_to_f32((uint16_t)(w[j] & 0xffffu));
+                            v[2 * j + 1] = f16_bits_to_f32((uint16_t)(w[j] >> 16));
+                        } else {
+                            v[2 * j] = __uint_as_float(w[j] << 16);
+                            v[2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+                        }
+                    }
+                }
+                ((float4*)xf_sm)[2 * blk] = make_float4(v[0], v[1], v[2], v[3]);
+                ((float4*)xf_sm)[2 * blk + 1] = make_float4(v[4], v[5], v[6], v[7]);
+            }
+            if (a.act_dtype != SHRIKE_DTYPE_FP16) {
+                bool over = false;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    if (fabsf(v[j]) > kHalfMax) {   // false for NaN, which passes through
+                        over = true;
+                        v[j] = copysignf(kHalfMax, v[j]);
+                    }
+                }
+                if (over) report_status(a.status, kStatusOperandRange);
+            }
+            uint16_t o[8];
+            float even = 0.f, odd = 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const __half h = __float2half_rn(v[j]);
+                o[perm_index(j, BITS == 4)] = __half_as_ushort(h);
+                if (BITS == 4 && (j & 1)) odd += __half2float(h);
+                else even += __half2float(h);
+            }
+            if (valid)
+                *(uint4*)(x_sm + (size_t)blk * 8) = make_uint4(o[0] | ((uint32_t)o[1] << 16), o[2] | ((uint32_t)o[3] << 16),
+                                                                 o[4] | ((uint32_t)o[5] << 16), o[6] | ((uint32_t)o[7] << 16));
+#pragma unroll
+            for (uint32_t m = 1; m < kLanes; m <<= 1) {
+                even += __shfl_xor_sync(0xffffffffu, even, m);
+                odd += __shfl_xor_sync(0xffffffffu, odd, m);
+            }
+            if (valid && (blk & (kLanes - 1)) == 0) xs_sm[blk / kLanes] = make_float2(even + odd, Q::kOffEven * even + Q::kOffOdd * odd);
+        }
     }
+    // the selecting blocks need the layer's residency table (a kernel before this one may have written it)
+    const uint32_t n_sel = min(kSelectors, gridDim.x);
+    const bool selector = blockIdx.x >= gridDim.x - n_sel;
+    const uint32_t tab_bytes = a.ne * 8u;
+    const bool tab_bulk = (tab_bytes & 15u) == 0 && ((uintptr_t)a.table & 15u) == 0;
+    if (selector) {
+        if (tid == 32) {
+            mbar_expect_tx(&st.tab_bar, tab_bulk ? tab_bytes : 0u);
+            if (tab_bulk) bulk_g2s(st.table, a.table, tab_bytes, &st.tab_bar);
+        }
+        if (!tab_bulk)
+            for (uint32_t e = tid; e < a.ne; e += kFusedThreads) st.table[e] = a.table[e];
+    }
+    FUSED_TS(16);
     __syncthreads();
-    const uint8_t* xraw = dsm + G.off_xraw;
+    const uint32_t epoch = st.epoch;
+    const uint32_t parity = epoch & 1u;
+    uint16_t* acts_mine = a.acts_pub + (size_t)parity * kMaxInst * G.acts_stride;
+    uint4* route_pub = (uint4*)(a.logits64 + ((a.ne + 2u) & ~1u));   // [n_sel][1 + kMaxInst] 16-byte entries
+
+    // ---- this block's router rows ----
     if (routes) {
         float acc;
         if (row_f32) {
@@ -610,166 +727,264 @@ __global__ void __launch_bounds__(kFusedThreads, 1) decode_layer_kernel(const __
             const uint16_t* es = row_is_gate ? nullptr : a.eff_scale;
             if (!wait_bar(&st.rw_bar, 0)) report_status(a.status, kStatusWaitTimeout);
             const float4* wrow = (const float4*)(dsm + G.off_rw + (size_t)cw * D * 4);
+            const float4* xf = (const float4*)(dsm + G.off_xraw);
             acc = 0.f;
             // lane l takes the float4 chunks l, l + 32, ... in order: the sequence of fused multiply-adds of
             // lane_dot_f32, both operands from shared memory
-#pragma unroll 2
+#pragma unroll 4
             for (uint32_t c = lane; c < chunks; c += 32) {
                 const float4 wv = wrow[c];
-                float xv[4];
-                if (a.act_dtype == SHRIKE_DTYPE_FP32) {
-                    const float4 v = ((const float4*)xraw)[c];
-                    xv[0] = v.x; xv[1] = v.y; xv[2] = v.z; xv[3] = v.w;
-                } else {
-                    const uint2 v = ((const uint2*)xraw)[c];
-                    if (a.act_dtype == SHRIKE_DTYPE_FP16) {
-                        xv[0] = f16_bits_to_f32(v.x & 0xffff); xv[1] = f16_bits_to_f32(v.x >> 16);
-                        xv[2] = f16_bits_to_f32(v.y & 0xffff); xv[3] = f16_bits_to_f32(v.y >> 16);
-                    } else {
-                        xv[0] = __uint_as_float(v.x << 16); xv[1] = __uint_as_float(v.x & 0xffff0000u);
-                        xv[2] = __uint_as_float(v.y << 16); xv[3] = __uint_as_float(v.y & 0xffff0000u);
-                    }
-                }
+                float4 xv = xf[c];
                 if (es) {
                     const uint2 q = __ldg((const uint2*)es + c);
-                    xv[0] = __fmul_rn(xv[0], __uint_as_float(q.x << 16));
-                    xv[1] = __fmul_rn(xv[1], __uint_as_float(q.x & 0xffff0000u));
-                    xv[2] = __fmul_rn(xv[2], __uint_as_float(q.y << 16));
-                    xv[3] = __fmul_rn(xv[3], __uint_as_float(q.y & 0xffff0000u));
+                    xv.x = __fmul_rn(xv.x, __uint_as_float(q.x << 16));
+                    xv.y = __fmul_rn(xv.y, __uint_as_float(q.x & 0xffff0000u));
+                    xv.z = __fmul_rn(xv.z, __uint_as_float(q.y << 16));
+                    xv.w = __fmul_rn(xv.w, __uint_as_float(q.y & 0xffff0000u));
                 }
-                acc = __fmaf_rn(wv.x, xv[0], acc);
-                acc = __fmaf_rn(wv.y, xv[1], acc);
-                acc = __fmaf_rn(wv.z, xv[2], acc);
-                acc = __fmaf_rn(wv.w, xv[3], acc);
+                acc = __fmaf_rn(wv.x, xv.x, acc);
+                acc = __fmaf_rn(wv.y, xv.y, acc);
+                acc = __fmaf_rn(wv.z, xv.z, acc);
+                acc = __fmaf_rn(wv.w, xv.w, acc);
             }
         } else {
             const uint32_t groups = D / 64;
             acc = affine_row_dot((const uint8_t*)a.rw + (size_t)my_row * (D * a.rbits / 8), a.rscales + (size_t)my_row * groups,
-                                 a.rbiases + (size_t)my_row * groups, a.rbits, groups, lane, xraw, a.act_dtype, a.eff_scale);
+                                 a.rbiases + (size_t)my_row * groups, a.rbits, groups, lane, a.x, a.act_dtype, a.eff_scale);
         }
         acc = butterfly_sum(acc);
         if (lane == 0)
-            st_relaxed_u64(a.logits64 + my_row, ((unsigned long long)st.epoch << 32) | (unsigned long long)__float_as_uint(acc));
-        if (cw == 0) FUSED_TS(3);   // this block's logits are published
+            st_relaxed_u64(a.logits64 + my_row, ((unsigned long long)epoch << 32) | (unsigned long long)__float_as_uint(acc));
+        FUSED_TS(3);   // this block's logits are published
     }
-    for (uint32_t blk = tid; blk < D / 8; blk += kFusedThreads)
-        xprep_block8(xraw, blk, a.act_dtype, BITS == 4, x_sm, a.status);
-    __syncthreads();
-    const uint32_t epoch = st.epoch;
-    const uint32_t parity = epoch & 1u;
-    uint16_t* acts_mine = a.acts_pub + (size_t)parity * kMaxInst * G.acts_stride;
-    for (uint32_t grp = tid; grp < GD; grp += kFusedThreads) xs_sm[grp] = group_sums<BITS, GROUP>(x_sm, grp);
-
-    // ---- gather every block's logits ----
-    if (tid < router_rows) {
-        bool ok = false;
-        for (uint32_t it = 0; it < (1u << 17); ++it) {
-            const unsigned long long v = ld_relaxed_u64(a.logits64 + tid);
-            if ((uint32_t)(v >> 32) == epoch) {
-                st.logits[tid] = __uint_as_float((uint32_t)v);
-                ok = true;
-                break;
-            }
-            if (it > 64) __nanosleep(64);
-        }
-        if (!ok) {
-            report_status(a.status, kStatusWaitTimeout);
-            st.logits[tid] = 0.f;
-        }
-    }
-    uint32_t io = 1u;
-    if (warp == kPW && a.io_status) io = *(volatile const uint32_t*)a.io_status;
     {   // the buffer the next call will use still holds the previous call's activations
         uint4* other = (uint4*)(a.acts_pub + (size_t)(parity ^ 1u) * kMaxInst * G.acts_stride);
         const uint32_t n16 = kMaxInst * G.acts_stride / 8;
         const uint4 fill = make_uint4(0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu);
         for (uint32_t i = blockIdx.x * kFusedThreads + tid; i < n16; i += gridDim.x * kFusedThreads) other[i] = fill;
     }
-    __syncthreads();
-    if (warp == 0) FUSED_TS(4);   // logits gathered
 
-    // ---- selection (every block repeats it), residency lookup, instance list ----
-    if (is_consumer) {
-        uint32_t id;
-        float w;
-        select_warps(st.logits, a, st.cand_key, st.cand_id, cw, lane, id, w);
-        if (cw == 0) {
-            const bool ready = io == 1u || io == 3u;
-            uint32_t slot = SHRIKE_SLOT_MISS;
-            if (lane < a.top_k) {
-                const uint64_t word = st.table[min(id, a.ne - 1u)];
-                slot = (uint32_t)(word & 0xffffffffu);
-                const bool hit = (uint32_t)(word >> 32) == 2u && slot != SHRIKE_SLOT_MISS;
-                if (!hit) slot = SHRIKE_SLOT_MISS;
-                if (blockIdx.x == 0) {
-                    // what the host reads back is the table's answer; what the kernel follows is range-checked
-                    a.out_ids[lane] = id;
-                    a.out_w[lane] = w;
-                    if (a.out_slots) a.out_slots[lane] = slot;
+    // ---- the selecting blocks (the last few: they have the fewest router rows) gather every block's logits,
+    // pick, look the picks up and publish the instance list; every other block reads one copy of it ----
+    if (selector) {
+        for (uint32_t e = tid; e < router_rows; e += kFusedThreads) {
+            bool ok = false;
+            for (uint32_t it = 0; it < (1u << 17); ++it) {
+                const unsigned long long v = ld_relaxed_u64(a.logits64 + e);
+                if ((uint32_t)(v >> 32) == epoch) {
+                    st.logits[e] = __uint_as_float((uint32_t)v);
+                    ok = true;
+                    break;
                 }
-                if (slot != SHRIKE_SLOT_MISS && slot >= a.pool_cells) {
-                    report_status(a.status, kStatusBadIndex);
-                    slot = SHRIKE_SLOT_MISS;
-                }
-                if (!ready) slot = SHRIKE_SLOT_MISS;
+                if (it > 64) __nanosleep(64);
             }
-            const uint32_t hits = __ballot_sync(0xffffffffu, slot != SHRIKE_SLOT_MISS);
-            if (slot != SHRIKE_SLOT_MISS) {
-                const uint32_t pos = has_shared + __popc(hits & ((1u << lane) - 1u));
-                st.route.cell[pos] = slot;
-                st.route.w[pos] = w;
+            if (!ok) {
+                report_status(a.status, kStatusWaitTimeout);
+                st.logits[e] = 0.f;
+            }
+        }
+        FUSED_TS(18);
+        __syncthreads();
+        FUSED_TS(4);   // logits gathered
+        if (!is_producer && cw < kSelWarps) {
+            uint32_t id;
+            float w;
+            FUSED_TS(12);
+            select_ranked(st.logits, a, st, cw, lane, id, w);
+            FUSED_TS(13);
+            if (cw == 0) {
+                uint32_t io = 1u;
+                if (a.io_status) io = *(volatile const uint32_t*)a.io_status;
+                const bool ready = io == 1u || io == 3u;
+                const bool first = blockIdx.x == gridDim.x - n_sel;   // the one that answers the caller
+                uint32_t slot = SHRIKE_SLOT_MISS;
+                if (!wait_bar(&st.tab_bar, 0)) report_status(a.status, kStatusWaitTimeout);
+                if (lane < a.top_k) {
+                    const uint64_t word = st.table[min(id, a.ne - 1u)];
+                    slot = (uint32_t)(word & 0xffffffffu);
+                    const bool hit = (uint32_t)(word >> 32) == 2u && slot != SHRIKE_SLOT_MISS;
+                    if (!hit) slot = SHRIKE_SLOT_MISS;
+                    if (first) {
+                        // what the host reads back is the table's answer; what the kernel follows is range-checked
+                        a.out_ids[lane] = id;
+                        a.out_w[lane] = w;
+                        if (a.out_slots) a.out_slots[lane] = slot;
+                    }
+                    if (slot != SHRIKE_SLOT_MISS && slot >= a.pool_cells) {
+                        report_status(a.status, kStatusBadIndex);
+                        slot = SHRIKE_SLOT_MISS;
+                    }
+                    if (!ready) slot = SHRIKE_SLOT_MISS;
+                }
+                const uint32_t hits = __ballot_sync(0xffffffffu, slot != SHRIKE_SLOT_MISS);
+                if (slot != SHRIKE_SLOT_MISS) {
+                    const uint32_t pos = has_shared + __popc(hits & ((1u << lane) - 1u));
+                    st.route.cell[pos] = slot;
+                    st.route.w[pos] = w;
+                }
+                if (lane == 0) {
+                    st.route.n_routed = __popc(hits);
+                    st.route.n_inst = has_shared + __popc(hits);
+                    if (has_shared) {
+                        st.route.cell[0] = 0;
+                        st.route.w[0] = a.gate_row ? sigmoid_det(st.logits[a.ne]) : 1.0f;
+                        if (a.gate_row && a.out_gate && first) a.out_gate[0] = st.route.w[0];
+                    }
+                }
+                __syncwarp();
+                // entry 0: the counts; entry 1 + i: instance i. Every 16-byte entry carries the epoch.
+                uint4* mine = route_pub + (size_t)(blockIdx.x - (gridDim.x - n_sel)) * (1u + kMaxInst);
+                if (lane == 0) st_relaxed_v4(mine, make_uint4(epoch, st.route.n_routed, st.route.n_inst, 0u));
+                else if (lane <= kMaxInst)
+                    st_relaxed_v4(mine + lane, make_uint4(epoch, st.route.cell[lane - 1], __float_as_uint(st.route.w[lane - 1]), 0u));
+            }
+        }
+    } else if (is_producer) {
+        if (lane <= kMaxInst) {
+            const uint4* src = route_pub + (size_t)(blockIdx.x % n_sel) * (1u + kMaxInst) + lane;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            bool ok = false;
+            for (uint32_t it = 0; it < (1u << 17); ++it) {
+                v = ld_relaxed_v4(src);
+                if (v.x == epoch) { ok = true; break; }
+                __nanosleep(it > 64 ? 256 : 100);
+            }
+            if (!ok) {
+                report_status(a.status, kStatusWaitTimeout);
+                v = make_uint4(epoch, 0u, has_shared, 0u);   // lane 0: no routed expert; the others are not read
             }
             if (lane == 0) {
-                st.route.n_routed = __popc(hits);
-                st.route.n_inst = has_shared + __popc(hits);
-                if (has_shared) {
-                    st.route.cell[0] = 0;
-                    st.route.w[0] = a.gate_row ? sigmoid_det(st.logits[a.ne]) : 1.0f;
-                    if (a.gate_row && a.out_gate && blockIdx.x == 0) a.out_gate[0] = st.route.w[0];
-                }
+                st.route.n_routed = min(v.y, (uint32_t)SHRIKE_MAX_TOP_K);
+                st.route.n_inst = has_shared + min(v.y, (uint32_t)SHRIKE_MAX_TOP_K);
+            } else {
+                st.route.cell[lane - 1] = v.y < a.pool_cells ? v.y : 0u;
+                st.route.w[lane - 1] = __uint_as_float(v.z);
             }
         }
     }
+    FUSED_TS(19);
     __syncthreads();
-    if (warp == 0) FUSED_TS(5);   // selection done
-    const uint32_t n_routed = st.route.n_routed, n_inst = st.route.n_inst;
+    FUSED_TS(5);   // the instance list is known
+    const uint32_t n_inst = st.route.n_inst;
+    plan.route(st.route.n_routed);
+    const uint32_t n_units = plan.n_units, packs_eff = plan.packs_eff;
 
     if (is_producer) {
-        // ================= producer =================
-        if (lane == 0) {
-            prod.n_routed = n_routed;
-            Unit u;
-#ifdef SHRIKE_TRACE
-            uint32_t k = 12;
-            if (a.trace) a.trace[(size_t)blockIdx.x * 16 + k++] = globaltimer_ns();
-            while (prod.next(u, true)) {
-                issue(u, prod_n++);
-                if (a.trace && k < 16) a.trace[(size_t)blockIdx.x * 16 + k++] = globaltimer_ns();
+        // ================= producer: one lane per unit =================
+        // first the units whose slot is fresh; then, a ring's worth at a time, those that wait for a slot
+        // (a lane never waits for a unit that a later lane of the same pass asks for)
+        // (the lanes run an issue together, copy by copy: the gate/up units first, then the down units, so
+        // that the copy engine's queue holds them in the order the consumers want them)
+        const uint32_t ring_a = min(n_units, G.n_slots);
+        if (lane >= n_pre && lane < min(plan.n1, ring_a)) issue(plan.unit(lane));
+        __syncwarp();
+        if (lane >= max(n_pre, plan.n1) && lane < ring_a) issue(plan.unit(lane));
+        __syncwarp();
+        FUSED_TS(7);   // the first ring's worth asked for
+        for (uint32_t base = G.n_slots; base < n_units; base += G.n_slots) {
+            const uint32_t i = base + lane;
+            if (lane < G.n_slots && i < n_units) {
+                const UnitRec u = plan.unit(i);
+                if (!wait_bar(&st.empty[u.slot()], u.parity() ^ 1u)) {
+                    report_status(a.status, kStatusWaitTimeout);
+                    st.failed = 1;
+                }
+                issue(u);
             }
-#else
-            while (prod.next(u, true)) issue(u, prod_n++);
-#endif
+            __syncwarp();
         }
         FUSED_TS(6);   // everything asked for
-    } else if (is_consumer) {
+        if (lane == 0) {
+            // The next kernel in the stream may begin its prologue from here on.
+            pdl_launch_dependents();
+            // every block read the epoch before it published its logits, and this block has gathered them all
+            if (blockIdx.x == 0) *(volatile uint32_t*)a.epoch = epoch + 1u;
+        }
+        if (st.failed && lane == 0) {
+            // a copy of this block may still be in flight: give it a bounded time to land before the block's
+            // shared memory goes away
+            for (int k = 0; k < 200; ++k) __nanosleep(1000);
+        }
+    } else {
         // ================= consumers =================
+        // Gate/up units: groups of four warps, a unit per group at a time, its columns split among the warps.
+        // Down tiles: all consumer warps share a tile's (expert, column chunk) items and meet once per tile.
         const uint32_t g = lane >> 2, t = lane & 3;
+        const uint32_t gi = cw / kGroupWarps, wi = cw % kGroupWarps;
         // this thread's byte offset inside its row's share of a group: rows are Q::kGroupBytes apart inside a
         // group's slab of a box ([group][row][group bytes])
         const uint32_t toff = t * (Q::kWords * 4);
-        const uint32_t ctid = tid - kPW * 32;
-        Walker wk;
-        wk.init(a);
-        wk.n_routed = n_routed;
-        Unit u;
-        uint32_t n = 0;
-        bool staged = false;
-        while (wk.next(u, true)) {
-            if (u.kind == 1 && !staged) {
-                if (cw == 0) FUSED_TS(8);   // this block's phase-1 units done
-                // ---- all instances' activations: poll until published, stage, group sums. A thread's blocks
-                // are all requested before the first is examined. ----
-                constexpr uint32_t kMaxPer = 4;
+        const uint32_t ctid = tid - 32u;
+        // the block's unit table, a unit per consumer thread (the producer works its units out itself)
+        if (ctid < n_units) st.units[ctid] = plan.unit(ctid);
+        consumers_sync();
+        uint32_t r = 0;   // units this group has taken
+        for (uint32_t n = gi; n < plan.n1; n += kGroups, ++r) {
+            const UnitRec u = st.units[n];
+            if (r == 0) FUSED_TS(14);
+            const uint32_t slot = u.slot();
+            if (!wait_bar(&st.full[slot], u.parity())) report_status(a.status, kStatusWaitTimeout);
+            if (r == 0) FUSED_TS(7);   // this group's first unit landed
+            const uint8_t* stage = ring + (size_t)slot * G.slot_bytes;
+            float tot0 = 0.f, tot1 = 0.f;
+            {
+                // rows g (gate) and g + 8 (up) of the unit: [gate|up][group][row 0..7][group bytes]
+                const uint8_t* rowA = stage + (size_t)g * Q::kGroupBytes + toff;
+                const uint8_t* rowB = rowA + 8 * (size_t)rb1;
+                const uint32_t slab = 8 * Q::kGroupBytes;
+                // scales and biases: [gate|up][scale|bias][row 0..7][group]
+                const uint8_t* s0p = stage + G.p1_meta_off + (size_t)g * GD * 2;
+                const uint8_t* b0p = s0p + 16 * GD;
+                const uint8_t* s1p = s0p + 32 * GD;
+                const uint8_t* b1p = s0p + 48 * GD;
+                const uint32_t cg = G.cg_p1, chunks = GD / cg;
+                for (uint32_t c = wi; c < chunks; c += kGroupWarps) {
+                    const float2 o = chunk_rows_cg<BITS, GROUP, META>(cg, rowA, rowB, slab, s0p, b0p, s1p, b1p, x_sm, xs_sm, c, t);
+                    tot0 += o.x;
+                    tot1 += o.y;
+                }
+                if (a.expert_bias && wi == 0) {
+                    const uint16_t* ab = (const uint16_t*)(stage + G.p1_ab_off);
+                    tot0 += bf16_bits_to_f32(ab[g]);
+                    tot1 += bf16_bits_to_f32(ab[8 + g]);
+                }
+            }
+            // the slot's bytes are consumed: hand it back; the group's partial sums meet in shared memory
+            __syncwarp();
+            if (r == 0) FUSED_TS(15);
+            if (lane == 0) bar_arrive(&st.empty[slot]);
+            float* red = &st.red[gi][r & 1u][0][0];
+            if (t == 0) {
+                red[wi * 16 + g] = tot0;
+                red[wi * 16 + g + 8] = tot1;
+            }
+            group_sync(gi);
+            if (wi != (r & 3u)) continue;
+            // ---- this warp finishes the unit (the four warps take turns) while the others go on ----
+            float v = 0.f;
+            if (lane < 16) {
+#pragma unroll
+                for (uint32_t w = 0; w < kGroupWarps; ++w) v += red[w * 16 + lane];
+            }
+            // rows 0..7 are gate rows; the up row of the same output sits 8 rows further
+            const float up = __shfl_down_sync(0xffffffffu, v, 8);
+            uint16_t* stg = st.act_stage[gi];
+            if (lane < 8) {
+                const float act = glu_call(v, up, a.activation);
+                stg[perm_index(lane, BITS == 4)] = act_to_half_bits(act, a.status);
+            }
+            __syncwarp();
+            if (lane == 0) {
+                const uint4 pk = *(const uint4*)stg;
+                st_relaxed_v4(acts_mine + (size_t)u.inst() * G.acts_stride + u.r0, pk);
+            }
+        }
+        FUSED_TS(8);   // this warp's gate/up units done
+        if (plan.n_tiles > 0) {
+            // ---- all instances' activations: poll until published, stage, group sums. A thread's blocks are
+            // all requested before the first is examined. ----
+            {
+                constexpr uint32_t kMaxPer = 2;
                 const uint32_t bps = G.acts_stride / 8;          // 16-byte blocks per instance (padded)
                 const uint32_t total = n_inst * bps;
                 for (uint32_t i0 = ctid; i0 < total; i0 += kCW * 32 * kMaxPer) {
@@ -791,7 +1006,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) decode_layer_kernel(const __
                         bool ok = !has_sentinel(v[k]);
 #pragma unroll 1
                         for (uint32_t it = 0; !ok && it < (1u << 17); ++it) {
-                            if (it > 32) __nanosleep(64);
+                            __nanosleep(it > 32 ? 256 : 100);   // 148 blocks poll the same few lines
                             v[k] = ld_relaxed_v4(acts_mine + (size_t)i * 8);
                             ok = !has_sentinel(v[k]);
                         }
@@ -802,50 +1017,35 @@ __global__ void __launch_bounds__(kFusedThreads, 1) decode_layer_kernel(const __
                         *(uint4*)(acts_sm + (size_t)i * 8) = v[k];
                     }
                 }
-                consumer_sync();
+                consumers_sync();
                 for (uint32_t i = ctid; i < n_inst * gmax2; i += kCW * 32) {
                     const uint32_t in = i / gmax2, grp = i - in * gmax2;
                     const uint32_t F = (has_shared && in == 0) ? a.f_shared : a.f;
                     if (grp < F / GROUP) asum_sm[i] = group_sums<BITS, GROUP>(acts_sm + (size_t)in * G.acts_stride, grp);
                 }
-                consumer_sync();
-                if (cw == 0) FUSED_TS(9);   // activations of every instance staged
-                staged = true;
+                consumers_sync();
             }
-            const uint32_t slot = n % G.n_slots, round = n / G.n_slots;
-            if (!wait_bar(&st.full[slot], round & 1)) report_status(a.status, kStatusWaitTimeout);
-            if (cw == 0 && n == 0) FUSED_TS(7);   // first unit landed
-            const uint8_t* stage = ring + (size_t)slot * G.slot_bytes;
-            float tot0 = 0.f, tot1 = 0.f;
-            if (u.kind == 0) {
-                // rows g (gate) and g + 8 (up) of the unit: [gate|up][group][row 0..7][group bytes]
-                const uint8_t* rowA = stage + (size_t)g * Q::kGroupBytes + toff;
-                const uint8_t* rowB = rowA + 8 * (size_t)rb1;
-                const uint32_t slab = 8 * Q::kGroupBytes;
-                // scales and biases: [gate|up][scale|bias][row 0..7][group]
-                const uint8_t* s0p = stage + G.p1_meta_off + (size_t)g * GD * 2;
-                const uint8_t* b0p = s0p + 16 * GD;
-                const uint8_t* s1p = s0p + 32 * GD;
-                const uint8_t* b1p = s0p + 48 * GD;
-                const uint32_t cg = G.cg_p1, chunks = GD / cg;
-                for (uint32_t c = cw; c < chunks; c += kCW) {
-                    const float2 o = chunk_rows_cg<BITS, GROUP, META>(cg, rowA, rowB, slab, s0p, b0p, s1p, b1p, x_sm, xs_sm, c, t);
-                    tot0 += o.x;
-                    tot1 += o.y;
-                }
-                if (a.expert_bias && cw == 0) {
-                    const uint16_t* ab = (const uint16_t*)(stage + G.p1_ab_off);
-                    tot0 += bf16_bits_to_f32(ab[g]);
-                    tot1 += bf16_bits_to_f32(ab[8 + g]);
-                }
-            } else {
-                const uint32_t sh = u.sh;
-                const uint32_t F = sh ? a.f_shared : a.f, G2 = F / GROUP;
-                const uint32_t cg = G.cg_p2[sh], cpe = G2 / cg;
-                for (uint32_t cc = cw; cc < u.count * cpe; cc += kCW) {
-                    const uint32_t q = cc / cpe, c = cc - q * cpe;
-                    const uint32_t in = u.inst + q;
-                    const uint8_t* eb = stage + (size_t)q * G.p2_expert_bytes[sh];
+            FUSED_TS(9);   // activations of every instance staged
+            const uint32_t cpe_s = has_shared ? (a.f_shared / GROUP) / G.cg_p2[1] : 0u;   // chunks of the shared expert
+            const uint32_t cpe_r = (a.f / GROUP) / G.cg_p2[0];                            // chunks of a routed expert
+            const uint32_t items = cpe_s + plan.n_routed * cpe_r;
+            for (uint32_t m = 0; m < plan.n_tiles; ++m) {
+                const uint32_t u0 = plan.n1 + m * packs_eff;   // the tile's first unit
+                const uint32_t row0 = (plan.n_blk - 1u - plan.blk + m * plan.n_blk) * 16u;
+                float tot0 = 0.f, tot1 = 0.f;
+                for (uint32_t it = cw; it < items; it += kCW) {
+                    uint32_t sh, in, c, p, q;
+                    if (it < cpe_s) {
+                        sh = 1u; in = 0u; c = it; p = 0u; q = 0u;
+                    } else {
+                        const uint32_t k = it - cpe_s, j = k / cpe_r, pj = j / plan.epp;
+                        sh = 0u; in = has_shared + j; c = k - j * cpe_r; p = has_shared + pj; q = j - pj * plan.epp;
+                    }
+                    const UnitRec u = st.units[u0 + p];
+                    if (!wait_bar(&st.full[u.slot()], u.parity())) report_status(a.status, kStatusWaitTimeout);
+                    if (it == cw && m == 0) FUSED_TS(22);
+                    const uint32_t F = sh ? a.f_shared : a.f, G2 = F / GROUP;
+                    const uint8_t* eb = ring + (size_t)u.slot() * G.slot_bytes + (size_t)q * G.p2_expert_bytes[sh];
                     // [group][row 0..15][group bytes]; scales and biases [scale|bias][row 0..15][group]
                     const uint8_t* rowA = eb + (size_t)g * Q::kGroupBytes + toff;
                     const uint8_t* rowB = rowA + 8 * Q::kGroupBytes;
@@ -856,7 +1056,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) decode_layer_kernel(const __
                     const uint8_t* b1p = s1p + 32 * G2;
                     const uint16_t* bsm = acts_sm + (size_t)in * G.acts_stride;
                     const float2* xs = asum_sm + (size_t)in * gmax2;
-                    const float2 o = chunk_rows_cg<BITS, GROUP, META>(cg, rowA, rowB, slab, s0p, b0p, s1p, b1p, bsm, xs, c, t);
+                    const float2 o = chunk_rows_cg<BITS, GROUP, META>(G.cg_p2[sh], rowA, rowB, slab, s0p, b0p, s1p, b1p, bsm, xs, c, t);
                     float o0 = o.x, o1 = o.y;
                     if (a.expert_bias && c == 0) {
                         const uint16_t* ab = (const uint16_t*)(eb + G.p2_ab_off[sh]);
@@ -866,81 +1066,36 @@ __global__ void __launch_bounds__(kFusedThreads, 1) decode_layer_kernel(const __
                     const float w = st.route.w[in];
                     tot0 = fmaf(w, o0, tot0);
                     tot1 = fmaf(w, o1, tot1);
+                    if (it == cw && m == 0) FUSED_TS(17);
                 }
-            }
-            // the slot's bytes are consumed; hand it back, then leave the partial sums for the epilogue warp
-            __syncwarp();
-            if (lane == 0) bar_arrive(&st.empty[slot]);
-            const uint32_t rbuf = n & 1u, rround = n >> 1;
-            if (rround > 0 && !wait_bar(&st.red_empty[rbuf], (rround - 1) & 1)) report_status(a.status, kStatusWaitTimeout);
-            if (t == 0) {
-                st.red[rbuf][cw][g] = tot0;
-                st.red[rbuf][cw][g + 8] = tot1;
-            }
-            __syncwarp();
-            if (lane == 0) bar_arrive(&st.red_full[rbuf]);
-            ++n;
-        }
-        if (cw == 0) FUSED_TS(10);   // consumers done
-    } else {
-        // ================= epilogue warp =================
-        // The next kernel in the stream may begin its prologue (its own weight prefetch) from here on. One lane
-        // says so for the block: the instruction was measured to hold a warp for about 3 us, and this warp has
-        // nothing to do until the first unit has been reduced.
-        if (lane == 0) pdl_launch_dependents();
-        Walker wk;
-        wk.init(a);
-        wk.n_routed = n_routed;
-        Unit u;
-        uint32_t n = 0;
-        float ysum = 0.f;
-        while (wk.next(u, true)) {
-            const uint32_t rbuf = n & 1u, rround = n >> 1;
-            if (!wait_bar(&st.red_full[rbuf], rround & 1)) report_status(a.status, kStatusWaitTimeout);
-            float v = 0.f;
-            if (lane < 16) {
-#pragma unroll
-                for (uint32_t w = 0; w < kCW; ++w) v += st.red[rbuf][w][lane];
-            }
-            __syncwarp();
-            if (lane == 0) bar_arrive(&st.red_empty[rbuf]);
-            if (u.kind == 0) {
-                // rows 0..7 are gate rows; the up row of the same output sits 8 rows further
-                const float up = __shfl_down_sync(0xffffffffu, v, 8);
-                if (lane < 8) {
-                    const float act = glu_call(v, up, a.activation);
-                    st.act_stage[perm_index(lane, BITS == 4)] = act_to_half_bits(act, a.status);
+                if (m == 0) FUSED_TS(20);
+                float* red = &st.red2[m & 1u][cw][0];
+                if (t == 0) {
+                    red[g] = tot0;
+                    red[g + 8] = tot1;
                 }
-                __syncwarp();
-                if (lane == 0) {
-                    const uint4 pk = *(const uint4*)st.act_stage;
-                    st_relaxed_v4(acts_mine + (size_t)u.inst * G.acts_stride + u.r0, pk);
-                }
-                __syncwarp();
-            } else {
-                ysum += v;
-                if (u.last) {
+                // one warp per tile adds the warps' sums up (in warp order) and writes the rows; it asks for the
+                // residual's values before the warps meet
+                const bool fin = cw == m % kCW;
+                float hid = 0.f;
+                if (fin && lane < 16 && a.hidden) hid = load_act(a.hidden, (size_t)row0 + lane, a.act_dtype);
+                consumers_sync();
+                if (m == 0) FUSED_TS(21);
+                if (fin) {
                     if (lane < 16) {
-                        const size_t o = (size_t)u.r0 + lane;
+                        float ysum = 0.f;
+#pragma unroll
+                        for (uint32_t w = 0; w < kCW; ++w) ysum += st.red2[m & 1u][w][lane];
+                        const size_t o = (size_t)row0 + lane;
                         store_act(a.y, o, a.y_dtype, ysum);
-                        if (a.hidden) {
-                            const float h = load_act(a.hidden, o, a.act_dtype) + round_act(a.y_dtype, ysum);
-                            store_act(a.hidden, o, a.act_dtype, h);
-                        }
+                        if (a.hidden) store_act(a.hidden, o, a.act_dtype, hid + round_act(a.y_dtype, ysum));
                     }
-                    ysum = 0.f;
+                    // every warp is past its reads of the tile's slots: they go back to the producer
+                    if (lane < packs_eff) bar_arrive_n(&st.empty[st.units[u0 + lane].slot()], kGroupWarps);
                 }
             }
-            ++n;
         }
-        // every block read the epoch before it published its logits, and this block has gathered them all
-        if (blockIdx.x == 0 && lane == 0) *(volatile uint32_t*)a.epoch = epoch + 1u;
-        FUSED_TS(11);   // block done
-    }
-    if (st.failed && warp == 0 && lane == 0) {
-        // a copy of this block may still be in flight: give it a bounded time to land before the block's
-        // shared memory goes away
-        for (int k = 0; k < 200; ++k) __nanosleep(1000);
+        FUSED_TS(10);   // this warp done
     }
 }
 
@@ -995,7 +1150,7 @@ bool fused_geometry(const shrike_moe_config& c, int sm_count, int max_smem_optin
     g.acts_stride = std::max(c.f, c.has_shared ? c.shared_f : 0u);
     g.off_x = 0;
     g.off_xraw = align_up(c.d * 2, 16);
-    g.off_rw = g.off_xraw + align_up(c.d * (c.act_dtype == SHRIKE_DTYPE_FP32 ? 4u : 2u), 16);
+    g.off_rw = g.off_xraw + c.d * 4;   // the row in fp32
     g.off_xs = g.off_rw + kMaxRouterRowsPerBlock * c.d * 4;   // this block's fp32 router rows
     g.off_acts = g.off_xs + align_up(G1 * 8, 16);
     g.off_asum = g.off_acts + n_inst * g.acts_stride * 2;
@@ -1006,7 +1161,14 @@ bool fused_geometry(const shrike_moe_config& c, int sm_count, int max_smem_optin
     g.smem_bytes = g.off_ring + g.n_slots * g.slot_bytes;
     const uint32_t rows = c.num_experts + (c.shared_gated ? 1u : 0u);
     g.router_rows_per_block = (rows + (uint32_t)sm_count - 1) / (uint32_t)sm_count;
-    return g.router_rows_per_block <= kMaxRouterRowsPerBlock && rows <= kFusedThreads;
+    if (g.router_rows_per_block > kMaxRouterRowsPerBlock) return false;
+    // the block's unit table and its per-tile sums, at the most work a block can get
+    const uint32_t n_blk = (uint32_t)sm_count;
+    const uint32_t units1 = ((c.has_shared ? c.shared_f / 8 : 0u) + c.top_k * (c.f / 8) + n_blk - 1) / n_blk;
+    const uint32_t tiles = (c.d / 16 + n_blk - 1) / n_blk;
+    const uint32_t packs = (c.has_shared ? 1u : 0u) + (c.top_k + g.experts_per_pack - 1) / g.experts_per_pack;
+    // (a tile's packs are held until the tile is done: they must fit the ring together)
+    return std::max(packs, 1u) <= g.n_slots && units1 + tiles * std::max(packs, 1u) <= kMaxUnits;
 }
 
 // ---- tensor maps of an expert-block layout -------------------------------------------------------------
@@ -1110,7 +1272,10 @@ static const FusedMaps* fused_maps_for(const shrike_moe* m, const ExpertArgs& ea
 size_t fused_map_cache_bytes() { return sizeof(FusedMapCache); }
 
 size_t fused_geom_bytes() { return sizeof(FusedGeom); }
-size_t fused_logits_bytes(const shrike_moe_config& c) { return (size_t)(c.num_experts + 1) * 8; }
+// {epoch, logit} words of the experts and the gate row, then the selecting blocks' copies of the instance list
+size_t fused_logits_bytes(const shrike_moe_config& c) {
+    return (size_t)((c.num_experts + 2u) & ~1u) * 8 + (size_t)kSelectors * (1 + kMaxInst) * 16;
+}
 size_t fused_acts_bytes(const shrike_moe_config& c) {
     return (size_t)2 * kMaxInst * std::max(c.f, c.has_shared ? c.shared_f : 0u) * 2;
 }
@@ -1127,8 +1292,13 @@ static cudaError_t launch_fused_t(const shrike_moe* m, cudaStream_t st, const Fu
     cfg.stream = st;
     cudaLaunchAttribute attr[2];
     unsigned n = 0;
-    if (!getenv("SHRIKE_NO_COOP")) {
-        attr[n].id = cudaLaunchAttributeCooperative;   // every block resident: the blocks wait on each other's results
+    // The blocks wait on each other's results, so all of them must be resident. The grid is one block per SM
+    // and a block needs most of an SM, so they are, as soon as the previous kernel of the stream has left --
+    // unless another stream's kernel holds SMs meanwhile: then the (bounded) waits give up and the call reports
+    // a timeout. A cooperative launch rules that out, but it also keeps every block from starting until the
+    // previous kernel has ended, prologue and launch latency exposed: it is the opt-in.
+    if (m->cooperative || m->no_pdl) {
+        attr[n].id = cudaLaunchAttributeCooperative;
         attr[n].val.cooperative = 1;
         ++n;
     }

@@ -118,6 +118,9 @@ struct shrike_moe {
     uint32_t residency_layers = 0;
     int sm_count = 148;
     bool no_pdl = false;          // SHRIKE_NO_PDL was set when the handle was created (diagnostics)
+    bool cooperative = false;     // SHRIKE_COOPERATIVE was set when the handle was created: the one-launch layer asks for a
+                                  // cooperative launch (all blocks resident before any starts) and gives up the overlap
+                                  // of its prologue with the previous kernel's tail
     bool force_warp_mma = false;  // SHRIKE_PREFILL_PATH=mma was set when the handle was created (test switch)
 #ifdef SHRIKE_TRACE
     uint64_t* trace = nullptr;
