@@ -561,8 +561,9 @@ def ep_block(args, rank: int, world: int, local_rank: int) -> dict:
         layer.forward(ops, x, y)
         torch.cuda.synchronize()
         got = y.float().cpu().numpy()[sample]
-        ids = layer.ids.cpu().numpy().astype(np.uint32)[sample]
-        wts = layer.w.cpu().numpy()[sample]
+        ids_d, w_d = layer.routing(ops, x)
+        ids = ids_d.cpu().numpy().astype(np.uint32)[sample]
+        wts = w_d.cpu().numpy()[sample]
         ecfg = O.expert_cfg(cfg.d, cfg.f, bits=8)
         lcfg = O.layer_cfg(ecfg, O.expert_cfg(cfg.d, cfg.shared_f, bits=8), False)
         blocks = {int(e): fx.synth_block(cfg, SEED, 0, int(e)) for e in np.unique(ids)}
@@ -581,7 +582,10 @@ def ep_block(args, rank: int, world: int, local_rank: int) -> dict:
             "world": world, "rows_per_rank": rows, "rows_per_s": round(rows_s_n), "ms_per_step": round(ms_n, 4),
             "rows_per_s_one_gpu": round(rows_s_1), "ms_per_step_one_gpu": round(ms1, 4),
             "efficiency": round(rows_s_n / (world * rows_s_1), 4),
-            "ms_dispatch": round(stats["ms_dispatch"], 4), "ms_combine": round(stats["ms_combine"], 4),
+            # the exchange is fused into the layer (rows stored into the peers' buffers by the dispatch kernels, partial
+            # rows returned by the combine of the local call): what it and the imbalance between ranks cost is the
+            # step's time over the same rank's one-GPU step on the same rows
+            "ms_exchange_and_imbalance": round(ms_n - ms1, 4),
             "bytes_sent_per_rank": stats["bytes_sent"], "rows_received_max_over_mean": round(
                 float(recv_max.item()) / (float(recv_sum.item()) / world), 4),
             "exchange": stats["exchange"], "parity_rel_l2": parity}

@@ -37,7 +37,10 @@ class ExpertParallelLayer:
     """One MoE layer under expert parallelism on this rank's GPU."""
 
     def __init__(self, config: MoEConfig, rank: int, world: int, device: int, rows_per_rank: int,
-                 group: Optional[dist.ProcessGroup] = None, exchange: str = "peer"):
+                 group: Optional[dist.ProcessGroup] = None, exchange: str = "peer", connect: bool = True):
+        """connect=False (peer exchange, world > 1): the ranks' buffers are not exchanged through the process
+        group; the caller hands the peers' base pointers to `connect_pointers` (one process driving several
+        GPUs, or a test that stands in for a peer)."""
         if exchange not in ("peer", "nccl"):
             raise ValueError("exchange must be 'peer' or 'nccl'")
         self.cfg = config
@@ -67,7 +70,7 @@ class ExpertParallelLayer:
             h = C.c_void_p()
             self.home._check(self._lib.shrike_ep_create(self.home._h, self.routed._h, rank, world, rows_per_rank, C.byref(h)))
             self._ep = h
-            if world > 1:
+            if world > 1 and connect:
                 token = C.create_string_buffer(capi.EP_HANDLE_BYTES)
                 self.home._check(self._lib.shrike_ep_export(self._ep, token))
                 tokens = [None] * world
@@ -99,6 +102,19 @@ class ExpertParallelLayer:
 
     def set_shared(self, shared: capi.SharedExpert) -> None:
         self.shared = shared
+
+    def buffer(self) -> tuple[int, int]:
+        """(base address, bytes) of this rank's exchange buffer."""
+        base, nbytes = C.c_void_p(), C.c_uint64()
+        self.home._check(self._lib.shrike_ep_buffer(self._ep, C.byref(base), C.byref(nbytes)))
+        return base.value, nbytes.value
+
+    def connect_pointers(self, bases) -> None:
+        """bases[g]: base address of rank g's exchange buffer as this process can address it (own entry ignored)."""
+        ptrs = (C.c_void_p * capi.EP_MAX_WORLD)()
+        for g, b in enumerate(bases):
+            ptrs[g] = b
+        self.home._check(self._lib.shrike_ep_connect_pointers(self._ep, ptrs))
 
     def set_wait_polls(self, polls: int) -> None:
         """Limit of the bounded device-side waits for the peers' arrival words (0 = the default, about a second)."""

@@ -419,15 +419,20 @@ def test_device_fill_is_the_host_function(cuda_device):
                                 dict(has_shared=False, shared_gated=False, expert_bias=True,
                                      activation=capi.ACT_CLAMPED_SWIGLU, group_size=32, top_k=2)])
 def test_fused_decode_layer_equals_the_separate_calls(cuda_device, T, kw):
-    """One-call decode layer (fused route kernel + dependent launches) against the five separate calls:
-    ids, weights and outputs bit for bit; and against the oracle."""
+    """One-call decode layer against the five separate calls: ids and weights bit for bit; outputs bit for bit
+    where the call runs the same kernels (more than one row), and to 1e-3 at one row, where the whole layer is
+    one launch that adds the column chunks up in another order; and against the oracle."""
     layer = Layer(small_config(d=256, **kw))
     x = inputs(T, 256, seed=T + 40)
     h0 = inputs(T, 256, seed=T + 41)
     a = layer.forward(x, hidden=h0)
     b = layer.forward(x, hidden=h0, fused=True)
     assert (a[1] == b[1]).all() and (a[2] == b[2]).all()
-    assert (a[0] == b[0]).all() and (a[3] == b[3]).all()
+    if T == 1:
+        assert np.linalg.norm(a[0] - b[0]) <= 1e-3 * np.linalg.norm(a[0])
+        assert np.linalg.norm(a[3] - b[3]) <= 1e-3 * np.linalg.norm(a[3])
+    else:
+        assert (a[0] == b[0]).all() and (a[3] == b[3]).all()
     check_layer(layer, x, fused=True)
     # repeated calls reuse the workspace and the completion counter
     c = layer.forward(x, hidden=h0, fused=True)
