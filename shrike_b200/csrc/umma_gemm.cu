@@ -45,10 +45,11 @@
 namespace shrike {
 
 constexpr uint32_t kUmmaMaxN = 256;
+constexpr int kActBoxes = 5;
 constexpr uint32_t kConverters = 512;                  // two threads per weight row
 constexpr uint32_t kConvWarps = kConverters / 32;
 constexpr uint32_t kUmmaThreads = kConverters + 96;    // + MMA warp, activation-copy warp, weight-copy warp
-constexpr uint32_t kAStages = 2, kBStages = 3, kPkSlots = 3;
+constexpr uint32_t kAStages = 2, kMaxAStages = 4, kBStages = 3, kPkSlots = 3;   // kAStages: at the widest activation tile
 constexpr uint32_t kTileBytes = 128 * 128;             // 128 rows x 64 fp16, one swizzle-128B K block
 constexpr uint32_t kAStageBytes = 2 * kTileBytes;      // both weight tiles
 constexpr uint32_t kBTileBytes = kUmmaMaxN * 128;      // 256 rows x 64 fp16
@@ -58,7 +59,7 @@ constexpr uint32_t kOffA = kBStages * kBTileBytes;
 constexpr uint32_t kOffPk = kOffA + kAStages * kAStageBytes;
 constexpr uint32_t kOffSc = kOffPk + kPkSlots * kPkSlotBytes;
 constexpr uint32_t kOffBar = kOffSc + 2 * kScHalfBytes;
-constexpr uint32_t kNumBars = 2 * kAStages + 2 * kBStages + 2 * kPkSlots + 3;
+constexpr uint32_t kNumBars = 2 * kMaxAStages + 2 * kBStages + 2 * kPkSlots + 3;
 constexpr uint32_t kUmmaSmemBytes = kOffBar + kNumBars * 8 + 2 * kUmmaMaxN * 4 + 16 + 1024 /*alignment slack*/;
 
 struct WeightMaps {       // TMA descriptors of the two 128-row tiles of a block
@@ -69,7 +70,7 @@ struct WeightMaps {       // TMA descriptors of the two 128-row tiles of a block
 struct UmmaMaps {
     WeightMaps routed[SHRIKE_MAX_POOL_CHUNKS];
     WeightMaps shared;
-    CUtensorMap act_routed[4], act_shared[4];   // boxes of 32, 64, 128 and 256 activation rows
+    CUtensorMap act_routed[kActBoxes], act_shared[kActBoxes];   // boxes of 16, 32, 64, 128 and 256 activation rows
 };
 
 // ---- tcgen05 wrappers -------------------------------------------------------
@@ -129,11 +130,18 @@ __device__ __forceinline__ uint32_t umma_idesc(uint32_t n) {
 template <int BITS>
 __device__ __forceinline__ void dequant_word(uint32_t w, uint32_t s2, uint32_t z2, uint32_t* out) {
     if constexpr (BITS == 4) {
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const uint32_t h = hsub2_u32(lop3_and_or(w >> (4 * j), 0x000F000Fu, 0x64006400u), 0x64086408u);
-            asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(out[j]) : "r"(h), "r"(s2), "r"(z2));
-        }
+        // nibbles j and j + 4 of the word make pair j. A nibble in bits 0..3 of a half is read as the fp16
+        // value 1024 + q, one in bits 4..7 as 64 + q (64's unit in the last place sits at bit 4): one shift
+        // per word instead of three.
+        const uint32_t v = w >> 8;
+        const uint32_t h0 = hsub2_u32(lop3_and_or(w, 0x000F000Fu, 0x64006400u), 0x64086408u);   // (1024 + q) - 1032
+        const uint32_t h1 = hsub2_u32(lop3_and_or(w, 0x00F000F0u, 0x54005400u), 0x54805480u);   // (64 + q) - 72
+        const uint32_t h2 = hsub2_u32(lop3_and_or(v, 0x000F000Fu, 0x64006400u), 0x64086408u);
+        const uint32_t h3 = hsub2_u32(lop3_and_or(v, 0x00F000F0u, 0x54005400u), 0x54805480u);
+        asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(out[0]) : "r"(h0), "r"(s2), "r"(z2));
+        asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(out[1]) : "r"(h1), "r"(s2), "r"(z2));
+        asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(out[2]) : "r"(h2), "r"(s2), "r"(z2));
+        asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(out[3]) : "r"(h3), "r"(s2), "r"(z2));
     } else {
         const uint32_t lo = hsub2_u32(prmt(w, 0x64646464u, 0x5140u), 0x64806480u);
         const uint32_t hi = hsub2_u32(prmt(w, 0x64646464u, 0x5342u), 0x64806480u);
@@ -244,13 +252,29 @@ umma_expert_kernel(const ExpertArgs a, const ChunkInstance* __restrict__ inst, c
     const uint32_t N = (in.count + 15u) & ~15u;           // MMA N: rows padded to 16
     uint32_t ncols = 32;                                   // TMEM columns of one accumulator
     while (ncols < N) ncols <<= 1;
+    // The activation tiles and the converted weight tiles share one region of shared memory: an instance with
+    // few rows needs narrow activation tiles and gets more weight stages instead. What paces such a block is the
+    // round trip converters -> tensor core -> converters (barrier, issue, commit, barrier: about half a
+    // microsecond against a few hundred nanoseconds of arithmetic), so it wants more tiles in flight.
+    // the instance's rows as one or two boxes of 16 << i rows: the largest that fits, then the smallest that
+    // holds the rest
+    uint32_t n1 = 16, b1 = 0;
+    while ((n1 << 1) <= N && b1 + 1 < (uint32_t)kActBoxes) { n1 <<= 1; ++b1; }
+    uint32_t n2 = 0, b2 = 0;
+    if (N > n1) {
+        n2 = 16;
+        while (n2 < N - n1) { n2 <<= 1; ++b2; }
+    }
+    const uint32_t b_stage = (((n1 + n2) * 128u + 2047u) / 2048u) * 2048u;   // bytes of one activation stage
+    const uint32_t off_a = kBStages * b_stage;
+    const uint32_t a_stages = min(kMaxAStages, (kOffPk - off_a) / kAStageBytes);
 
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem = smem_raw + (smem_base - smem_u32(smem_raw));
     uint64_t* bars = (uint64_t*)(smem + kOffBar);
     uint64_t* a_full = bars;                       // converters -> MMA
-    uint64_t* a_empty = a_full + kAStages;         // MMA -> converters
-    uint64_t* b_full = a_empty + kAStages;         // activation copy -> MMA
+    uint64_t* a_empty = a_full + kMaxAStages;      // MMA -> converters
+    uint64_t* b_full = a_empty + kMaxAStages;      // activation copy -> MMA
     uint64_t* b_empty = b_full + kBStages;         // MMA -> activation copy
     uint64_t* pk_full = b_empty + kBStages;        // weight copy -> converters
     uint64_t* pk_empty = pk_full + kPkSlots;       // converters -> weight copy
@@ -263,7 +287,7 @@ umma_expert_kernel(const ExpertArgs a, const ChunkInstance* __restrict__ inst, c
     __shared__ uint32_t s_failed;
 
     if (tid == 0) {
-        for (uint32_t s = 0; s < kAStages; ++s) { mbar_init(&a_full[s], kConvWarps); mbar_init(&a_empty[s], 1); }
+        for (uint32_t s = 0; s < kMaxAStages; ++s) { mbar_init(&a_full[s], kConvWarps); mbar_init(&a_empty[s], 1); }
         for (uint32_t s = 0; s < kBStages; ++s) { mbar_init(&b_full[s], 1); mbar_init(&b_empty[s], 1); }
         for (uint32_t s = 0; s < kPkSlots; ++s) { mbar_init(&pk_full[s], 1); mbar_init(&pk_empty[s], kConvWarps); }
         mbar_init(sc_full, 1);
@@ -272,18 +296,15 @@ umma_expert_kernel(const ExpertArgs a, const ChunkInstance* __restrict__ inst, c
         fence_mbar_init();
         s_failed = 0;
     }
-    if (PHASE == 1) {
-        for (uint32_t n = tid; n < kUmmaMaxN; n += kUmmaThreads) {
-            const uint32_t src = n < in.count ? n : 0;
-            if (shared) {
-                rowid[n] = in.first + src;
-                roww[n] = a.shared_gate ? a.shared_gate[in.first + src] : 1.0f;
-            } else {
-                const uint32_t pair = a.sorted[in.first + src];
-                rowid[n] = pair / a.top_k;
-                roww[n] = a.route_w[pair];
-            }
-        }
+    // the descriptors this block's copy threads will use: fetched while the barriers are set up
+    if (warp == kConvWarps + 1 && lane < 2) {
+        const CUtensorMap* mb = shared ? maps.act_shared : maps.act_routed;
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&mb[lane == 0 ? b1 : b2]) : "memory");
+    }
+    if (warp == kConvWarps + 2 && lane < 6) {
+        const WeightMaps* wm = shared ? &maps.shared : &maps.routed[in.slot / a.pool.cells_per_chunk];
+        const CUtensorMap* mp = lane < 2 ? &wm->w[lane] : lane < 4 ? &wm->s[lane - 2] : &wm->b[lane - 4];
+        asm volatile("prefetch.tensormap [%0];" ::"l"(mp) : "memory");
     }
     if (warp == kConvWarps) tmem_alloc(smem_u32(tmem_slot), 2 * ncols);
     tc_fence_before();
@@ -301,6 +322,20 @@ umma_expert_kernel(const ExpertArgs a, const ChunkInstance* __restrict__ inst, c
 
     if (warp < kConvWarps) {
         // ---------------- converters ----------------
+        // the tokens and route weights of the columns: the epilogue reads them, long after these loads
+        if (PHASE == 1) {
+            for (uint32_t n = tid; n < kUmmaMaxN; n += kConverters) {
+                const uint32_t src = n < in.count ? n : 0;
+                if (shared) {
+                    rowid[n] = in.first + src;
+                    roww[n] = a.shared_gate ? a.shared_gate[in.first + src] : 1.0f;
+                } else {
+                    const uint32_t pair = a.sorted[in.first + src];
+                    rowid[n] = pair / a.top_k;
+                    roww[n] = a.route_w[pair];
+                }
+            }
+        }
         // Two threads per weight row: thread `half` converts 32 of the K block's 64 weights.
         const uint32_t tile = tid >> 8, r = (tid >> 1) & 127, half = tid & 1;
         constexpr uint32_t kWordsPerThread = kWordsPerBlock / 2;   // 4 (int4) or 8 (int8)
@@ -331,79 +366,105 @@ umma_expert_kernel(const ExpertArgs a, const ChunkInstance* __restrict__ inst, c
             }
         };
         if (!sc_tma) fetch_scales(0);
-        for (uint32_t kb = 0; kb < KB; ++kb) {
-            if (*(volatile uint32_t*)&s_failed) break;
-            if (kb % kKbPerSc == 0) {
-                if (sc_tma) {
-                    if (!pipe_wait(sc_full, (kb / kKbPerSc) & 1)) give_up();
-                    const uint4 sv = *(const uint4*)(smem + kOffSc + tile * (kScHalfBytes / 2) + r * 16);
-                    const uint4 bv = *(const uint4*)(smem + kOffSc + kScHalfBytes + tile * (kScHalfBytes / 2) + r * 16);
-                    sreg[0] = sv.x; sreg[1] = sv.y; sreg[2] = sv.z; sreg[3] = sv.w;
-                    breg[0] = bv.x; breg[1] = bv.y; breg[2] = bv.z; breg[3] = bv.w;
-                } else {
-                    // this block's 8 groups were fetched one block ago; fetch the next block's now
+        // What does not change along K: this thread's chunk positions in a packed slot and in the converted
+        // tile (both swizzled by the row), and the tile rows of the two stages.
+        uint32_t pk_off[kKbPerPk * (kWordsPerThread / 4)];
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) { sreg[i] = snext[i]; breg[i] = bnext[i]; }
-                    fetch_scales(kb / kKbPerSc + 1);
-                }
-            }
-            const uint32_t u = kb / kKbPerPk, slot = u % kPkSlots;
-            if (kb % kKbPerPk == 0 && !pipe_wait(&pk_full[slot], (u / kPkSlots) & 1)) give_up();
-            uint32_t pk[kWordsPerThread];
+        for (uint32_t sub = 0; sub < kKbPerPk; ++sub)
 #pragma unroll
             for (uint32_t q = 0; q < kWordsPerThread / 4; ++q) {
-                // 16-byte chunk of the 64-byte row: this K block's share, then this thread's half of it
-                const uint32_t c = (kb % kKbPerPk) * (kRowBlockBytes / 16) + half * (kWordsPerThread / 4) + q;
-                const uint4 v = *(const uint4*)(smem + pk_row + slot * kPkSlotBytes + ((c ^ pk_xor) << 4));
-                pk[4 * q] = v.x; pk[4 * q + 1] = v.y; pk[4 * q + 2] = v.z; pk[4 * q + 3] = v.w;
+                // 16-byte chunk of the 64-byte row: the K block's share, then this thread's half of it
+                const uint32_t c = sub * (kRowBlockBytes / 16) + half * (kWordsPerThread / 4) + q;
+                pk_off[sub * (kWordsPerThread / 4) + q] = pk_row + ((c ^ pk_xor) << 4);
             }
-            // a thread's half of a 64-wide block lies inside one group of 32 or 64
-            const uint32_t gsel = (kb % kKbPerSc) * kGroupsPerBlock + (GROUP == 64 ? 0u : half);
-            const float sc = meta_to_f32<META>(pick16(sreg, gsel));
-            const float zf = fmaf(kZero, sc, meta_to_f32<META>(pick16(breg, gsel)));
-            const uint32_t s2 = half2_dup(sc), z2 = half2_dup(zf);
-            const uint32_t st = kb % kAStages;
-            if (kb >= kAStages && !pipe_wait(&a_empty[st], ((kb / kAStages) - 1) & 1)) give_up();
-            uint8_t* a_row = smem + kOffA + st * kAStageBytes + tile * kTileBytes + r * 128;
-            // A row r: 8 chunks of 8 fp16; chunk c lives at chunk position c ^ (r & 7)
+        constexpr uint32_t kStores = BITS == 4 ? kWordsPerThread : kWordsPerThread / 2;   // 16-byte chunks written
+        uint32_t a_off[kStores];
 #pragma unroll
-            for (uint32_t i = 0; i < kWordsPerThread; ++i) {
-                constexpr uint32_t kPerWord = BITS == 4 ? 8 : 4;           // weights per packed word
-                const uint32_t w = half * kWordsPerThread + i;             // word of the K block
-                uint32_t o[4];
-                dequant_word<BITS>(pk[i], s2, z2, o);
-                if constexpr (BITS == 4) {
-                    *(uint4*)(a_row + ((w ^ (r & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
-                } else {
-                    // two words make one 16-byte chunk
-                    uint2* dst = (uint2*)(a_row + (((w >> 1) ^ (r & 7)) << 4)) + (w & 1);
-                    *dst = make_uint2(o[0], o[1]);
-                }
+        for (uint32_t i = 0; i < kStores; ++i)   // A row r: 8 chunks of 8 fp16; chunk c lives at position c ^ (r & 7)
+            a_off[i] = off_a + tile * kTileBytes + r * 128 + (((half * kStores + i) ^ (r & 7)) << 4);
+        // A scale block (8 groups of the row) at a time, its K blocks unrolled: the position in the packed slot
+        // and the group of a K block are then constants of the instruction stream.
+        uint32_t st = 0, a_round = 0;   // the stage of the next K block and how often the stages have gone round
+        for (uint32_t kb0 = 0; kb0 < KB; kb0 += kKbPerSc) {
+            if (*(volatile uint32_t*)&s_failed) break;
+            if (sc_tma) {
+                if (!pipe_wait(sc_full, (kb0 / kKbPerSc) & 1)) { give_up(); break; }
+                const uint4 sv = *(const uint4*)(smem + kOffSc + tile * (kScHalfBytes / 2) + r * 16);
+                const uint4 bv = *(const uint4*)(smem + kOffSc + kScHalfBytes + tile * (kScHalfBytes / 2) + r * 16);
+                sreg[0] = sv.x; sreg[1] = sv.y; sreg[2] = sv.z; sreg[3] = sv.w;
+                breg[0] = bv.x; breg[1] = bv.y; breg[2] = bv.z; breg[3] = bv.w;
+                // the values are in registers: the copy thread may fetch the next block's
+                __syncwarp();
+                if (lane == 0) mbar_arrive(sc_empty);
+            } else {
+                // this block's 8 groups were fetched one block ago; fetch the next block's now
+#pragma unroll
+                for (int i = 0; i < 4; ++i) { sreg[i] = snext[i]; breg[i] = bnext[i]; }
+                fetch_scales(kb0 / kKbPerSc + 1);
             }
-            fence_async_smem();
-            __syncwarp();
-            if (lane == 0) {
-                // one arrival per warp: 512 arrivals on one barrier word would serialise every K block
-                mbar_arrive(&a_full[st]);
-                // The ring slots are handed back only here: by now the values read from them have been
-                // consumed, so the reads are complete before the copy thread may overwrite the slot.
-                if ((kb + 1) % kKbPerPk == 0 || kb + 1 == KB) mbar_arrive(&pk_empty[slot]);
-                if (sc_tma && kb % kKbPerSc == 0) mbar_arrive(sc_empty);
+            uint32_t slot_base = 0, slot = 0;
+#pragma unroll
+            for (uint32_t j = 0; j < kKbPerSc; ++j) {
+                const uint32_t kb = kb0 + j;
+                if (kb >= KB) break;
+                constexpr uint32_t kSubMask = kKbPerPk - 1;
+                const uint32_t sub = j & kSubMask;         // K block within its packed slot
+                if (sub == 0) {
+                    const uint32_t u = kb / kKbPerPk;
+                    slot = u % kPkSlots;
+                    slot_base = slot * kPkSlotBytes;
+                    if (!pipe_wait(&pk_full[slot], (u / kPkSlots) & 1)) { give_up(); break; }
+                }
+                uint32_t pk[kWordsPerThread];
+#pragma unroll
+                for (uint32_t q = 0; q < kWordsPerThread / 4; ++q) {
+                    const uint4 v = *(const uint4*)(smem + slot_base + pk_off[sub * (kWordsPerThread / 4) + q]);
+                    pk[4 * q] = v.x; pk[4 * q + 1] = v.y; pk[4 * q + 2] = v.z; pk[4 * q + 3] = v.w;
+                }
+                // a thread's half of a 64-wide block lies inside one group of 32 or 64
+                const uint32_t gsel = j * kGroupsPerBlock + (GROUP == 64 ? 0u : half);
+                const float sc = meta_to_f32<META>(pick16(sreg, gsel));
+                const float zf = fmaf(kZero, sc, meta_to_f32<META>(pick16(breg, gsel)));
+                const uint32_t s2 = half2_dup(sc), z2 = half2_dup(zf);
+                if (a_round && !pipe_wait(&a_empty[st], (a_round - 1) & 1)) { give_up(); break; }
+                uint8_t* a_stage = smem + st * kAStageBytes;
+#pragma unroll
+                for (uint32_t i = 0; i < kWordsPerThread; ++i) {
+                    uint32_t o[4];
+                    dequant_word<BITS>(pk[i], s2, z2, o);
+                    if constexpr (BITS == 4) {
+                        *(uint4*)(a_stage + a_off[i]) = make_uint4(o[0], o[1], o[2], o[3]);
+                    } else {
+                        // two words make one 16-byte chunk
+                        *((uint2*)(a_stage + a_off[i >> 1]) + (i & 1)) = make_uint2(o[0], o[1]);
+                    }
+                }
+                fence_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    // one arrival per warp: 512 arrivals on one barrier word would serialise every K block
+                    mbar_arrive(&a_full[st]);
+                    // The ring slots are handed back only here: by now the values read from them have been
+                    // consumed, so the reads are complete before the copy thread may overwrite the slot.
+                    if (sub == kSubMask || kb + 1 == KB) mbar_arrive(&pk_empty[slot]);
+                }
+                if (++st == a_stages) { st = 0; ++a_round; }
             }
         }
     } else if (warp == kConvWarps && lane == 0) {
         // ---------------- MMA issue ----------------
         const uint32_t idesc = umma_idesc(N);
+        uint32_t sa = 0, a_round = 0;
         for (uint32_t kb = 0; kb < KB; ++kb) {
-            const uint32_t sa = kb % kAStages, sb = kb % kBStages;
-            if (!pipe_wait(&a_full[sa], (kb / kAStages) & 1) || !pipe_wait(&b_full[sb], (kb / kBStages) & 1)) {
+            const uint32_t sb = kb % kBStages;
+            if (!pipe_wait(&a_full[sa], a_round & 1) || !pipe_wait(&b_full[sb], (kb / kBStages) & 1)) {
                 give_up();
                 break;
             }
             tc_fence_after();
-            const uint32_t a_addr = smem_base + kOffA + sa * kAStageBytes;
+            const uint32_t a_addr = smem_base + off_a + sa * kAStageBytes;
             const uint64_t da0 = umma_smem_desc(a_addr), da1 = umma_smem_desc(a_addr + kTileBytes);
-            const uint64_t db = umma_smem_desc(smem_base + sb * kBTileBytes);
+            const uint64_t db = umma_smem_desc(smem_base + sb * b_stage);
 #pragma unroll
             for (uint32_t k = 0; k < 4; ++k)  // 4 x K16 per 64-wide block: 32 bytes further along the row
                 umma_f16(tmem_base, da0 + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
@@ -412,20 +473,24 @@ umma_expert_kernel(const ExpertArgs a, const ChunkInstance* __restrict__ inst, c
                 umma_f16(tmem_base + ncols, da1 + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
             umma_commit(&a_empty[sa]);
             umma_commit(&b_empty[sb]);
+            if (++sa == a_stages) { sa = 0; ++a_round; }
         }
         umma_commit(accum);
     } else if (warp == kConvWarps + 1 && lane == 0) {
         // ---------------- activation tiles ----------------
-        // the smallest box that holds the instance's rows: a short instance does not pay for 256 rows
-        const uint32_t bi = N <= 32 ? 0u : N <= 64 ? 1u : N <= 128 ? 2u : 3u;
-        const CUtensorMap* tmap = shared ? &maps.act_shared[bi] : &maps.act_routed[bi];
-        const uint32_t b_bytes = (32u << bi) * 128u;
+        // One or two boxes per K block: these tiles are most of what a block pulls out of L2, and a short instance
+        // does not pay for 256 rows, nor one of 80 rows for 128.
+        const CUtensorMap* maps_b = shared ? maps.act_shared : maps.act_routed;
+        const uint32_t b_bytes = (n1 + n2) * 128u;
         for (uint32_t kb = 0; kb < KB; ++kb) {
             if (*(volatile uint32_t*)&s_failed) break;
             const uint32_t sb = kb % kBStages;
             if (kb >= kBStages && !pipe_wait(&b_empty[sb], ((kb / kBStages) - 1) & 1)) { give_up(); break; }
             mbar_expect_tx(&b_full[sb], b_bytes);
-            tma_load_2d(smem_base + sb * kBTileBytes, tmap, (int32_t)(kb * 64), (int32_t)in.first, &b_full[sb]);
+            tma_load_2d(smem_base + sb * b_stage, &maps_b[b1], (int32_t)(kb * 64), (int32_t)in.first, &b_full[sb]);
+            if (n2)
+                tma_load_2d(smem_base + sb * b_stage + n1 * 128u, &maps_b[b2], (int32_t)(kb * 64),
+                            (int32_t)(in.first + n1), &b_full[sb]);
         }
     } else if (warp == kConvWarps + 2 && lane == 0) {
         // ---------------- packed weights, scales, biases ----------------
@@ -461,6 +526,8 @@ umma_expert_kernel(const ExpertArgs a, const ChunkInstance* __restrict__ inst, c
         if (!ok) report_status(a.status, kStatusWaitTimeout);
         if (*(volatile uint32_t*)&s_failed) ok = false;
         tc_fence_after();
+        // the columns' tokens and weights were written by other converter threads at the start of the block
+        if (PHASE == 1) asm volatile("bar.sync 1, %0;" ::"n"(kConverters) : "memory");
 #ifdef SHRIKE_TRACE
         if (tr && tid == 0) tr[5] = globaltimer_ns();
 #endif
@@ -675,13 +742,13 @@ cudaError_t umma_prepare(shrike_moe* m) {
     CUtensorMap* am = (CUtensorMap*)ws.tensor_maps;
     const uint64_t pairs = (uint64_t)c.max_tokens * c.top_k;
     bool ok = true;
-    for (uint32_t bi = 0; bi < 4 && ok; ++bi) {
-        const uint32_t box_rows = 32u << bi;
-        ok = make_rows_map(&am[0 * 4 + bi], ws.xs, c.d, pairs, box_rows) &&
-             make_rows_map(&am[1 * 4 + bi], ws.acts, c.f, pairs, box_rows);
+    for (int bi = 0; bi < kActBoxes && ok; ++bi) {
+        const uint32_t box_rows = 16u << bi;
+        ok = make_rows_map(&am[0 * kActBoxes + bi], ws.xs, c.d, pairs, box_rows) &&
+             make_rows_map(&am[1 * kActBoxes + bi], ws.acts, c.f, pairs, box_rows);
         if (ok && c.has_shared)
-            ok = make_rows_map(&am[2 * 4 + bi], ws.xh, c.d, c.max_tokens, box_rows) &&
-                 make_rows_map(&am[3 * 4 + bi], ws.acts_shared, c.shared_f, c.max_tokens, box_rows);
+            ok = make_rows_map(&am[2 * kActBoxes + bi], ws.xh, c.d, c.max_tokens, box_rows) &&
+                 make_rows_map(&am[3 * kActBoxes + bi], ws.acts_shared, c.shared_f, c.max_tokens, box_rows);
     }
     return ok ? cudaSuccess : cudaErrorInvalidValue;
 }
@@ -711,7 +778,7 @@ uint32_t umma_max_chunk_instances(const shrike_moe_config& c, uint32_t T) {
 }
 
 size_t umma_chunk_instance_bytes() { return sizeof(ChunkInstance); }
-size_t umma_tensor_map_bytes() { return 16 * sizeof(CUtensorMap); }
+size_t umma_tensor_map_bytes() { return 4 * kActBoxes * sizeof(CUtensorMap); }
 
 // Gate/up + GLU, then down, for the instances built from the grouping the
 // prefill plan left in the workspace.
@@ -735,16 +802,16 @@ cudaError_t launch_umma_prefill(const shrike_moe* m, cudaStream_t st, const Expe
                 return cudaErrorInvalidValue;
             left -= cells;
         }
-        for (int bi = 0; bi < 4; ++bi) mp.act_routed[bi] = am[phase * 4 + bi];
+        for (int bi = 0; bi < kActBoxes; ++bi) mp.act_routed[bi] = am[phase * kActBoxes + bi];
         if (c.has_shared) {
             const uint32_t kds = phase == 0 ? c.d : c.shared_f, rws = phase == 0 ? c.shared_f : c.d;
             if (!make_weight_maps(&mp.shared, a.shared_block, a.shared, phase, kds, rws, c.weight_bits, c.group_size, 1,
                                   16))
                 return cudaErrorInvalidValue;
-            for (int bi = 0; bi < 4; ++bi) mp.act_shared[bi] = am[(2 + phase) * 4 + bi];
+            for (int bi = 0; bi < kActBoxes; ++bi) mp.act_shared[bi] = am[(2 + phase) * kActBoxes + bi];
         } else {
             mp.shared = mp.routed[0];
-            for (int bi = 0; bi < 4; ++bi) mp.act_shared[bi] = mp.act_routed[bi];
+            for (int bi = 0; bi < kActBoxes; ++bi) mp.act_shared[bi] = mp.act_routed[bi];
         }
     }
     ChunkInstance* inst = (ChunkInstance*)ws.chunk_inst;
