@@ -465,12 +465,13 @@ umma_expert_kernel(const ExpertArgs a, const ChunkInstance* __restrict__ inst, c
             const uint32_t a_addr = smem_base + off_a + sa * kAStageBytes;
             const uint64_t da0 = umma_smem_desc(a_addr), da1 = umma_smem_desc(a_addr + kTileBytes);
             const uint64_t db = umma_smem_desc(smem_base + sb * b_stage);
+            // 4 x K16 per 64-wide block: 32 bytes further along the row. The two tiles alternate: consecutive
+            // instructions then add into different accumulators.
 #pragma unroll
-            for (uint32_t k = 0; k < 4; ++k)  // 4 x K16 per 64-wide block: 32 bytes further along the row
+            for (uint32_t k = 0; k < 4; ++k) {
                 umma_f16(tmem_base, da0 + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
-#pragma unroll
-            for (uint32_t k = 0; k < 4; ++k)
                 umma_f16(tmem_base + ncols, da1 + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
+            }
             umma_commit(&a_empty[sa]);
             umma_commit(&b_empty[sb]);
             if (++sa == a_stages) { sa = 0; ++a_round; }

@@ -144,3 +144,42 @@ def test_layer_forward_host_round_trip(cuda_device):
     assert (y_host.numpy() == y_dev).all()
     assert (ids_host.numpy().astype(np.uint32) == ids_dev).all() and (w_host.numpy() == w_dev).all()
     layer.close()
+
+
+@pytest.mark.parametrize("T", [1, 3])
+def test_decode_stack_host_entry_point_equals_the_layer_calls(cuda_device, T):
+    """shrike_decode_stack_forward_host (host rows in, every layer, host rows out) against the same layers called
+    one by one with device pointers, and the first layer's output against the oracle. Three stacked layers that
+    share one pool; the residual stream takes a fresh row before every layer."""
+    import torch
+    from shrike_b200.moe import DecodeStack
+    cfg = fx.qwen_config(max_tokens=16, d=512, f=256, shared_f=256, num_experts=64, y_dtype=capi.DTYPE_FP32)
+    layers = [Layer(cfg, seed=150 + l, device_fill=True) for l in range(3)]
+    # block 0 enters layer 0; block l + 1 is what layer l's output is added to and what layer l + 1 reads
+    rows = np.stack([fx.round_bf16(inputs(T, cfg.d, seed=60 + l)) for l in range(4)])
+    rows_host = torch.from_numpy(rows).to(torch.bfloat16).contiguous()
+    out_host = torch.empty((T, cfg.d), dtype=torch.bfloat16)
+    stack = DecodeStack([(L.moe, L.pool, L.offsets, 0, L.router_ops, L.shared) for L in layers], T)
+    for _ in range(2):   # a second call reuses every buffer
+        stack.forward_host(rows_host, out_host)
+    for L in layers:
+        L.moe.status()
+    # the same stream, layer by layer
+    dev = torch.device("cuda:0")
+    blocks = rows_host.to(dev)
+    y = torch.empty((T, cfg.d), dtype=torch.float32, device=dev)
+    ids = torch.zeros((T, cfg.top_k), dtype=torch.int32, device=dev)
+    w = torch.zeros((T, cfg.top_k), dtype=torch.float32, device=dev)
+    for l, L in enumerate(layers):
+        L.moe.encode_decode_layer(L.pool, L.offsets, 0, L.router_ops, blocks[l], y, blocks[l + 1], L.shared, ids, w)
+        if l == 0:
+            torch.cuda.synchronize()
+            y0, ids0, w0 = y.cpu().numpy().copy(), ids.cpu().numpy().astype(np.uint32), w.cpu().numpy().copy()
+    torch.cuda.synchronize()
+    assert torch.equal(out_host, blocks[3].cpu())
+    ids_ref, w_ref, _ = layers[0].oracle_route(rows[0])
+    assert (ids0 == ids_ref).all() and (w0 == w_ref).all()
+    assert rel_l2(y0, layers[0].oracle_forward(rows[0], ids_ref, w_ref)) <= TOL
+    stack.close()
+    for L in layers:
+        L.close()
