@@ -293,7 +293,11 @@ int shrike_encode_moe_prefill(shrike_moe* moe, void* stream, const shrike_pool* 
  * on the device: sorts the query_count*top_k (token, expert, rank, weight bits)
  * pairs by (expert, token, rank). sorted_pairs: 4 u32 per pair
  * (PrefillTokenExpertPair, PrefillRouter.swift:5-28); offsets/counts u32
- * [num_experts] (offset 0xffffffff for an unrouted expert). */
+ * [num_experts] (offset 0xffffffff for an unrouted expert).
+ * A row's top_k ids must be distinct (a router never picks an expert twice);
+ * a row that names an expert twice, or an id >= num_experts other than the
+ * expert-parallel sentinel 0xffffffff, is reported through the status word
+ * (SHRIKE_ERANGE) by this call and by shrike_encode_moe_prefill. */
 int shrike_encode_group_pairs(shrike_moe* moe, void* stream, const uint32_t* topk_indices,
                               const float* routing_weights, uint32_t query_count,
                               uint32_t* sorted_pairs, uint32_t* per_expert_offsets,
