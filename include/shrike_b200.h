@@ -172,6 +172,17 @@ int shrike_pool_fill_synthetic(shrike_moe* moe, shrike_pool* pool, uint32_t firs
                                uint32_t count, uint64_t seed, uint32_t layer,
                                uint32_t first_expert, int shared, void* stream);
 
+/* Affine rows -> fp32, on the device: out[r][c] = q[r][c] * scale[r][c / group] + bias[r][c / group], one rounding
+ * (fmaf). For operands this library takes as fp32 and a `.gturbo` file holds packed: the shared expert's scalar
+ * gate row -- int8 [1 x d] with g64 scales and biases, multiplied by the Metal host with its own int8 GEMV
+ * (SharedExpertInt8.swift:55-227, RealForwardRunner.swift:5447-5467) -- is uploaded verbatim and turned into the
+ * `shared_gate` operand of shrike_router_operands once per layer, at load time. No handle, no allocation.
+ * bits 4 or 8 (nibbles low first); group 32 or 64; meta_dtype SHRIKE_DTYPE_BF16 or _FP16; cols a multiple of
+ * group; packed rows are cols * bits / 8 bytes, scale and bias rows cols / group elements, all dense. */
+int shrike_dequant_affine_rows(void* stream, const void* packed, const void* scales, const void* biases,
+                               uint32_t bits, uint32_t group, uint32_t meta_dtype, uint32_t rows, uint32_t cols,
+                               float* out);
+
 /* ---- residency table ----------------------------------------------------- */
 
 /* ExpertResidencyEntry (ExpertResidencyTable.swift:4-19): one u64 per expert,

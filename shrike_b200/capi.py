@@ -102,6 +102,7 @@ SIGNATURES = {
     "shrike_ep_destroy": (None, [_P]),
     "shrike_ep_export": (_INT, [_P, _P]),
     "shrike_ep_connect": (_INT, [_P, _P]),
+    "shrike_dequant_affine_rows": (_INT, [_P, _P, _P, _P, _U32, _U32, _U32, _U32, _U32, _P]),
     "shrike_ep_buffer": (_INT, [_P, C.POINTER(_P), C.POINTER(_U64)]),
     "shrike_ep_connect_pointers": (_INT, [_P, C.POINTER(_P)]),
     "shrike_ep_set_wait_polls": (_INT, [_P, _U32]),

@@ -792,6 +792,19 @@ int shrike_moe_layer_forward_host(shrike_moe* m, void* stream, const shrike_pool
     return shrike_moe_status(m, stream);
 }
 
+int shrike_dequant_affine_rows(void* stream, const void* packed, const void* scales, const void* biases,
+                               uint32_t bits, uint32_t group, uint32_t meta_dtype, uint32_t rows, uint32_t cols,
+                               float* out) {
+    if (!packed || !scales || !biases || !out) return SHRIKE_EINVAL;
+    if ((bits != 4 && bits != 8) || (group != 32 && group != 64) || cols == 0 || cols % group != 0 ||
+        (meta_dtype != SHRIKE_DTYPE_BF16 && meta_dtype != SHRIKE_DTYPE_FP16))
+        return SHRIKE_EINVAL;
+    if (rows == 0) return SHRIKE_OK;
+    if ((uint64_t)rows * cols > 0x7fffffffull * 256) return SHRIKE_ERANGE;
+    return launch_dequant_affine_rows((cudaStream_t)stream, packed, scales, biases, bits, group, meta_dtype, rows, cols,
+                                      out) == cudaSuccess ? SHRIKE_OK : SHRIKE_EIO;
+}
+
 // ---- expert parallelism over peer memory ---------------------------------------------------------------
 
 struct shrike_ep {
@@ -839,10 +852,14 @@ int shrike_ep_create(shrike_moe* home, shrike_moe* routed, uint32_t rank, uint32
         return fail(m, SHRIKE_EINVAL, "ep: world must be 1..%u and rank below it", SHRIKE_EP_MAX_WORLD);
     if (c.num_experts % world != 0 || r.num_experts != c.num_experts / world)
         return fail(m, SHRIKE_EINVAL, "ep: the routed handle must hold num_experts / world experts");
-    if (r.d != c.d || r.f != c.f || r.top_k != c.top_k || r.weight_bits != c.weight_bits || r.group_size != c.group_size ||
-        r.meta_dtype != c.meta_dtype || r.act_dtype != c.act_dtype || r.y_dtype != c.y_dtype ||
+    // weight_bits, group_size and meta_dtype may differ: the home handle's describe the shared expert's block, the
+    // routed handle's the routed experts' (an int8 shared expert beside int4 routed experts,
+    // SharedExpertInt8.swift:55-227)
+    if (r.d != c.d || r.f != c.f || r.top_k != c.top_k || r.act_dtype != c.act_dtype || r.y_dtype != c.y_dtype ||
         r.activation != c.activation || r.expert_bias != c.expert_bias || r.has_shared || home->device != routed->device)
         return fail(m, SHRIKE_EINVAL, "ep: the routed handle must share the layer's shape, dtypes and device and have no shared expert");
+    if ((r.weight_bits != c.weight_bits || r.group_size != c.group_size || r.meta_dtype != c.meta_dtype) && !c.has_shared)
+        return fail(m, SHRIKE_EINVAL, "ep: the handles' weight formats differ but the home handle has no shared expert to describe");
     if (rows_per_call == 0 || rows_per_call > c.max_tokens)
         return fail(m, SHRIKE_ERANGE, "ep: rows_per_call must be 1..max_tokens of the home handle");
     const uint32_t t_max = world * rows_per_call;

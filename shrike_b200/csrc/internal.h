@@ -227,6 +227,9 @@ size_t fused_geom_bytes();
 size_t fused_map_cache_bytes();
 size_t fused_logits_bytes(const shrike_moe_config& c);
 size_t fused_acts_bytes(const shrike_moe_config& c);
+cudaError_t launch_dequant_affine_rows(cudaStream_t st, const void* packed, const void* scales, const void* biases,
+                                       uint32_t bits, uint32_t group, uint32_t meta_dtype, uint32_t rows, uint32_t cols,
+                                       float* out);
 cudaError_t launch_fused_layer(const shrike_moe* m, cudaStream_t st, const ExpertArgs& ea,
                                const shrike_router_operands& ops, const uint64_t* table, uint32_t pool_cells,
                                const uint32_t* io_status, const void* x, uint32_t* ids, float* weights,

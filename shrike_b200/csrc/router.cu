@@ -648,6 +648,33 @@ static int static_router_fail(char* text, size_t bytes, int code, const char* ms
     return code;
 }
 
+
+// Affine rows -> fp32 (load-time utility for operands a packed file holds quantised): one thread per element.
+__global__ void __launch_bounds__(256)
+dequant_affine_rows_kernel(const uint8_t* __restrict__ packed, const uint16_t* __restrict__ scales,
+                           const uint16_t* __restrict__ biases, uint32_t bits, uint32_t group, uint32_t meta_f16,
+                           uint32_t rows, uint32_t cols, float* __restrict__ out) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (size_t)rows * cols) return;
+    const uint32_t r = (uint32_t)(i / cols), c = (uint32_t)(i - (size_t)r * cols);
+    const uint8_t byte = packed[(size_t)r * (cols * bits / 8) + (bits == 4 ? c / 2 : c)];
+    const uint32_t q = bits == 4 ? ((c & 1u) ? (uint32_t)(byte >> 4) : (uint32_t)(byte & 15u)) : (uint32_t)byte;
+    const size_t g = (size_t)r * (cols / group) + c / group;
+    const float sc = meta_f16 ? f16_bits_to_f32(scales[g]) : bf16_bits_to_f32(scales[g]);
+    const float bi = meta_f16 ? f16_bits_to_f32(biases[g]) : bf16_bits_to_f32(biases[g]);
+    out[i] = __fmaf_rn((float)q, sc, bi);
+}
+
+cudaError_t launch_dequant_affine_rows(cudaStream_t st, const void* packed, const void* scales, const void* biases,
+                                       uint32_t bits, uint32_t group, uint32_t meta_dtype, uint32_t rows, uint32_t cols,
+                                       float* out) {
+    const size_t n = (size_t)rows * cols;
+    dequant_affine_rows_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(
+        (const uint8_t*)packed, (const uint16_t*)scales, (const uint16_t*)biases, bits, group,
+        meta_dtype == SHRIKE_DTYPE_FP16 ? 1u : 0u, rows, cols, out);
+    return cudaGetLastError();
+}
+
 }  // namespace shrike
 
 extern "C" int shrike_encode_router_static(const shrike_moe_config* config, void* stream,

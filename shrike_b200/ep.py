@@ -37,10 +37,13 @@ class ExpertParallelLayer:
     """One MoE layer under expert parallelism on this rank's GPU."""
 
     def __init__(self, config: MoEConfig, rank: int, world: int, device: int, rows_per_rank: int,
-                 group: Optional[dist.ProcessGroup] = None, exchange: str = "peer", connect: bool = True):
+                 group: Optional[dist.ProcessGroup] = None, exchange: str = "peer", connect: bool = True,
+                 routed_config: Optional[MoEConfig] = None):
         """connect=False (peer exchange, world > 1): the ranks' buffers are not exchanged through the process
         group; the caller hands the peers' base pointers to `connect_pointers` (one process driving several
-        GPUs, or a test that stands in for a peer)."""
+        GPUs, or a test that stands in for a peer).
+        routed_config: the routed experts' weight format where it differs from the shared expert's (`config` then
+        describes the shared expert's block: an int8 shared expert beside int4 routed experts); peer exchange only."""
         if exchange not in ("peer", "nccl"):
             raise ValueError("exchange must be 'peer' or 'nccl'")
         self.cfg = config
@@ -54,9 +57,12 @@ class ExpertParallelLayer:
         self.home = MoE(dataclasses.replace(config, max_tokens=max(rows_per_rank, 1)), device)
         # routed handle: this rank's experts on every row it may receive
         recv_rows = world * self.cap
-        self.routed = MoE(dataclasses.replace(config, num_experts=self.epr, has_shared=False, shared_gated=False,
+        rcfg = routed_config if routed_config is not None else config
+        if routed_config is not None and exchange != "peer":
+            raise ValueError("routed_config needs the peer exchange")
+        self.routed = MoE(dataclasses.replace(rcfg, num_experts=self.epr, has_shared=False, shared_gated=False,
                                               shared_f=0, max_tokens=max(recv_rows, 65)), device)
-        self.offsets, self.block_bytes = expert_offsets(config)
+        self.offsets, self.block_bytes = expert_offsets(rcfg)
         self.pool = ExpertCellArena(self.routed, self.epr, round_up(self.block_bytes, 256))
         self.routed.create_residency(1)
         self.routed.residency_set_layer_identity(0, 0)

@@ -268,3 +268,41 @@ def test_two_ranks_over_peer_memory_match_the_oracle(cuda_device, tmp_path):
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 def test_two_nccl_ranks_match_the_oracle(cuda_device, tmp_path):
     _two_ranks(tmp_path, "nccl")
+
+
+@pytest.mark.parametrize("T", [8, 96])
+def test_int8_shared_expert_beside_int4_routed_experts(cuda_device, T):
+    """The reference's Qwen layers keep the shared expert in int8 and the routed experts in int4
+    (SharedExpertInt8.swift:55-227): the home handle describes the shared expert's block, the routed handle the
+    routed experts'; one rank. Against the oracle with the two formats."""
+    import fixtures as fx
+    import oracle_lib as O
+    from shrike_b200 import capi
+    from shrike_b200.ep import ExpertParallelLayer
+    from shrike_b200.moe import RouterOperands, expert_offsets
+    seed = 27
+    cfg4 = _config()                                         # routed experts: int4
+    cfg8 = dataclasses.replace(cfg4, weight_bits=8)          # the shared expert's format
+    x, router = _problem(T, cfg4)
+    dev = torch.device("cuda:0")
+    layer = ExpertParallelLayer(cfg8, 0, 1, 0, T, None, exchange="peer", routed_config=cfg4)
+    for e in range(layer.lo, layer.hi):
+        layer.pool.upload(e - layer.lo, fx.synth_block(cfg4, seed, 0, e))
+    sh_block = fx.synth_block(cfg8, seed, 0, 100000, shared=True)
+    sh = torch.from_numpy(sh_block.copy()).to(dev)
+    layer.set_shared(capi.SharedExpert(sh.data_ptr(), expert_offsets(cfg8, shared=True)[0]))
+    ops = RouterOperands(weights=torch.from_numpy(router).to(dev))
+    xd = torch.from_numpy(x).to(dev)
+    y = torch.empty_like(xd)
+    layer.forward(ops, xd, y)
+    layer.status()
+    ids = np.zeros((T, cfg4.top_k), np.uint32)
+    w = np.zeros((T, cfg4.top_k), np.float32)
+    for t in range(T):
+        ids[t], w[t] = O.router_select(O.router_logits_f32(router, x[t]), cfg4.top_k, round_f16=True)
+    blocks = {int(e): fx.synth_block(cfg4, seed, 0, int(e)) for e in np.unique(ids)}
+    lcfg = O.layer_cfg(O.expert_cfg(cfg4.d, cfg4.f), O.expert_cfg(cfg4.d, cfg4.shared_f, bits=8), False)
+    y_ref = O.moe_layer(lcfg, blocks, sh_block, None, x, ids, w)
+    got = y.cpu().numpy()
+    assert np.linalg.norm(got - y_ref) / np.linalg.norm(y_ref) <= 1e-3
+    layer.close()

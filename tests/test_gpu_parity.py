@@ -632,3 +632,30 @@ def test_slot_outside_the_pool_is_reported_not_followed(cuda_device):
     assert e.value.code == capi.ERANGE
     layer.moe.status()  # the word was cleared; the handle stays usable
     layer.close()
+
+
+@pytest.mark.parametrize("bits,group,meta", [(8, 64, capi.DTYPE_BF16), (4, 32, capi.DTYPE_FP16)])
+def test_affine_rows_to_fp32(cuda_device, bits, group, meta):
+    """shrike_dequant_affine_rows (how the shared expert's int8 gate row of a packed file becomes the fp32
+    `shared_gate` operand) against numpy, bit for bit; a width it does not know is refused."""
+    import ctypes as C
+    import torch
+    lib = capi.load()
+    rng = np.random.default_rng(9)
+    rows, cols = 3, 512
+    wf = rng.normal(0, 0.05, (rows, cols)).astype(np.float32)
+    packed, s_bits, b_bits = fx.quantize_affine(wf, bits, group, meta)
+    dev = torch.device("cuda:0")
+    pk, sc, bi = (torch.from_numpy(np.ascontiguousarray(a)).to(dev) for a in (packed, s_bits.view(np.int16), b_bits.view(np.int16)))
+    out = torch.empty((rows, cols), dtype=torch.float32, device=dev)
+    rc = lib.shrike_dequant_affine_rows(None, pk.data_ptr(), sc.data_ptr(), bi.data_ptr(), bits, group, meta, rows, cols,
+                                        out.data_ptr())
+    assert rc == 0
+    torch.cuda.synchronize()
+    q = packed.astype(np.float32) if bits == 8 else np.stack([packed & 15, packed >> 4], axis=2).reshape(rows, cols).astype(np.float32)
+    s = np.repeat(fx.meta_to_f32(s_bits, meta), group, axis=1)
+    b = np.repeat(fx.meta_to_f32(b_bits, meta), group, axis=1)
+    ref = (q.astype(np.float64) * s.astype(np.float64) + b.astype(np.float64)).astype(np.float32)   # one rounding, as fmaf
+    assert (out.cpu().numpy() == ref).all()
+    assert lib.shrike_dequant_affine_rows(None, pk.data_ptr(), sc.data_ptr(), bi.data_ptr(), 5, group, meta, rows, cols,
+                                          out.data_ptr()) == capi.EINVAL
