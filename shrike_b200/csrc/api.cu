@@ -799,6 +799,7 @@ int shrike_dequant_affine_rows(void* stream, const void* packed, const void* sca
     if ((bits != 4 && bits != 8) || (group != 32 && group != 64) || cols == 0 || cols % group != 0 ||
         (meta_dtype != SHRIKE_DTYPE_BF16 && meta_dtype != SHRIKE_DTYPE_FP16))
         return SHRIKE_EINVAL;
+    if (((uintptr_t)scales & 1) || ((uintptr_t)biases & 1) || ((uintptr_t)out & 3)) return SHRIKE_EINVAL;
     if (rows == 0) return SHRIKE_OK;
     if ((uint64_t)rows * cols > 0x7fffffffull * 256) return SHRIKE_ERANGE;
     return launch_dequant_affine_rows((cudaStream_t)stream, packed, scales, biases, bits, group, meta_dtype, rows, cols,
