@@ -981,6 +981,10 @@ __global__ void __launch_bounds__(kFusedThreads, 1) decode_layer_kernel(const __
         }
         FUSED_TS(8);   // this warp's gate/up units done
         if (plan.n_tiles > 0) {
+            // (worked out before the wait for the activations, not after it)
+            const uint32_t cpe_s = has_shared ? (a.f_shared / GROUP) / G.cg_p2[1] : 0u;   // chunks of the shared expert
+            const uint32_t cpe_r = (a.f / GROUP) / G.cg_p2[0];                            // chunks of a routed expert
+            const uint32_t items = cpe_s + plan.n_routed * cpe_r;
             // ---- all instances' activations: poll until published, stage, group sums. A thread's blocks are
             // all requested before the first is examined. ----
             {
@@ -1026,9 +1030,6 @@ __global__ void __launch_bounds__(kFusedThreads, 1) decode_layer_kernel(const __
                 consumers_sync();
             }
             FUSED_TS(9);   // activations of every instance staged
-            const uint32_t cpe_s = has_shared ? (a.f_shared / GROUP) / G.cg_p2[1] : 0u;   // chunks of the shared expert
-            const uint32_t cpe_r = (a.f / GROUP) / G.cg_p2[0];                            // chunks of a routed expert
-            const uint32_t items = cpe_s + plan.n_routed * cpe_r;
             for (uint32_t m = 0; m < plan.n_tiles; ++m) {
                 const uint32_t u0 = plan.n1 + m * packs_eff;   // the tile's first unit
                 const uint32_t row0 = (plan.n_blk - 1u - plan.blk + m * plan.n_blk) * 16u;
