@@ -325,7 +325,7 @@ __device__ __forceinline__ void lds_words(const uint8_t* p, uint32_t (&w)[W]) {
     }
 }
 
-// CG consecutive 16-bit values starting at an address that is a multiple of 2 * CG bytes.
+// CG consecutive 16-bit values starting at an address that is a multiple of min(2 * CG, 4) bytes.
 template <int CG, int META>
 __device__ __forceinline__ void lds_meta(const uint8_t* p, float (&out)[CG]) {
     if constexpr (CG == 1) {
@@ -335,7 +335,8 @@ __device__ __forceinline__ void lds_meta(const uint8_t* p, float (&out)[CG]) {
         out[0] = meta_to_f32<META>((uint16_t)(v & 0xffffu));
         out[1] = meta_to_f32<META>((uint16_t)(v >> 16));
     } else {
-        const uint2 v = *(const uint2*)p;
+        // two 32-bit loads where a row of scales is only 4-byte aligned (group count even, not a multiple of 4)
+        const uint2 v = make_uint2(*(const uint32_t*)p, *(const uint32_t*)(p + 4));
         out[0] = meta_to_f32<META>((uint16_t)(v.x & 0xffffu));
         out[1] = meta_to_f32<META>((uint16_t)(v.x >> 16));
         out[2] = meta_to_f32<META>((uint16_t)(v.y & 0xffffu));
@@ -396,16 +397,22 @@ __device__ __noinline__ float2 chunk_rows(const uint8_t* rowA, const uint8_t* ro
     return make_float2(q0 + z0, q1 + z1);
 }
 
-// The chunk width is uniform for a unit; one call site per width.
+// Chunk c of a row of `groups` groups. Width 4: chunks of four groups and, when two groups are left over, a last
+// chunk of two (90 groups of 32 at d = 2880: 22 + 1 chunks, not 45 of two). One call site per width.
 template <int BITS, int GROUP, int META>
-__device__ __forceinline__ float2 chunk_rows_cg(uint32_t cg, const uint8_t* rowA, const uint8_t* rowB, uint32_t slab,
-                                                const uint8_t* s0p, const uint8_t* b0p, const uint8_t* s1p,
+__device__ __forceinline__ float2 chunk_rows_cg(uint32_t cg, uint32_t groups, const uint8_t* rowA, const uint8_t* rowB,
+                                                uint32_t slab, const uint8_t* s0p, const uint8_t* b0p, const uint8_t* s1p,
                                                 const uint8_t* b1p, const uint16_t* bsm, const float2* xs, uint32_t c,
                                                 uint32_t t) {
-    if (cg == 4) return chunk_rows<BITS, GROUP, META, 4>(rowA, rowB, slab, s0p, b0p, s1p, b1p, bsm, xs, c * 4, t);
+    if (cg == 4) {
+        if (c * 4 + 4 <= groups) return chunk_rows<BITS, GROUP, META, 4>(rowA, rowB, slab, s0p, b0p, s1p, b1p, bsm, xs, c * 4, t);
+        return chunk_rows<BITS, GROUP, META, 2>(rowA, rowB, slab, s0p, b0p, s1p, b1p, bsm, xs, c * 4, t);
+    }
     if (cg == 2) return chunk_rows<BITS, GROUP, META, 2>(rowA, rowB, slab, s0p, b0p, s1p, b1p, bsm, xs, c * 2, t);
     return chunk_rows<BITS, GROUP, META, 1>(rowA, rowB, slab, s0p, b0p, s1p, b1p, bsm, xs, c, t);
 }
+// chunks of a row of `groups` groups at width cg
+__device__ __forceinline__ uint32_t chunks_of(uint32_t groups, uint32_t cg) { return cg == 4 ? (groups + 3) / 4 : groups / cg; }
 
 // {sum x, sum offset * x} of group `grp` of an fp16 operand row in shared memory.
 template <int BITS, int GROUP>
@@ -937,9 +944,9 @@ __global__ void __launch_bounds__(kFusedThreads, 1) decode_layer_kernel(const __
                 const uint8_t* b0p = s0p + 16 * GD;
                 const uint8_t* s1p = s0p + 32 * GD;
                 const uint8_t* b1p = s0p + 48 * GD;
-                const uint32_t cg = G.cg_p1, chunks = GD / cg;
+                const uint32_t cg = G.cg_p1, chunks = chunks_of(GD, cg);
                 for (uint32_t c = wi; c < chunks; c += kGroupWarps) {
-                    const float2 o = chunk_rows_cg<BITS, GROUP, META>(cg, rowA, rowB, slab, s0p, b0p, s1p, b1p, x_sm, xs_sm, c, t);
+                    const float2 o = chunk_rows_cg<BITS, GROUP, META>(cg, GD, rowA, rowB, slab, s0p, b0p, s1p, b1p, x_sm, xs_sm, c, t);
                     tot0 += o.x;
                     tot1 += o.y;
                 }
@@ -982,8 +989,8 @@ __global__ void __launch_bounds__(kFusedThreads, 1) decode_layer_kernel(const __
         FUSED_TS(8);   // this warp's gate/up units done
         if (plan.n_tiles > 0) {
             // (worked out before the wait for the activations, not after it)
-            const uint32_t cpe_s = has_shared ? (a.f_shared / GROUP) / G.cg_p2[1] : 0u;   // chunks of the shared expert
-            const uint32_t cpe_r = (a.f / GROUP) / G.cg_p2[0];                            // chunks of a routed expert
+            const uint32_t cpe_s = has_shared ? chunks_of(a.f_shared / GROUP, G.cg_p2[1]) : 0u;   // chunks of the shared expert
+            const uint32_t cpe_r = chunks_of(a.f / GROUP, G.cg_p2[0]);                            // chunks of a routed expert
             const uint32_t items = cpe_s + plan.n_routed * cpe_r;
             // ---- all instances' activations: poll until published, stage, group sums. A thread's blocks are
             // all requested before the first is examined. ----
@@ -1057,7 +1064,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) decode_layer_kernel(const __
                     const uint8_t* b1p = s1p + 32 * G2;
                     const uint16_t* bsm = acts_sm + (size_t)in * G.acts_stride;
                     const float2* xs = asum_sm + (size_t)in * gmax2;
-                    const float2 o = chunk_rows_cg<BITS, GROUP, META>(G.cg_p2[sh], rowA, rowB, slab, s0p, b0p, s1p, b1p, bsm, xs, c, t);
+                    const float2 o = chunk_rows_cg<BITS, GROUP, META>(G.cg_p2[sh], G2, rowA, rowB, slab, s0p, b0p, s1p, b1p, bsm, xs, c, t);
                     float o0 = o.x, o1 = o.y;
                     if (a.expert_bias && c == 0) {
                         const uint16_t* ab = (const uint16_t*)(eb + G.p2_ab_off[sh]);
@@ -1132,7 +1139,7 @@ bool fused_geometry(const shrike_moe_config& c, int sm_count, int max_smem_optin
     g.p1_meta_off = align_up(16 * rb1, 128);
     g.p1_ab_off = align_up(g.p1_meta_off + 64 * G1, 128);
     g.p1_bytes = g.p1_ab_off + 128;
-    auto pick_cg = [](uint32_t groups) { return groups % 4 == 0 ? 4u : groups % 2 == 0 ? 2u : 1u; };
+    auto pick_cg = [](uint32_t groups) { return groups % 2 == 0 && groups >= 4 ? 4u : groups % 2 == 0 ? 2u : 1u; };
     g.cg_p1 = pick_cg(G1);
     for (int sh = 0; sh < 2; ++sh) {
         const uint32_t F = sh ? (c.has_shared ? c.shared_f : c.f) : c.f;
