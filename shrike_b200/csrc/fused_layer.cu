@@ -529,8 +529,15 @@ __device__ __noinline__ float affine_row_dot(const uint8_t* row, const uint16_t*
 }
 __device__ __noinline__ float glu_call(float gate, float up, uint32_t activation) { return glu(gate, up, activation); }
 
-template <int BITS, int GROUP, int META>
+// PLAIN: the layer is bf16 rows in, fp32 router rows, SiLU, no additive expert biases (the flagship shapes): those
+// choices are then constants of the instruction stream instead of branches in it. A kernel of this kind runs
+// every code region once per launch, so what it does not fetch it does not wait for.
+template <int BITS, int GROUP, int META, bool PLAIN>
 __global__ void __launch_bounds__(kFusedThreads, 1) decode_layer_kernel(const __grid_constant__ FusedArgs a) {
+    const uint32_t cfg_act_dtype = PLAIN ? (uint32_t)SHRIKE_DTYPE_BF16 : a.act_dtype;
+    const uint32_t cfg_activation = PLAIN ? (uint32_t)SHRIKE_ACT_SILU : a.activation;
+    const uint32_t cfg_expert_bias = PLAIN ? 0u : a.expert_bias;
+    const uint32_t cfg_rbits = PLAIN ? 0u : a.rbits;
     using Q = FQ<BITS, GROUP>;
     extern __shared__ __align__(128) uint8_t dsm[];
     __shared__ FusedStatic st;
@@ -572,7 +579,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) decode_layer_kernel(const __
     const uint32_t my_row = blockIdx.x + cw * gridDim.x;
     const bool routes = !is_producer && cw < G.router_rows_per_block && my_row < router_rows;
     const bool row_is_gate = routes && a.gate_row && my_row == a.ne;
-    const bool row_f32 = a.rbits == 0 || row_is_gate;
+    const bool row_f32 = cfg_rbits == 0 || row_is_gate;
     __syncthreads();   // barriers initialised
     if (tid == 32) {
         // fp32 router rows (and the gate row) of this block -> shared memory, one bulk copy each
@@ -580,13 +587,13 @@ __global__ void __launch_bounds__(kFusedThreads, 1) decode_layer_kernel(const __
         for (uint32_t k = 0; k < G.router_rows_per_block; ++k) {
             const uint32_t e = blockIdx.x + k * gridDim.x;
             const bool gate = a.gate_row && e == a.ne;
-            if (e < router_rows && (a.rbits == 0 || gate)) bytes += D * 4;
+            if (e < router_rows && (cfg_rbits == 0 || gate)) bytes += D * 4;
         }
         mbar_expect_tx(&st.rw_bar, bytes);
         for (uint32_t k = 0; k < G.router_rows_per_block; ++k) {
             const uint32_t e = blockIdx.x + k * gridDim.x;
             const bool gate = a.gate_row && e == a.ne;
-            if (e < router_rows && (a.rbits == 0 || gate))
+            if (e < router_rows && (cfg_rbits == 0 || gate))
                 bulk_g2s(dsm + G.off_rw + (size_t)k * D * 4, gate ? (const void*)a.gate_row : (const void*)((const float*)a.rw + (size_t)e * D),
                          D * 4, &st.rw_bar);
         }
@@ -602,10 +609,10 @@ __global__ void __launch_bounds__(kFusedThreads, 1) decode_layer_kernel(const __
             const uint32_t cell = sh ? 0u : st.route.cell[u.inst()];
             const uint32_t mi = sh ? SHRIKE_MAX_POOL_CHUNKS : cell / a.pool.cells_per_chunk;
             const int32_t cc = sh ? 0 : (int32_t)(cell % a.pool.cells_per_chunk);
-            mbar_expect_tx(bar, 16 * rb1 + 64 * GD + (a.expert_bias ? 32u : 0u));
+            mbar_expect_tx(bar, 16 * rb1 + 64 * GD + (cfg_expert_bias ? 32u : 0u));
             tma_5d(stage + G.p1_meta_off, &a.maps.m1[mi], 0, (int32_t)(u.r0 / 8), 0, 0, cc, bar);   // the small one first
             tma_5d(stage, &a.maps.w1[mi], 0, (int32_t)u.r0, 0, 0, cc, bar);
-            if (a.expert_bias) {
+            if (cfg_expert_bias) {
                 const uint8_t* base = sh ? a.shared_block : pool_cell_base(a.pool, cell);
                 const Offsets3& off = sh ? a.shared : a.routed;
                 bulk_g2s(ring + (size_t)slot * G.slot_bytes + G.p1_ab_off, base + off.ab[0] + (size_t)u.r0 * 2, 16, bar);
@@ -614,7 +621,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) decode_layer_kernel(const __
         } else {
             const uint32_t F = sh ? a.f_shared : a.f, G2 = F / GROUP, rb2 = F * BITS / 8;
             const uint32_t count = u.count();
-            mbar_expect_tx(bar, count * (16 * rb2 + 64 * G2 + (a.expert_bias ? 32u : 0u)));   // count 0: the arrival alone
+            mbar_expect_tx(bar, count * (16 * rb2 + 64 * G2 + (cfg_expert_bias ? 32u : 0u)));   // count 0: the arrival alone
             for (uint32_t q = 0; q < count; ++q) {
                 const uint32_t cell = sh ? 0u : st.route.cell[u.inst() + q];
                 const uint32_t mi = sh ? SHRIKE_MAX_POOL_CHUNKS : cell / a.pool.cells_per_chunk;
@@ -622,7 +629,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) decode_layer_kernel(const __
                 const uint32_t eb = stage + q * G.p2_expert_bytes[sh];
                 tma_4d(eb + G.p2_meta_off[sh], &a.maps.m2[mi], 0, (int32_t)(u.r0 / 8), 0, cc, bar);
                 tma_4d(eb, &a.maps.w2[mi], 0, (int32_t)u.r0, 0, cc, bar);
-                if (a.expert_bias) {
+                if (cfg_expert_bias) {
                     const uint8_t* base = sh ? a.shared_block : pool_cell_base(a.pool, cell);
                     const Offsets3& off = sh ? a.shared : a.routed;
                     bulk_g2s(ring + (size_t)slot * G.slot_bytes + q * G.p2_expert_bytes[sh] + G.p2_ab_off[sh],
@@ -655,7 +662,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) decode_layer_kernel(const __
 #pragma unroll
             for (int j = 0; j < 8; ++j) v[j] = 0.f;
             if (valid) {
-                if (a.act_dtype == SHRIKE_DTYPE_FP32) {
+                if (cfg_act_dtype == SHRIKE_DTYPE_FP32) {
                     const float4 lo = __ldg((const float4*)a.x + 2 * blk), hi = __ldg((const float4*)a.x + 2 * blk + 1);
                     v[0] = lo.x; v[1] = lo.y; v[2] = lo.z; v[3] = lo.w; v[4] = hi.x; v[5] = hi.y; v[6] = hi.z; v[7] = hi.w;
                 } else {
@@ -663,7 +670,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) decode_layer_kernel(const __
                     const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
-                        if (a.act_dtype == SHRIKE_DTYPE_FP16) {
+                        if (cfg_act_dtype == SHRIKE_DTYPE_FP16) {
                             v[2 * j] = f16_bits_to_f32((uint16_t)(w[j] & 0xffffu));
                             v[2 * j + 1] = f16_bits_to_f32((uint16_t)(w[j] >> 16));
                         } else {
@@ -675,7 +682,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) decode_layer_kernel(const __
                 ((float4*)xf_sm)[2 * blk] = make_float4(v[0], v[1], v[2], v[3]);
                 ((float4*)xf_sm)[2 * blk + 1] = make_float4(v[4], v[5], v[6], v[7]);
             }
-            if (a.act_dtype != SHRIKE_DTYPE_FP16) {
+            if (cfg_act_dtype != SHRIKE_DTYPE_FP16) {
                 bool over = false;
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
@@ -756,8 +763,8 @@ __global__ void __launch_bounds__(kFusedThreads, 1) decode_layer_kernel(const __
             }
         } else {
             const uint32_t groups = D / 64;
-            acc = affine_row_dot((const uint8_t*)a.rw + (size_t)my_row * (D * a.rbits / 8), a.rscales + (size_t)my_row * groups,
-                                 a.rbiases + (size_t)my_row * groups, a.rbits, groups, lane, a.x, a.act_dtype, a.eff_scale);
+            acc = affine_row_dot((const uint8_t*)a.rw + (size_t)my_row * (D * cfg_rbits / 8), a.rscales + (size_t)my_row * groups,
+                                 a.rbiases + (size_t)my_row * groups, cfg_rbits, groups, lane, a.x, cfg_act_dtype, a.eff_scale);
         }
         acc = butterfly_sum(acc);
         if (lane == 0)
@@ -950,7 +957,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) decode_layer_kernel(const __
                     tot0 += o.x;
                     tot1 += o.y;
                 }
-                if (a.expert_bias && wi == 0) {
+                if (cfg_expert_bias && wi == 0) {
                     const uint16_t* ab = (const uint16_t*)(stage + G.p1_ab_off);
                     tot0 += bf16_bits_to_f32(ab[g]);
                     tot1 += bf16_bits_to_f32(ab[8 + g]);
@@ -977,7 +984,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) decode_layer_kernel(const __
             const float up = __shfl_down_sync(0xffffffffu, v, 8);
             uint16_t* stg = st.act_stage[gi];
             if (lane < 8) {
-                const float act = glu_call(v, up, a.activation);
+                const float act = PLAIN ? glu(v, up, SHRIKE_ACT_SILU) : glu_call(v, up, cfg_activation);
                 stg[perm_index(lane, BITS == 4)] = act_to_half_bits(act, a.status);
             }
             __syncwarp();
@@ -1066,7 +1073,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) decode_layer_kernel(const __
                     const float2* xs = asum_sm + (size_t)in * gmax2;
                     const float2 o = chunk_rows_cg<BITS, GROUP, META>(G.cg_p2[sh], G2, rowA, rowB, slab, s0p, b0p, s1p, b1p, bsm, xs, c, t);
                     float o0 = o.x, o1 = o.y;
-                    if (a.expert_bias && c == 0) {
+                    if (cfg_expert_bias && c == 0) {
                         const uint16_t* ab = (const uint16_t*)(eb + G.p2_ab_off[sh]);
                         o0 += bf16_bits_to_f32(ab[g]);
                         o1 += bf16_bits_to_f32(ab[g + 8]);
@@ -1086,7 +1093,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) decode_layer_kernel(const __
                 // residual's values before the warps meet
                 const bool fin = cw == m % kCW;
                 float hid = 0.f;
-                if (fin && lane < 16 && a.hidden) hid = load_act(a.hidden, (size_t)row0 + lane, a.act_dtype);
+                if (fin && lane < 16 && a.hidden) hid = load_act(a.hidden, (size_t)row0 + lane, cfg_act_dtype);
                 consumers_sync();
                 if (m == 0) FUSED_TS(21);
                 if (fin) {
@@ -1096,7 +1103,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) decode_layer_kernel(const __
                         for (uint32_t w = 0; w < kCW; ++w) ysum += st.red2[m & 1u][w][lane];
                         const size_t o = (size_t)row0 + lane;
                         store_act(a.y, o, a.y_dtype, ysum);
-                        if (a.hidden) store_act(a.hidden, o, a.act_dtype, hid + round_act(a.y_dtype, ysum));
+                        if (a.hidden) store_act(a.hidden, o, cfg_act_dtype, hid + round_act(a.y_dtype, ysum));
                     }
                     // every warp is past its reads of the tile's slots: they go back to the producer
                     if (lane < packs_eff) bar_arrive_n(&st.empty[st.units[u0 + lane].slot()], kGroupWarps);
@@ -1288,9 +1295,9 @@ size_t fused_acts_bytes(const shrike_moe_config& c) {
     return (size_t)2 * kMaxInst * std::max(c.f, c.has_shared ? c.shared_f : 0u) * 2;
 }
 
-template <int BITS, int GROUP, int META>
-static cudaError_t launch_fused_t(const shrike_moe* m, cudaStream_t st, const FusedArgs& a) {
-    auto k = decode_layer_kernel<BITS, GROUP, META>;
+template <int BITS, int GROUP, int META, bool PLAIN>
+static cudaError_t launch_fused_tp(const shrike_moe* m, cudaStream_t st, const FusedArgs& a) {
+    auto k = decode_layer_kernel<BITS, GROUP, META, PLAIN>;
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)a.g.smem_bytes);
     if (e != cudaSuccess) return e;
     cudaLaunchConfig_t cfg = {};
@@ -1318,6 +1325,12 @@ static cudaError_t launch_fused_t(const shrike_moe* m, cudaStream_t st, const Fu
     cfg.attrs = attr;
     cfg.numAttrs = n;
     return cudaLaunchKernelEx(&cfg, k, a);
+}
+
+template <int BITS, int GROUP, int META>
+static cudaError_t launch_fused_t(const shrike_moe* m, cudaStream_t st, const FusedArgs& a) {
+    const bool plain = a.act_dtype == SHRIKE_DTYPE_BF16 && a.activation == SHRIKE_ACT_SILU && !a.expert_bias && a.rbits == 0;
+    return plain ? launch_fused_tp<BITS, GROUP, META, true>(m, st, a) : launch_fused_tp<BITS, GROUP, META, false>(m, st, a);
 }
 
 cudaError_t launch_fused_layer(const shrike_moe* m, cudaStream_t st, const ExpertArgs& ea,
