@@ -529,7 +529,18 @@ __device__ __noinline__ float affine_row_dot(const uint8_t* row, const uint16_t*
 }
 __device__ __noinline__ float glu_call(float gate, float up, uint32_t activation) { return glu(gate, up, activation); }
 
-// PLAIN: the layer is bf16 rows in, fp32 router rows, SiLU, no additive expert biases (the flagship shapes): those
+// What the selection helpers read of the router, with the plain router's choices (softmax scores, no selection
+// bias, no per-expert scale) as constants.
+struct PlainRouterView {
+    uint32_t ne, top_k, round_f16;
+    static constexpr uint32_t sigmoid_scores = 0;
+    static constexpr const uint16_t* logit_bias = nullptr;
+    static constexpr const uint16_t* per_expert_scale = nullptr;
+    static constexpr float scaling = 1.0f;
+};
+
+// PLAIN: the layer is bf16 rows in, fp32 router rows with softmax scores and no bias or scale operands, SiLU, no
+// additive expert biases (the flagship shapes): those
 // choices are then constants of the instruction stream instead of branches in it. A kernel of this kind runs
 // every code region once per launch, so what it does not fetch it does not wait for.
 template <int BITS, int GROUP, int META, bool PLAIN>
@@ -738,7 +749,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) decode_layer_kernel(const __
         float acc;
         if (row_f32) {
             const uint32_t chunks = D / 4;
-            const uint16_t* es = row_is_gate ? nullptr : a.eff_scale;
+            const uint16_t* es = (PLAIN || row_is_gate) ? nullptr : a.eff_scale;
             if (!wait_bar(&st.rw_bar, 0)) report_status(a.status, kStatusWaitTimeout);
             const float4* wrow = (const float4*)(dsm + G.off_rw + (size_t)cw * D * 4);
             const float4* xf = (const float4*)(dsm + G.off_xraw);
@@ -804,7 +815,12 @@ __global__ void __launch_bounds__(kFusedThreads, 1) decode_layer_kernel(const __
             uint32_t id;
             float w;
             FUSED_TS(12);
-            select_ranked(st.logits, a, st, cw, lane, id, w);
+            if constexpr (PLAIN) {
+                const PlainRouterView view{a.ne, a.top_k, a.round_f16};
+                select_ranked(st.logits, view, st, cw, lane, id, w);
+            } else {
+                select_ranked(st.logits, a, st, cw, lane, id, w);
+            }
             FUSED_TS(13);
             if (cw == 0) {
                 uint32_t io = 1u;
@@ -1329,7 +1345,8 @@ static cudaError_t launch_fused_tp(const shrike_moe* m, cudaStream_t st, const F
 
 template <int BITS, int GROUP, int META>
 static cudaError_t launch_fused_t(const shrike_moe* m, cudaStream_t st, const FusedArgs& a) {
-    const bool plain = a.act_dtype == SHRIKE_DTYPE_BF16 && a.activation == SHRIKE_ACT_SILU && !a.expert_bias && a.rbits == 0;
+    const bool plain = a.act_dtype == SHRIKE_DTYPE_BF16 && a.activation == SHRIKE_ACT_SILU && !a.expert_bias && a.rbits == 0 &&
+                       !a.sigmoid_scores && !a.logit_bias && !a.per_expert_scale && !a.eff_scale;
     return plain ? launch_fused_tp<BITS, GROUP, META, true>(m, st, a) : launch_fused_tp<BITS, GROUP, META, false>(m, st, a);
 }
 
