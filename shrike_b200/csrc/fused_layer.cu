@@ -86,6 +86,8 @@ struct FusedGeom {
     uint32_t acts_stride;                // halves per instance in the activation buffers
     uint32_t cg_p1, cg_p2[2];            // groups per chunk (1, 2 or 4)
     uint32_t router_rows_per_block;
+    // ceil(2^24 / c) for the divisors the block plan uses (numerators below 4096): a multiply and a shift
+    uint32_t rcp_blocks, rcp_upe, rcp_slots, rcp_epp, rcp_bps, rcp_gmax2;
 };
 
 // Tensor maps of one expert block layout: entries 0..7 the pool's chunks, entry 8 the shared expert's block.
@@ -129,6 +131,8 @@ struct FusedArgs {
 #ifdef SHRIKE_TRACE
     uint64_t* trace;   // debug builds: 16 timestamps per block
 #endif
+    uint32_t rcp_cpc;               // ceil(2^32 / cells_per_chunk): cell / cells_per_chunk = mulhi(cell, rcp_cpc)
+    uint32_t n_pool_chunks;
     FusedGeom g;
     FusedMaps maps;
 };
@@ -243,8 +247,12 @@ __device__ __forceinline__ bool has_sentinel(uint4 v) {
 // What a block does, in closed form (every lane can work out any unit on its own): phase-1 units blk, blk +
 // n_blk, ... of the sequence [shared expert's units | first pick's | second pick's ...], then the packs of the
 // output tiles n_blk - 1 - blk, + n_blk, ... (blocks that are light in one phase are heavy in the other).
+// n / c for n < 4096 and c < 4096, with rcp = ceil(2^24 / c)
+__device__ __forceinline__ uint32_t div_rcp(uint32_t n, uint32_t rcp) { return (uint32_t)(((unsigned long long)n * rcp) >> 24); }
+
 struct BlockPlan {
     uint32_t n_blk, blk, su, upe, has_shared, tiles, epp, n_slots;
+    uint32_t rcp_blocks, rcp_upe, rcp_slots, rcp_epp;
     uint32_t n_routed, n1, n_tiles, packs, packs_eff, n_units;
 
     __device__ void init(const FusedArgs& a) {
@@ -255,16 +263,17 @@ struct BlockPlan {
         tiles = a.d / 16;
         epp = a.g.experts_per_pack;
         n_slots = a.g.n_slots;
+        rcp_blocks = a.g.rcp_blocks; rcp_upe = a.g.rcp_upe; rcp_slots = a.g.rcp_slots; rcp_epp = a.g.rcp_epp;
         const uint32_t t0 = n_blk - 1u - blk;
-        n_tiles = t0 < tiles ? (tiles - t0 + n_blk - 1u) / n_blk : 0u;
+        n_tiles = t0 < tiles ? div_rcp(tiles - t0 + n_blk - 1u, rcp_blocks) : 0u;
     }
     // phase-1 units of the shared expert: they do not depend on the routing
-    __device__ uint32_t shared_units() const { return blk < su ? (su - blk + n_blk - 1u) / n_blk : 0u; }
+    __device__ uint32_t shared_units() const { return blk < su ? div_rcp(su - blk + n_blk - 1u, rcp_blocks) : 0u; }
     __device__ void route(uint32_t routed) {
         n_routed = routed;
         const uint32_t total1 = su + n_routed * upe;
-        n1 = blk < total1 ? (total1 - blk + n_blk - 1u) / n_blk : 0u;
-        packs = has_shared + (n_routed + epp - 1u) / epp;
+        n1 = blk < total1 ? div_rcp(total1 - blk + n_blk - 1u, rcp_blocks) : 0u;
+        packs = has_shared + div_rcp(n_routed + epp - 1u, rcp_epp);
         packs_eff = packs ? packs : 1u;
         n_units = n1 + n_tiles * packs_eff;
     }
@@ -275,11 +284,12 @@ struct BlockPlan {
             u.bits = 0u | 2u | (1u << 8);
             u.r0 = idx * 8u;
         } else {
-            const uint32_t k = idx - su, e = k / upe;
+            const uint32_t k = idx - su, e = div_rcp(k, rcp_upe);
             u.bits = ((has_shared + e) << 4) | (1u << 8);
             u.r0 = (k - e * upe) * 8u;
         }
-        u.bits |= ((i % n_slots) << 20) | (((i / n_slots) & 1u) << 25);
+        const uint32_t round = div_rcp(i, rcp_slots);
+        u.bits |= ((i - round * n_slots) << 20) | ((round & 1u) << 25);
         return u;
     }
     __device__ UnitRec unit(uint32_t i) const {
@@ -287,7 +297,8 @@ struct BlockPlan {
         const uint32_t j = i - n1, m = j / packs_eff, p = j - m * packs_eff;
         UnitRec u;
         u.r0 = (n_blk - 1u - blk + m * n_blk) * 16u;
-        u.bits = 1u | ((i % n_slots) << 20) | (((i / n_slots) & 1u) << 25);
+        const uint32_t round = div_rcp(i, rcp_slots);
+        u.bits = 1u | ((i - round * n_slots) << 20) | ((round & 1u) << 25);
         if (packs == 0u) return u;   // count 0
         if (has_shared && p == 0u) {
             u.bits |= 2u | (1u << 8);
@@ -580,7 +591,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) decode_layer_kernel(const __
     if (tid <= 32) fence_mbar_init();
     if (tid == 0) st.failed = 0;
     {   // the descriptors this block may use: the shared expert's, and every pool chunk's
-        const uint32_t n_chunks = (a.pool.cells + a.pool.cells_per_chunk - 1) / a.pool.cells_per_chunk;
+        const uint32_t n_chunks = a.n_pool_chunks;
         const uint32_t which = tid >> 2, kind = tid & 3;
         const bool wanted = which < n_chunks || (which == SHRIKE_MAX_POOL_CHUNKS && a.shared_block);
         if (tid < 4 * (SHRIKE_MAX_POOL_CHUNKS + 1) && wanted)
@@ -618,8 +629,9 @@ __global__ void __launch_bounds__(kFusedThreads, 1) decode_layer_kernel(const __
         const uint32_t sh = u.sh();
         if (u.kind() == 0) {
             const uint32_t cell = sh ? 0u : st.route.cell[u.inst()];
-            const uint32_t mi = sh ? SHRIKE_MAX_POOL_CHUNKS : cell / a.pool.cells_per_chunk;
-            const int32_t cc = sh ? 0 : (int32_t)(cell % a.pool.cells_per_chunk);
+            const uint32_t ch = __umulhi(cell, a.rcp_cpc);   // cell / cells_per_chunk
+            const uint32_t mi = sh ? SHRIKE_MAX_POOL_CHUNKS : ch;
+            const int32_t cc = sh ? 0 : (int32_t)(cell - ch * a.pool.cells_per_chunk);
             mbar_expect_tx(bar, 16 * rb1 + 64 * GD + (cfg_expert_bias ? 32u : 0u));
             tma_5d(stage + G.p1_meta_off, &a.maps.m1[mi], 0, (int32_t)(u.r0 / 8), 0, 0, cc, bar);   // the small one first
             tma_5d(stage, &a.maps.w1[mi], 0, (int32_t)u.r0, 0, 0, cc, bar);
@@ -635,8 +647,9 @@ __global__ void __launch_bounds__(kFusedThreads, 1) decode_layer_kernel(const __
             mbar_expect_tx(bar, count * (16 * rb2 + 64 * G2 + (cfg_expert_bias ? 32u : 0u)));   // count 0: the arrival alone
             for (uint32_t q = 0; q < count; ++q) {
                 const uint32_t cell = sh ? 0u : st.route.cell[u.inst() + q];
-                const uint32_t mi = sh ? SHRIKE_MAX_POOL_CHUNKS : cell / a.pool.cells_per_chunk;
-                const int32_t cc = sh ? 0 : (int32_t)(cell % a.pool.cells_per_chunk);
+                const uint32_t ch = __umulhi(cell, a.rcp_cpc);   // cell / cells_per_chunk
+                const uint32_t mi = sh ? SHRIKE_MAX_POOL_CHUNKS : ch;
+                const int32_t cc = sh ? 0 : (int32_t)(cell - ch * a.pool.cells_per_chunk);
                 const uint32_t eb = stage + q * G.p2_expert_bytes[sh];
                 tma_4d(eb + G.p2_meta_off[sh], &a.maps.m2[mi], 0, (int32_t)(u.r0 / 8), 0, cc, bar);
                 tma_4d(eb, &a.maps.w2[mi], 0, (int32_t)u.r0, 0, cc, bar);
@@ -1027,7 +1040,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) decode_layer_kernel(const __
 #pragma unroll
                     for (uint32_t k = 0; k < kMaxPer; ++k) {
                         const uint32_t i = i0 + k * kCW * 32;
-                        const uint32_t in = i / bps, b = i - in * bps;
+                        const uint32_t in = div_rcp(i, G.rcp_bps), b = i - in * bps;
                         const uint32_t F = (has_shared && in == 0) ? a.f_shared : a.f;
                         need[k] = i < total && b < F / 8;
                         v[k] = make_uint4(0xffffffffu, 0, 0, 0);
@@ -1053,7 +1066,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) decode_layer_kernel(const __
                 }
                 consumers_sync();
                 for (uint32_t i = ctid; i < n_inst * gmax2; i += kCW * 32) {
-                    const uint32_t in = i / gmax2, grp = i - in * gmax2;
+                    const uint32_t in = div_rcp(i, G.rcp_gmax2), grp = i - in * gmax2;
                     const uint32_t F = (has_shared && in == 0) ? a.f_shared : a.f;
                     if (grp < F / GROUP) asum_sm[i] = group_sums<BITS, GROUP>(acts_sm + (size_t)in * G.acts_stride, grp);
                 }
@@ -1069,7 +1082,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) decode_layer_kernel(const __
                     if (it < cpe_s) {
                         sh = 1u; in = 0u; c = it; p = 0u; q = 0u;
                     } else {
-                        const uint32_t k = it - cpe_s, j = k / cpe_r, pj = j / plan.epp;
+                        const uint32_t k = it - cpe_s, j = k / cpe_r, pj = div_rcp(j, plan.rcp_epp);
                         sh = 0u; in = has_shared + j; c = k - j * cpe_r; p = has_shared + pj; q = j - pj * plan.epp;
                     }
                     const UnitRec u = st.units[u0 + p];
@@ -1193,6 +1206,14 @@ bool fused_geometry(const shrike_moe_config& c, int sm_count, int max_smem_optin
     const uint32_t rows = c.num_experts + (c.shared_gated ? 1u : 0u);
     g.router_rows_per_block = (rows + (uint32_t)sm_count - 1) / (uint32_t)sm_count;
     if (g.router_rows_per_block > kMaxRouterRowsPerBlock) return false;
+    auto rcp = [](uint32_t c) { return (uint32_t)(((1ull << 24) + c - 1) / c); };
+    if (c.f / 8 >= 4096 || (c.has_shared ? c.shared_f / 8 : 0u) + c.top_k * (c.f / 8) + (uint32_t)sm_count >= 4096 ||
+        c.d / 16 + (uint32_t)sm_count >= 4096)
+        return false;   // the plan's divisions are a multiply by these reciprocals: numerators and divisors below 4096
+    g.rcp_blocks = rcp((uint32_t)sm_count); g.rcp_upe = rcp(c.f / 8); g.rcp_slots = rcp(g.n_slots);
+    g.rcp_epp = rcp(g.experts_per_pack);
+    g.rcp_bps = rcp(g.acts_stride / 8); g.rcp_gmax2 = rcp(g.acts_stride / c.group_size);
+    if (n_inst * (g.acts_stride / 8) >= 4096) return false;
     // the block's unit table and its per-tile sums, at the most work a block can get
     const uint32_t n_blk = (uint32_t)sm_count;
     const uint32_t units1 = ((c.has_shared ? c.shared_f / 8 : 0u) + c.top_k * (c.f / 8) + n_blk - 1) / n_blk;
@@ -1361,6 +1382,12 @@ cudaError_t launch_fused_layer(const shrike_moe* m, cudaStream_t st, const Exper
     memset(&a, 0, sizeof a);
     a.maps = *maps;
     a.pool = ea.pool; a.routed = ea.routed; a.shared = ea.shared; a.shared_block = ea.shared_block;
+    {   // cell -> (chunk, cell in chunk) by a multiply: exact while cells * cells_per_chunk < 2^32
+        const uint64_t cpc = ea.pool.cells_per_chunk ? ea.pool.cells_per_chunk : 1;
+        if (cpc < 2 || (uint64_t)ea.pool.cells * cpc >= (1ull << 32)) return cudaErrorNotSupported;   // (the three launches)
+        a.rcp_cpc = (uint32_t)(((1ull << 32) + cpc - 1) / cpc);
+        a.n_pool_chunks = (uint32_t)((ea.pool.cells + cpc - 1) / cpc);
+    }
     a.d = c.d; a.f = c.f; a.f_shared = c.has_shared ? c.shared_f : 0; a.top_k = c.top_k;
     a.activation = c.activation; a.expert_bias = c.expert_bias; a.act_dtype = c.act_dtype; a.y_dtype = c.y_dtype;
     a.rw = ops.weights; a.rscales = ops.scales; a.rbiases = ops.biases; a.rbits = c.router_weight_bits;
