@@ -87,7 +87,7 @@ struct FusedGeom {
     uint32_t cg_p1, cg_p2[2];            // groups per chunk (1, 2 or 4)
     uint32_t router_rows_per_block;
     // ceil(2^24 / c) for the divisors the block plan uses (numerators below 4096): a multiply and a shift
-    uint32_t rcp_blocks, rcp_upe, rcp_slots, rcp_epp, rcp_bps, rcp_gmax2;
+    uint32_t rcp_blocks, rcp_upe, rcp_slots, rcp_epp, rcp_bps, rcp_gmax2, rcp_cpe_r;
 };
 
 // Tensor maps of one expert block layout: entries 0..7 the pool's chunks, entry 8 the shared expert's block.
@@ -423,7 +423,9 @@ __device__ __forceinline__ float2 chunk_rows_cg(uint32_t cg, uint32_t groups, co
     return chunk_rows<BITS, GROUP, META, 1>(rowA, rowB, slab, s0p, b0p, s1p, b1p, bsm, xs, c, t);
 }
 // chunks of a row of `groups` groups at width cg
-__device__ __forceinline__ uint32_t chunks_of(uint32_t groups, uint32_t cg) { return cg == 4 ? (groups + 3) / 4 : groups / cg; }
+__device__ __forceinline__ uint32_t chunks_of(uint32_t groups, uint32_t cg) {
+    return cg == 4 ? (groups + 3) >> 2 : cg == 2 ? groups >> 1 : groups;
+}
 
 // {sum x, sum offset * x} of group `grp` of an fp16 operand row in shared memory.
 template <int BITS, int GROUP>
@@ -1082,7 +1084,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) decode_layer_kernel(const __
                     if (it < cpe_s) {
                         sh = 1u; in = 0u; c = it; p = 0u; q = 0u;
                     } else {
-                        const uint32_t k = it - cpe_s, j = k / cpe_r, pj = div_rcp(j, plan.rcp_epp);
+                        const uint32_t k = it - cpe_s, j = div_rcp(k, G.rcp_cpe_r), pj = div_rcp(j, plan.rcp_epp);
                         sh = 0u; in = has_shared + j; c = k - j * cpe_r; p = has_shared + pj; q = j - pj * plan.epp;
                     }
                     const UnitRec u = st.units[u0 + p];
@@ -1212,6 +1214,7 @@ bool fused_geometry(const shrike_moe_config& c, int sm_count, int max_smem_optin
         return false;   // the plan's divisions are a multiply by these reciprocals: numerators and divisors below 4096
     g.rcp_blocks = rcp((uint32_t)sm_count); g.rcp_upe = rcp(c.f / 8); g.rcp_slots = rcp(g.n_slots);
     g.rcp_epp = rcp(g.experts_per_pack);
+    g.rcp_cpe_r = rcp(g.cg_p2[0] == 4 ? (c.f / c.group_size + 3) / 4 : c.f / c.group_size / g.cg_p2[0]);
     g.rcp_bps = rcp(g.acts_stride / 8); g.rcp_gmax2 = rcp(g.acts_stride / c.group_size);
     if (n_inst * (g.acts_stride / 8) >= 4096) return false;
     // the block's unit table and its per-tile sums, at the most work a block can get
