@@ -197,15 +197,19 @@ int encode_prefill(shrike_moe* m, void* stream, const shrike_pool* pool,
     // every expert on the 8-row warp-MMA tiles (the decode kernels); SHRIKE_PREFILL_PATH=mma in the
     // environment of shrike_moe_create forces them for a handle (a test switch).
     const bool warp_mma = m->force_warp_mma || !umma_supported(m->cfg);
+    // fp32 rows out and no residual to add: the down epilogue adds straight into y (zeroed by the plan; x is read
+    // after that, so not when y is x) and no pass over the rows follows
+    const bool direct = m->cfg.y_dtype == SHRIKE_DTYPE_FP32 && !hidden && y != x;
+    if (direct) a.yacc = (float*)y;
     CU(launch_prefill_plan(m, st, topk_indices, resolved_slots, x, query_count, m->cfg.has_shared != 0,
-                           pool->view.cells, warp_mma, io_status));
+                           pool->view.cells, warp_mma, io_status, nullptr, nullptr, direct ? (float*)y : nullptr));
     if (warp_mma) {
         CU(launch_phase1(m, st, a, mi, false));
         CU(launch_phase2_accumulate(m, st, a, mi));
     } else {
         CU(launch_umma_prefill(m, st, a, query_count, pool->view.cells));
     }
-    CU(launch_prefill_combine(m, st, query_count, y, hidden));
+    if (!direct) CU(launch_prefill_combine(m, st, query_count, y, hidden));
     return SHRIKE_OK;
 }
 

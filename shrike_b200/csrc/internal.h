@@ -186,7 +186,8 @@ cudaError_t launch_phase2_accumulate(const shrike_moe* m, cudaStream_t st, const
 cudaError_t launch_prefill_plan(const shrike_moe* m, cudaStream_t st, const uint32_t* ids,
                                 const uint32_t* slots, const void* x, uint32_t T, bool with_shared,
                                 uint32_t pool_cells, bool warp_mma_instances, const uint32_t* io_status,
-                                const uint32_t* row_map = nullptr, const uint32_t* n_rows = nullptr);
+                                const uint32_t* row_map = nullptr, const uint32_t* n_rows = nullptr,
+                                float* accumulator = nullptr);
 cudaError_t launch_prefill_combine(const shrike_moe* m, cudaStream_t st, uint32_t T, void* y, void* hidden);
 }  // namespace shrike
 

@@ -109,12 +109,13 @@ prefill_combine_kernel(const float* __restrict__ yacc, uint32_t n, uint32_t act_
 cudaError_t launch_prefill_plan(const shrike_moe* m, cudaStream_t st, const uint32_t* ids,
                                 const uint32_t* slots, const void* x, uint32_t T, bool with_shared,
                                 uint32_t pool_cells, bool warp_mma_instances, const uint32_t* io_status,
-                                const uint32_t* row_map, const uint32_t* n_rows) {
+                                const uint32_t* row_map, const uint32_t* n_rows, float* accumulator) {
     const shrike_moe_config& c = m->cfg;
     const Workspace& ws = m->ws;
     cudaError_t e = cudaMemsetAsync(ws.slot_of_expert, 0xff, c.num_experts * 4, st);
     if (e != cudaSuccess) return e;
-    e = cudaMemsetAsync(ws.yacc, 0, (size_t)T * c.d * 4, st);
+    // the rows the down epilogue adds into: the workspace's, or the caller's fp32 output itself
+    e = cudaMemsetAsync(accumulator ? accumulator : ws.yacc, 0, (size_t)T * c.d * 4, st);
     if (e != cudaSuccess) return e;
     const uint32_t n_pairs = T * c.top_k;
     prefill_slot_of_expert_kernel<<<(n_pairs + 255) / 256, 256, 0, st>>>(ids, slots, n_pairs, c.num_experts,
