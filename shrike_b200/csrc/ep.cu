@@ -294,13 +294,15 @@ __global__ void __launch_bounds__(256)
 ep_return_kernel(const float* __restrict__ yacc, const uint32_t* __restrict__ row_map,
                  const uint32_t* __restrict__ n_rows, uint32_t rank, uint32_t cap, uint32_t d, uint32_t y_dtype,
                  EpPeers peers, EpLayout lay) {
-    const uint32_t t = blockIdx.y;
-    if (t >= *n_rows) return;
+    // grid (column blocks, a fixed number of row walkers): the number of received rows is only known on the device
     const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= d) return;
-    const uint32_t g_row = row_map[t], s = g_row / cap, row = g_row - s * cap;
-    void* dst = peers.base[s] + lay.off_ret;
-    store_act(dst, ((size_t)rank * cap + row) * d + i, y_dtype, yacc[(size_t)t * d + i]);
+    const uint32_t n = *n_rows;
+    for (uint32_t t = blockIdx.y; t < n; t += gridDim.y) {
+        const uint32_t g_row = row_map[t], s = g_row / cap, row = g_row - s * cap;
+        void* dst = peers.base[s] + lay.off_ret;
+        store_act(dst, ((size_t)rank * cap + row) * d + i, y_dtype, yacc[(size_t)t * d + i]);
+    }
 }
 
 EpLayout ep_layout(const shrike_moe_config& c, uint32_t world, uint32_t cap) {
@@ -359,7 +361,7 @@ cudaError_t launch_ep_return(const shrike_moe* routed, cudaStream_t st, const ui
                              const EpLayout& lay, uint32_t epoch) {
     const shrike_moe_config& c = routed->cfg;
     const EpPeers peers = make_peers(peer_base, world);
-    ep_return_kernel<<<dim3((c.d + 255) / 256, t_max), 256, 0, st>>>(routed->ws.yacc, row_map, n_rows, rank, cap, c.d,
+    ep_return_kernel<<<dim3((c.d + 255) / 256, t_max < 1024u ? t_max : 1024u), 256, 0, st>>>(routed->ws.yacc, row_map, n_rows, rank, cap, c.d,
                                                                      c.y_dtype, peers, lay);
     ep_signal_kernel<<<1, SHRIKE_EP_MAX_WORLD, 0, st>>>(peers, lay, world, rank, epoch, 1, nullptr);
     return cudaGetLastError();
