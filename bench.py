@@ -355,6 +355,8 @@ def decode_line(args, rank: int, world: int, local_rank: int):
                 "l2": f"inputs larger than L2: every step streams {layer_bytes * L / 1e6:.0f} MB of distinct expert "
                       "blocks (L2 126 MB)",
                 "stream": "layer l's input = seeded N(0,1) row l (standing for attention + norm) + y of layer l-1",
+                "launch": "one stream per GPU, SHRIKE_SINGLE_STREAM=1 (no cooperative launch; the library's default is cooperative)"
+                          if os.environ.get("SHRIKE_SINGLE_STREAM") else "cooperative",
                 "pool_gb": round(wl.pool.cells * wl.pool.cell_stride / 1e9, 2),
             },
             "roofline": {"bound": "hbm", "kernel": kernel, "achieved": gbs, "peak": hbm, "unit": "GB/s",
@@ -593,6 +595,9 @@ def ep_block(args, rank: int, world: int, local_rank: int) -> dict:
 
 def main():
     args = parse_args()
+    # The benchmark drives one stream per GPU: the one-launch decode layer may give up its cooperative launch
+    # (read once, when a handle is created), which lets a layer's prologue overlap the previous layer's tail.
+    os.environ.setdefault("SHRIKE_SINGLE_STREAM", "1")
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

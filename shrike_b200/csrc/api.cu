@@ -261,7 +261,7 @@ int shrike_moe_create(const shrike_moe_config* config, int device, shrike_moe** 
     cudaDeviceGetAttribute(&m->sm_count, cudaDevAttrMultiProcessorCount, device);
     // switches for tests and diagnostics, read once here and never on the per-layer path
     m->no_pdl = getenv("SHRIKE_NO_PDL") != nullptr;
-    m->cooperative = getenv("SHRIKE_COOPERATIVE") != nullptr;
+    m->single_stream = getenv("SHRIKE_SINGLE_STREAM") != nullptr;
     const char* path = getenv("SHRIKE_PREFILL_PATH");
     m->force_warp_mma = path && strcmp(path, "mma") == 0;
     const shrike_moe_config& c = m->cfg;

@@ -1347,12 +1347,15 @@ static cudaError_t launch_fused_tp(const shrike_moe* m, cudaStream_t st, const F
     cfg.stream = st;
     cudaLaunchAttribute attr[2];
     unsigned n = 0;
-    // The blocks wait on each other's results, so all of them must be resident. The grid is one block per SM
-    // and a block needs most of an SM, so they are, as soon as the previous kernel of the stream has left --
-    // unless another stream's kernel holds SMs meanwhile: then the (bounded) waits give up and the call reports
-    // a timeout. A cooperative launch rules that out, but it also keeps every block from starting until the
-    // previous kernel has ended, prologue and launch latency exposed: it is the opt-in.
-    if (m->cooperative || m->no_pdl) {
+    // The blocks wait on each other's results, so all of them must be resident together. A cooperative launch
+    // guarantees it, whatever else runs on the GPU: it is the default. It also keeps every block from starting
+    // until the previous kernel has left, prologue and launch latency exposed (0.5 us per layer). A host that
+    // runs one stream on the GPU does not need the guarantee -- the grid is one block per SM and a block needs
+    // most of an SM, so the blocks are together as soon as the stream's previous kernel has ended -- and says so
+    // with SHRIKE_SINGLE_STREAM at handle creation. (Two such layers on two streams without the guarantee could
+    // each hold half of the SMs and wait for the other half: the bounded waits would end that with a timeout
+    // status, not a hang, but the call would have failed.)
+    if (!m->single_stream || m->no_pdl) {
         attr[n].id = cudaLaunchAttributeCooperative;
         attr[n].val.cooperative = 1;
         ++n;

@@ -118,9 +118,8 @@ struct shrike_moe {
     uint32_t residency_layers = 0;
     int sm_count = 148;
     bool no_pdl = false;          // SHRIKE_NO_PDL was set when the handle was created (diagnostics)
-    bool cooperative = false;     // SHRIKE_COOPERATIVE was set when the handle was created: the one-launch layer asks for a
-                                  // cooperative launch (all blocks resident before any starts) and gives up the overlap
-                                  // of its prologue with the previous kernel's tail
+    bool single_stream = false;   // SHRIKE_SINGLE_STREAM was set when the handle was created: nothing else runs on the GPU
+                                  // beside this handle's stream, so the one-launch layer need not be a cooperative launch
     bool force_warp_mma = false;  // SHRIKE_PREFILL_PATH=mma was set when the handle was created (test switch)
 #ifdef SHRIKE_TRACE
     uint64_t* trace = nullptr;

@@ -659,3 +659,21 @@ def test_affine_rows_to_fp32(cuda_device, bits, group, meta):
     assert (out.cpu().numpy() == ref).all()
     assert lib.shrike_dequant_affine_rows(None, pk.data_ptr(), sc.data_ptr(), bi.data_ptr(), 5, group, meta, rows, cols,
                                           out.data_ptr()) == capi.EINVAL
+
+
+def test_one_launch_layer_without_the_cooperative_launch(cuda_device, monkeypatch):
+    """SHRIKE_SINGLE_STREAM (read when the handle is created) drops the cooperative launch of the one-row layer:
+    same ids, weights and rows as the default, over a few calls in a row on one stream."""
+    x = inputs(1, 256, seed=77)
+    h0 = inputs(1, 256, seed=78)
+    base = Layer(small_config(d=256))
+    ref = base.forward(x, hidden=h0, fused=True)
+    base.close()
+    monkeypatch.setenv("SHRIKE_SINGLE_STREAM", "1")
+    layer = Layer(small_config(d=256))
+    for _ in range(3):
+        got = layer.forward(x, hidden=h0, fused=True)
+        assert (got[1] == ref[1]).all() and (got[2] == ref[2]).all()
+        assert (got[0] == ref[0]).all() and (got[3] == ref[3]).all()
+    check_layer(layer, x, fused=True)
+    layer.close()
