@@ -677,3 +677,34 @@ def test_one_launch_layer_without_the_cooperative_launch(cuda_device, monkeypatc
         assert (got[0] == ref[0]).all() and (got[3] == ref[3]).all()
     check_layer(layer, x, fused=True)
     layer.close()
+
+
+def test_two_streams_run_the_one_launch_layer_side_by_side(cuda_device):
+    """Two handles on two streams, forty one-row layer calls each, issued alternately: the cooperative launch
+    (the default) keeps each call's blocks together, so both streams give what a stream alone gives and no
+    wait runs out."""
+    import torch
+    from gpu_harness import to_act_tensor
+    layers = [Layer(small_config(d=256), seed=300 + i) for i in range(2)]
+    xs = [inputs(1, 256, seed=80 + i) for i in range(2)]
+    ref = [L.forward(x, fused=True) for L, x in zip(layers, xs)]
+    dev = layers[0].device
+    streams = [torch.cuda.Stream(device=dev) for _ in range(2)]
+    bufs = []
+    for L, x in zip(layers, xs):
+        cfg = L.cfg
+        bufs.append((to_act_tensor(x, cfg.act_dtype, dev), torch.empty((1, 256), dtype=cfg.torch_y_dtype, device=dev),
+                     torch.empty((1, cfg.top_k), dtype=torch.int32, device=dev),
+                     torch.empty((1, cfg.top_k), dtype=torch.float32, device=dev)))
+    torch.cuda.synchronize()
+    for _ in range(40):
+        for L, s, (xd, y, ids, w) in zip(layers, streams, bufs):
+            with torch.cuda.stream(s):
+                L.moe.encode_decode_layer(L.pool, L.offsets, L.layer, L.router_ops, xd, y, None, L.shared, ids, w, None)
+    torch.cuda.synchronize()
+    for L, s, (xd, y, ids, w), r in zip(layers, streams, bufs, ref):
+        with torch.cuda.stream(s):
+            L.moe.status()
+        assert (ids.cpu().numpy().astype(np.uint32) == r[1]).all() and (w.cpu().numpy() == r[2]).all()
+        assert (y.float().cpu().numpy() == r[0]).all()
+        L.close()
