@@ -397,14 +397,28 @@ __global__ void __launch_bounds__(kRouterWarps * 32) route_fused_kernel(const Ro
     if (!s_last) return;
     __threadfence();
 
-    for (uint32_t row = 0; row < a.T; ++row) {
+    if (a.T == 1) {
+        // one row: the whole block ranks it (no serial rounds)
         uint32_t id;
         float w;
-        select_row_block(a.logits + (size_t)row * a.ne, a, sel, id, w);
+        select_row_block(a.logits, a, sel, id, w);
         if (warp == 0 && lane < a.top_k) {
-            a.ids[(size_t)row * a.top_k + lane] = id;
-            a.weights[(size_t)row * a.top_k + lane] = w;
-            ids_sm[row * a.top_k + lane] = id;
+            a.ids[lane] = id;
+            a.weights[lane] = w;
+            ids_sm[lane] = id;
+        }
+    } else {
+        // several rows: a warp per row, the rows side by side (the same picks and weights: both forms build the
+        // list of the reference's insertion scan)
+        for (uint32_t row = warp; row < a.T; row += kRouterWarps) {
+            uint32_t id;
+            float w;
+            select_row<true>(a.logits + (size_t)row * a.ne, a, lane, id, w);
+            if (lane < a.top_k) {
+                a.ids[(size_t)row * a.top_k + lane] = id;
+                a.weights[(size_t)row * a.top_k + lane] = w;
+                ids_sm[row * a.top_k + lane] = id;
+            }
         }
     }
     __syncthreads();
