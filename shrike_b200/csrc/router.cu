@@ -361,7 +361,7 @@ __global__ void __launch_bounds__(128) router_select_kernel(const RouterArgs a) 
 // finishes last then selects, looks the experts up in the residency table and
 // builds the work lists -- no wait on another block anywhere. Every block also
 // converts its slice of the activation rows to the fp16 operand layout.
-// grid (ceil((ne + has_gate)/4), 1).
+// grid (ceil((ne + has_gate)/4), 1..4 token groups).
 __global__ void __launch_bounds__(kRouterWarps * 32) route_fused_kernel(const RouterArgs a) {
     __shared__ PlanSmem sm;
     __shared__ uint32_t ids_sm[kPlanMaxPairs];
@@ -379,7 +379,8 @@ __global__ void __launch_bounds__(kRouterWarps * 32) route_fused_kernel(const Ro
     {
         const uint32_t items = a.T * (a.d / 8);
         const size_t esz = a.dt == SHRIKE_DTYPE_FP32 ? 4 : 2;
-        for (uint32_t i0 = blockIdx.x * blockDim.x; i0 < items; i0 += gridDim.x * blockDim.x)
+        const uint32_t n_blocks = gridDim.x * gridDim.y, block = blockIdx.y * gridDim.x + blockIdx.x;
+        for (uint32_t i0 = block * blockDim.x; i0 < items; i0 += n_blocks * blockDim.x)
             xprep_item(a.hidden, (size_t)a.stride * esz, a.d, a.group, a.dt, a.int4 != 0, i0 + tid, i0 + tid < items,
                        a.xh, a.xsum, a.status);
     }
@@ -389,7 +390,7 @@ __global__ void __launch_bounds__(kRouterWarps * 32) route_fused_kernel(const Ro
     __syncthreads();
     if (tid == 0) {
         const uint32_t ticket = atomicAdd(a.done_counter, 1u);
-        s_last = ticket == gridDim.x - 1 ? 1u : 0u;
+        s_last = ticket == gridDim.x * gridDim.y - 1 ? 1u : 0u;
         if (s_last) *a.done_counter = 0;
         s_miss = 0;
     }
@@ -592,7 +593,10 @@ cudaError_t launch_route_fused(const shrike_moe* m, cudaStream_t st, const shrik
     a.xh = m->ws.xh; a.done_counter = m->ws.done_counter; a.status = m->ws.status; a.max_inst = max_instances(m->cfg, T);
     const uint32_t rows = a.ne + (a.gate_row ? 1u : 0u);
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((rows + kRouterWarps - 1) / kRouterWarps);
+    // several rows: up to four blocks share an expert row's tokens (65 blocks would leave half of the SMs idle)
+    const uint32_t gy = T < 4 ? (T ? T : 1u) : 4u;
+    a.tokens_per_block = (T + gy - 1) / gy;
+    cfg.gridDim = dim3((rows + kRouterWarps - 1) / kRouterWarps, gy);
     cfg.blockDim = dim3(kRouterWarps * 32);
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
