@@ -18,7 +18,8 @@
 
 namespace shrike {
 
-constexpr int kRouterWarps = 4;       // rows per block, as router_gemv_r4
+constexpr int kRouterWarps = 8;       // expert rows per block (router_gemv_r4 has four); the block that finishes last
+                                      // selects with as many warps
 
 struct RouterArgs {
     const void* w;                 // fp32 rows, or packed affine rows
