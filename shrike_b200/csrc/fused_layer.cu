@@ -910,7 +910,6 @@ __global__ void __launch_bounds__(kFusedThreads, 1) decode_layer_kernel(const __
     FUSED_TS(19);
     __syncthreads();
     FUSED_TS(5);   // the instance list is known
-    const uint32_t n_inst = st.route.n_inst;
     plan.route(st.route.n_routed);
     const uint32_t n_units = plan.n_units, packs_eff = plan.packs_eff;
 
@@ -1030,51 +1029,8 @@ __global__ void __launch_bounds__(kFusedThreads, 1) decode_layer_kernel(const __
             const uint32_t cpe_s = has_shared ? chunks_of(a.f_shared / GROUP, G.cg_p2[1]) : 0u;   // chunks of the shared expert
             const uint32_t cpe_r = chunks_of(a.f / GROUP, G.cg_p2[0]);                            // chunks of a routed expert
             const uint32_t items = cpe_s + plan.n_routed * cpe_r;
-            // ---- all instances' activations: poll until published, stage, group sums. A thread's blocks are
-            // all requested before the first is examined. ----
-            {
-                constexpr uint32_t kMaxPer = 2;
-                const uint32_t bps = G.acts_stride / 8;          // 16-byte blocks per instance (padded)
-                const uint32_t total = n_inst * bps;
-                for (uint32_t i0 = ctid; i0 < total; i0 += kCW * 32 * kMaxPer) {
-                    uint4 v[kMaxPer];
-                    bool need[kMaxPer];
-#pragma unroll
-                    for (uint32_t k = 0; k < kMaxPer; ++k) {
-                        const uint32_t i = i0 + k * kCW * 32;
-                        const uint32_t in = div_rcp(i, G.rcp_bps), b = i - in * bps;
-                        const uint32_t F = (has_shared && in == 0) ? a.f_shared : a.f;
-                        need[k] = i < total && b < F / 8;
-                        v[k] = make_uint4(0xffffffffu, 0, 0, 0);
-                        if (need[k]) v[k] = ld_relaxed_v4(acts_mine + (size_t)i * 8);
-                    }
-#pragma unroll
-                    for (uint32_t k = 0; k < kMaxPer; ++k) {
-                        if (!need[k]) continue;
-                        const uint32_t i = i0 + k * kCW * 32;
-                        bool ok = !has_sentinel(v[k]);
-#pragma unroll 1
-                        for (uint32_t it = 0; !ok && it < (1u << 17); ++it) {
-                            __nanosleep(it > 32 ? 256 : 100);   // 148 blocks poll the same few lines
-                            v[k] = ld_relaxed_v4(acts_mine + (size_t)i * 8);
-                            ok = !has_sentinel(v[k]);
-                        }
-                        if (!ok) {
-                            report_status(a.status, kStatusWaitTimeout);
-                            v[k] = make_uint4(0, 0, 0, 0);
-                        }
-                        *(uint4*)(acts_sm + (size_t)i * 8) = v[k];
-                    }
-                }
-                consumers_sync();
-                for (uint32_t i = ctid; i < n_inst * gmax2; i += kCW * 32) {
-                    const uint32_t in = div_rcp(i, G.rcp_gmax2), grp = i - in * gmax2;
-                    const uint32_t F = (has_shared && in == 0) ? a.f_shared : a.f;
-                    if (grp < F / GROUP) asum_sm[i] = group_sums<BITS, GROUP>(acts_sm + (size_t)in * G.acts_stride, grp);
-                }
-                consumers_sync();
-            }
-            FUSED_TS(9);   // activations of every instance staged
+            // (each warp stages what its own items multiply -- see below -- so no warp waits for an instance it
+            // does not use, and nothing in this phase needs the whole block)
             for (uint32_t m = 0; m < plan.n_tiles; ++m) {
                 const uint32_t u0 = plan.n1 + m * packs_eff;   // the tile's first unit
                 const uint32_t row0 = (plan.n_blk - 1u - plan.blk + m * plan.n_blk) * 16u;
@@ -1087,10 +1043,55 @@ __global__ void __launch_bounds__(kFusedThreads, 1) decode_layer_kernel(const __
                         const uint32_t k = it - cpe_s, j = div_rcp(k, G.rcp_cpe_r), pj = div_rcp(j, plan.rcp_epp);
                         sh = 0u; in = has_shared + j; c = k - j * cpe_r; p = has_shared + pj; q = j - pj * plan.epp;
                     }
+                    const uint32_t F = sh ? a.f_shared : a.f, G2 = F / GROUP;
+                    if (m == 0) {
+                        // ---- the activations this item multiplies: its chunk of its instance's row, at most 32
+                        // 16-byte blocks, a lane each. Poll until published, stage, and -- with the lanes that
+                        // share a group -- the group's sums. (Later tiles of the block find them staged.) ----
+                        constexpr uint32_t kLanes = GROUP / 8;
+                        const uint32_t cgw = G.cg_p2[sh];
+                        const uint32_t grp0 = c * cgw, ngrp = min(cgw, G2 - grp0);
+                        const uint32_t blk0 = (in * G.acts_stride + grp0 * GROUP) / 8, nblk = ngrp * kLanes;
+                        uint4 v = make_uint4(0, 0, 0, 0);
+                        if (lane < nblk) {
+                            const uint16_t* src = acts_mine + (size_t)(blk0 + lane) * 8;
+                            v = ld_relaxed_v4(src);
+                            bool got = !has_sentinel(v);
+#pragma unroll 1
+                            for (uint32_t tries = 0; !got && tries < (1u << 17); ++tries) {
+                                __nanosleep(tries > 32 ? 256 : 100);   // 148 blocks poll the same few lines
+                                v = ld_relaxed_v4(src);
+                                got = !has_sentinel(v);
+                            }
+                            if (!got) {
+                                report_status(a.status, kStatusWaitTimeout);
+                                v = make_uint4(0, 0, 0, 0);
+                            }
+                            *(uint4*)(acts_sm + (size_t)(blk0 + lane) * 8) = v;
+                        }
+                        __syncwarp();
+                        // the block's halves in operand order: positions {0,1,4,5} hold the even elements (int4)
+                        const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
+                        float even = 0.f, odd = 0.f;
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const float lo = f16_bits_to_f32((uint16_t)(w4[j] & 0xffffu)), hi = f16_bits_to_f32((uint16_t)(w4[j] >> 16));
+                            if (BITS == 4 && (j & 1)) odd += lo + hi;
+                            else even += lo + hi;
+                        }
+#pragma unroll
+                        for (uint32_t o = 1; o < kLanes; o <<= 1) {
+                            even += __shfl_xor_sync(0xffffffffu, even, o);
+                            odd += __shfl_xor_sync(0xffffffffu, odd, o);
+                        }
+                        if (lane < nblk && (lane & (kLanes - 1)) == 0)
+                            asum_sm[in * gmax2 + grp0 + lane / kLanes] = make_float2(even + odd, Q::kOffEven * even + Q::kOffOdd * odd);
+                        __syncwarp();
+                        if (it == cw) FUSED_TS(9);   // this warp's first item's activations staged
+                    }
                     const UnitRec u = st.units[u0 + p];
                     if (!wait_bar(&st.full[u.slot()], u.parity())) report_status(a.status, kStatusWaitTimeout);
                     if (it == cw && m == 0) FUSED_TS(22);
-                    const uint32_t F = sh ? a.f_shared : a.f, G2 = F / GROUP;
                     const uint8_t* eb = ring + (size_t)u.slot() * G.slot_bytes + (size_t)q * G.p2_expert_bytes[sh];
                     // [group][row 0..15][group bytes]; scales and biases [scale|bias][row 0..15][group]
                     const uint8_t* rowA = eb + (size_t)g * Q::kGroupBytes + toff;
