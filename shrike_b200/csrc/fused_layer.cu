@@ -1059,7 +1059,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) decode_layer_kernel(const __
                             bool got = !has_sentinel(v);
 #pragma unroll 1
                             for (uint32_t tries = 0; !got && tries < (1u << 17); ++tries) {
-                                __nanosleep(tries > 32 ? 256 : 100);   // 148 blocks poll the same few lines
+                                __nanosleep(tries > 32 ? 512 : 300);   // 148 blocks poll the same few lines (measured: 100 and 600 ns are both slower)
                                 v = ld_relaxed_v4(src);
                                 got = !has_sentinel(v);
                             }
