@@ -69,6 +69,9 @@ constexpr uint32_t kSelWarps = 8;                    // consumer warps that take
 constexpr uint32_t kFusedThreads = (1 + kCW) * 32;   // + the producer warp (its lanes issue the copies)
 constexpr uint32_t kMaxUnits = 64;                   // units of one block
 constexpr uint32_t kSelectors = 2;                   // blocks that select and publish the instance list (measured: 1-3 best, 8 +0.3 us, all +2 us)
+constexpr uint32_t kRouteCopies = 1;                 // copies of the list each of them writes (measured: 4 and 8 change nothing)
+constexpr uint32_t kActCopies = 8;                   // copies of the published activations, block b polls copy b % 8
+                                                     // (measured: 1 copy +0.5 us, 4 to 16 alike, one per block +2.2 us)
 constexpr uint32_t kMaxInst = SHRIKE_MAX_TOP_K + 1;  // picks + shared expert
 constexpr uint32_t kMaxSlots = 16;
 constexpr uint32_t kMaxRouterRowsPerBlock = 2;
@@ -125,7 +128,7 @@ struct FusedArgs {
     uint32_t* out_slots;
     float* out_gate;
     unsigned long long* logits64;   // [ne + 1]: {epoch, logit bits}
-    uint16_t* acts_pub;             // [2][kMaxInst][acts_stride] halves, 0xFFFF = not yet written
+    uint16_t* acts_pub;             // [2][kActCopies][kMaxInst][acts_stride] halves, 0xFFFF = not yet written
     uint32_t* epoch;
     uint32_t* status;
 #ifdef SHRIKE_TRACE
@@ -756,7 +759,11 @@ __global__ void __launch_bounds__(kFusedThreads, 1) decode_layer_kernel(const __
     __syncthreads();
     const uint32_t epoch = st.epoch;
     const uint32_t parity = epoch & 1u;
-    uint16_t* acts_mine = a.acts_pub + (size_t)parity * kMaxInst * G.acts_stride;
+    // the published activations exist in a few copies, so that the polls of all the blocks do not meet on the
+    // same lines; whoever finishes a gate/up unit writes the unit's 16 bytes into every copy
+    const size_t acts_copy = (size_t)kMaxInst * G.acts_stride;
+    uint16_t* acts_call = a.acts_pub + (size_t)parity * kActCopies * acts_copy;
+    uint16_t* acts_mine = acts_call + (size_t)(blockIdx.x % kActCopies) * acts_copy;
     uint4* route_pub = (uint4*)(a.logits64 + ((a.ne + 2u) & ~1u));   // [n_sel][1 + kMaxInst] 16-byte entries
 
     // ---- this block's router rows ----
@@ -798,8 +805,8 @@ __global__ void __launch_bounds__(kFusedThreads, 1) decode_layer_kernel(const __
         FUSED_TS(3);   // this block's logits are published
     }
     {   // the buffer the next call will use still holds the previous call's activations
-        uint4* other = (uint4*)(a.acts_pub + (size_t)(parity ^ 1u) * kMaxInst * G.acts_stride);
-        const uint32_t n16 = kMaxInst * G.acts_stride / 8;
+        uint4* other = (uint4*)(a.acts_pub + (size_t)(parity ^ 1u) * kActCopies * acts_copy);
+        const uint32_t n16 = kActCopies * kMaxInst * G.acts_stride / 8;
         const uint4 fill = make_uint4(0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu);
         for (uint32_t i = blockIdx.x * kFusedThreads + tid; i < n16; i += gridDim.x * kFusedThreads) other[i] = fill;
     }
@@ -878,15 +885,18 @@ __global__ void __launch_bounds__(kFusedThreads, 1) decode_layer_kernel(const __
                 }
                 __syncwarp();
                 // entry 0: the counts; entry 1 + i: instance i. Every 16-byte entry carries the epoch.
-                uint4* mine = route_pub + (size_t)(blockIdx.x - (gridDim.x - n_sel)) * (1u + kMaxInst);
-                if (lane == 0) st_relaxed_v4(mine, make_uint4(epoch, st.route.n_routed, st.route.n_inst, 0u));
-                else if (lane <= kMaxInst)
-                    st_relaxed_v4(mine + lane, make_uint4(epoch, st.route.cell[lane - 1], __float_as_uint(st.route.w[lane - 1]), 0u));
+                uint4* mine = route_pub + (size_t)(blockIdx.x - (gridDim.x - n_sel)) * kRouteCopies * (1u + kMaxInst);
+                if (lane <= kMaxInst) {
+                    const uint4 e = lane == 0 ? make_uint4(epoch, st.route.n_routed, st.route.n_inst, 0u)
+                                              : make_uint4(epoch, st.route.cell[lane - 1], __float_as_uint(st.route.w[lane - 1]), 0u);
+#pragma unroll
+                    for (uint32_t c = 0; c < kRouteCopies; ++c) st_relaxed_v4(mine + c * (1u + kMaxInst) + lane, e);
+                }
             }
         }
     } else if (is_producer) {
         if (lane <= kMaxInst) {
-            const uint4* src = route_pub + (size_t)(blockIdx.x % n_sel) * (1u + kMaxInst) + lane;
+            const uint4* src = route_pub + (size_t)(blockIdx.x % (n_sel * kRouteCopies)) * (1u + kMaxInst) + lane;
             uint4 v = make_uint4(0, 0, 0, 0);
             bool ok = false;
             for (uint32_t it = 0; it < (1u << 17); ++it) {
@@ -1018,9 +1028,10 @@ __global__ void __launch_bounds__(kFusedThreads, 1) decode_layer_kernel(const __
                 stg[perm_index(lane, BITS == 4)] = act_to_half_bits(act, a.status);
             }
             __syncwarp();
-            if (lane == 0) {
+            {
                 const uint4 pk = *(const uint4*)stg;
-                st_relaxed_v4(acts_mine + (size_t)u.inst() * G.acts_stride + u.r0, pk);
+                uint16_t* dst = acts_call + (size_t)u.inst() * G.acts_stride + u.r0;
+                if (lane < kActCopies) st_relaxed_v4(dst + (size_t)lane * acts_copy, pk);
             }
         }
         FUSED_TS(8);   // this warp's gate/up units done
@@ -1059,7 +1070,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) decode_layer_kernel(const __
                             bool got = !has_sentinel(v);
 #pragma unroll 1
                             for (uint32_t tries = 0; !got && tries < (1u << 17); ++tries) {
-                                __nanosleep(tries > 32 ? 512 : 300);   // 148 blocks poll the same few lines (measured: 100 and 600 ns are both slower)
+                                __nanosleep(tries > 32 ? 512 : 80);   // (measured with 8 copies: 300 ns +0.1 us, 150 ns +0.03 us)
                                 v = ld_relaxed_v4(src);
                                 got = !has_sentinel(v);
                             }
@@ -1330,10 +1341,10 @@ size_t fused_map_cache_bytes() { return sizeof(FusedMapCache); }
 size_t fused_geom_bytes() { return sizeof(FusedGeom); }
 // {epoch, logit} words of the experts and the gate row, then the selecting blocks' copies of the instance list
 size_t fused_logits_bytes(const shrike_moe_config& c) {
-    return (size_t)((c.num_experts + 2u) & ~1u) * 8 + (size_t)kSelectors * (1 + kMaxInst) * 16;
+    return (size_t)((c.num_experts + 2u) & ~1u) * 8 + (size_t)kSelectors * kRouteCopies * (1 + kMaxInst) * 16;
 }
 size_t fused_acts_bytes(const shrike_moe_config& c) {
-    return (size_t)2 * kMaxInst * std::max(c.f, c.has_shared ? c.shared_f : 0u) * 2;
+    return (size_t)2 * kActCopies * kMaxInst * std::max(c.f, c.has_shared ? c.shared_f : 0u) * 2;
 }
 
 template <int BITS, int GROUP, int META, bool PLAIN>
