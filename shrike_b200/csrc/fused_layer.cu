@@ -1199,6 +1199,19 @@ bool fused_geometry(const shrike_moe_config& c, int sm_count, int max_smem_optin
         g.p2_expert_bytes[sh] = g.p2_ab_off[sh] + 128;
         g.cg_p2[sh] = pick_cg(G2);
     }
+    {   // the sixteen consumer warps share a down tile's (expert, chunk) items: narrower chunks when they split
+        // more evenly (18 items of 4 groups are two rounds of 4; as 36 items of 2 they are three rounds of 2)
+        auto rounds = [&](uint32_t cap) {
+            uint32_t items = 0;
+            for (int sh = 0; sh < 2; ++sh) {
+                if (sh && !c.has_shared) continue;
+                const uint32_t G2 = (sh ? c.shared_f : c.f) / c.group_size, cg = std::min(g.cg_p2[sh], cap);
+                items += (sh ? 1u : c.top_k) * ((G2 + cg - 1) / cg);
+            }
+            return (items + kCW - 1) / kCW * cap;
+        };
+        if (g.cg_p2[0] == 4 && (!c.has_shared || g.cg_p2[1] == 4) && rounds(2) < rounds(4)) g.cg_p2[0] = g.cg_p2[1] = 2;
+    }
     // a routed pack holds as many experts as fit beside the larger of the other unit kinds
     uint32_t slot = std::max(g.p1_bytes, g.p2_expert_bytes[0]);
     if (c.has_shared) slot = std::max(slot, g.p2_expert_bytes[1]);
