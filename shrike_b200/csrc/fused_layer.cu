@@ -15,7 +15,7 @@
 // order) into a ring of shared-memory slots, each slot completing on an mbarrier. The consumers walk
 // the slots with the dequant-fused skinny tiles (packed words -> exact fp16 integers with one logic
 // op per register, mma.sync m16n8k16, fp32 accumulate, one fused multiply-add per group with the
-// scale and one with the zero-point bias): gate/up units by groups of four warps, a unit per group
+// scale and one with the zero-point bias): gate/up units by groups of eight warps, a unit per group
 // at a time; the down tile of a block by all sixteen warps, one meeting per tile. What a block does
 // is a closed form of its index (BlockPlan), so no warp walks a list to find its work.
 //
@@ -44,7 +44,7 @@
 // What bounds the kernel (measured with per-warp cycle stamps): not HBM. A warp of this code issues
 // an instruction every 5 to 10 cycles (dependent shared-memory loads, logic ops and tiles; four warps
 // share an issue port), so the serial chain router row -> gather -> rank -> publish -> read ->
-// request -> first bytes -> gate/up -> exchange -> down costs about 18 us at the Qwen shape, of which
+// request -> first bytes -> gate/up -> exchange -> down costs about 15 us at the Qwen shape, of which
 // the bytes need 2.4. Code that runs once per launch also pays for its instruction fetches (a body
 // beyond about 32 KB streams at 6 bytes a cycle), which is why the waits, the walkers and the tile
 // bodies are out of line and shared.
@@ -62,8 +62,9 @@ namespace shrike {
 
 namespace {
 
-constexpr uint32_t kGroups = 4;                      // consumer groups: each takes every fourth unit of the block
-constexpr uint32_t kGroupWarps = 4;                  // warps of a group: they split a unit's columns
+constexpr uint32_t kGroups = 2;                      // consumer groups: each takes every second gate/up unit of the block
+constexpr uint32_t kGroupWarps = 8;                  // warps of a group: they split a unit's columns (measured: 4 groups
+                                                     // of 4 warps +0.16 us, one group of 16 +1.2 us)
 constexpr uint32_t kCW = kGroups * kGroupWarps;      // consumer warps
 constexpr uint32_t kSelWarps = 8;                    // consumer warps that take part in the selection (32 experts each)
 constexpr uint32_t kFusedThreads = (1 + kCW) * 32;   // + the producer warp (its lanes issue the copies)
@@ -961,7 +962,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) decode_layer_kernel(const __
         }
     } else {
         // ================= consumers =================
-        // Gate/up units: groups of four warps, a unit per group at a time, its columns split among the warps.
+        // Gate/up units: groups of eight warps, a unit per group at a time, its columns split among the warps.
         // Down tiles: all consumer warps share a tile's (expert, column chunk) items and meet once per tile.
         const uint32_t g = lane >> 2, t = lane & 3;
         const uint32_t gi = cw / kGroupWarps, wi = cw % kGroupWarps;
@@ -1013,8 +1014,8 @@ __global__ void __launch_bounds__(kFusedThreads, 1) decode_layer_kernel(const __
                 red[wi * 16 + g + 8] = tot1;
             }
             group_sync(gi);
-            if (wi != (r & 3u)) continue;
-            // ---- this warp finishes the unit (the four warps take turns) while the others go on ----
+            if (wi != r % kGroupWarps) continue;
+            // ---- this warp finishes the unit (the group's warps take turns) while the others go on ----
             float v = 0.f;
             if (lane < 16) {
 #pragma unroll
@@ -1191,6 +1192,7 @@ bool fused_geometry(const shrike_moe_config& c, int sm_count, int max_smem_optin
     g.p1_bytes = g.p1_ab_off + 128;
     auto pick_cg = [](uint32_t groups) { return groups % 2 == 0 && groups >= 4 ? 4u : groups % 2 == 0 ? 2u : 1u; };
     g.cg_p1 = pick_cg(G1);
+    while (g.cg_p1 > 1 && G1 / g.cg_p1 < kGroupWarps) g.cg_p1 /= 2;   // a chunk for every warp of the group
     for (int sh = 0; sh < 2; ++sh) {
         const uint32_t F = sh ? (c.has_shared ? c.shared_f : c.f) : c.f;
         const uint32_t rb2 = F * c.weight_bits / 8, G2 = F / c.group_size;
