@@ -327,6 +327,118 @@ __global__ void __launch_bounds__(256, 1) router_logits_tiled_kernel(const Route
     }
 }
 
+// The same tile for 16-bit activations without a per-column scale (the common case): both operands go to
+// shared memory by cp.async, three stages deep, the activations as they are (half the bytes), and are widened
+// where they are multiplied -- exact, so the logits are unchanged. Thread t of a row's eight copies 16-byte
+// units t, t + 8, ...: a warp's copies land 128 bytes a row, free of bank conflicts. (The kernel above holds
+// the next stage's activations in registers across the multiply loop; the compiler sinks those loads to their
+// use, and a block of 8 warps then waits for L2 once per stage.)
+constexpr uint32_t kTile16WBytes = kTileRows * kTileStage * 4, kTile16XBytes = kTileTokens * kTileStage * 2;
+constexpr uint32_t kTile16Buf = kTile16WBytes + kTile16XBytes, kTile16Bufs = 3;
+constexpr size_t kTile16SmemBytes = (size_t)kTile16Bufs * kTile16Buf;
+
+template <bool FP16>
+__global__ void __launch_bounds__(256, 1) router_logits_tiled16_kernel(const RouterArgs a) {
+    extern __shared__ __align__(16) uint8_t tile16_smem[];
+    const uint32_t smem0 = (uint32_t)__cvta_generic_to_shared(tile16_smem);
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t e0 = blockIdx.x * kTileRows, t0 = blockIdx.y * kTileTokens;
+    const uint32_t chunks = a.d / 4, units = a.d / 8;   // float4 chunks of a weight row, 16-byte units of an activation row
+    const uint32_t stages = (a.d + kTileStage - 1) / kTileStage;
+    const uint32_t srow = tid >> 3, l8 = tid & 7;
+    const float* const wsrc = (const float*)a.w + (size_t)min(e0 + srow, a.ne - 1) * a.d;
+    const uint8_t* const xsrc = (const uint8_t*)a.hidden + (size_t)min(t0 + srow, a.T - 1) * a.stride * 2;
+
+    auto fetch = [&](uint32_t s, uint32_t buf) {
+        const uint32_t wdst = smem0 + buf * kTile16Buf + srow * (kTileStage * 4);
+#pragma unroll
+        for (uint32_t j = 0; j < 8; ++j) {
+            const uint32_t u = j * 8 + l8, c = s * (kTileStage / 4) + u;
+            cp_async_16_zfill(wdst + u * 16, wsrc + (size_t)min(c, chunks - 1) * 4, c < chunks);
+        }
+        const uint32_t xdst = smem0 + buf * kTile16Buf + kTile16WBytes + srow * (kTileStage * 2);
+#pragma unroll
+        for (uint32_t j = 0; j < 4; ++j) {
+            const uint32_t u = j * 8 + l8, c = s * (kTileStage / 8) + u;
+            cp_async_16_zfill(xdst + u * 16, xsrc + (size_t)min(c, units - 1) * 16, c < units);
+        }
+        cp_async_commit();
+    };
+
+    float acc[kTileWarpRows][kTileWarpTokens];
+#pragma unroll
+    for (int r = 0; r < kTileWarpRows; ++r)
+#pragma unroll
+        for (int t = 0; t < kTileWarpTokens; ++t) acc[r][t] = 0.f;
+
+    fetch(0, 0);
+    if (stages > 1) fetch(1, 1);
+    const uint32_t rg = warp & 3, tg = warp >> 2;
+    for (uint32_t s = 0; s < stages; ++s) {
+        const uint32_t buf = s % kTile16Bufs;
+        if (s + 1 < stages) cp_async_wait<1>();
+        else cp_async_wait<0>();
+        __syncthreads();   // stage s has landed for every thread, and every warp is done with stage s - 1
+        if (s + 2 < stages) fetch(s + 2, (s + 2) % kTile16Bufs);
+        const float4* const wb = (const float4*)(tile16_smem + (size_t)buf * kTile16Buf) + rg * kTileWarpRows * (kTileStage / 4);
+        const uint2* const xb = (const uint2*)(tile16_smem + (size_t)buf * kTile16Buf + kTile16WBytes) + tg * kTileWarpTokens * (kTileStage / 4);
+#pragma unroll
+        for (int ii = 0; ii < kTileStage / 128; ++ii) {
+            float4 wv[kTileWarpRows];
+#pragma unroll
+            for (int r = 0; r < kTileWarpRows; ++r) wv[r] = wb[r * (kTileStage / 4) + ii * 32 + lane];
+#pragma unroll
+            for (int t = 0; t < kTileWarpTokens; ++t) {
+                const uint2 q = xb[t * (kTileStage / 4) + ii * 32 + lane];
+                float4 xv;
+                if (FP16)
+                    xv = make_float4(f16_bits_to_f32(q.x & 0xffff), f16_bits_to_f32(q.x >> 16), f16_bits_to_f32(q.y & 0xffff),
+                                     f16_bits_to_f32(q.y >> 16));
+                else
+                    xv = make_float4(__uint_as_float(q.x << 16), __uint_as_float(q.x & 0xffff0000u), __uint_as_float(q.y << 16),
+                                     __uint_as_float(q.y & 0xffff0000u));
+#pragma unroll
+                for (int r = 0; r < kTileWarpRows; ++r) {
+                    float v = acc[r][t];
+                    v = __fmaf_rn(wv[r].x, xv.x, v);
+                    v = __fmaf_rn(wv[r].y, xv.y, v);
+                    v = __fmaf_rn(wv[r].z, xv.z, v);
+                    v = __fmaf_rn(wv[r].w, xv.w, v);
+                    acc[r][t] = v;
+                }
+            }
+        }
+    }
+
+    // butterfly, then lane 2t + (r / 4) stores the four logits (r & ~3 .. +3) of token t
+    float4 out = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int t = 0; t < kTileWarpTokens; ++t)
+#pragma unroll
+        for (int r = 0; r < kTileWarpRows; ++r) {
+            const float v = butterfly_sum(acc[r][t]);
+            if (lane == (uint32_t)(2 * t + r / 4)) {
+                if ((r & 3) == 0) out.x = v;
+                else if ((r & 3) == 1) out.y = v;
+                else if ((r & 3) == 2) out.z = v;
+                else out.w = v;
+            }
+        }
+    const uint32_t tok = t0 + tg * kTileWarpTokens + (lane >> 1);
+    const uint32_t e = e0 + rg * kTileWarpRows + (lane & 1) * 4;
+    if (tok < a.T) {
+        float* const dst = a.logits + (size_t)tok * a.ne + e;
+        if (e + 4 <= a.ne && (a.ne & 3u) == 0) {
+            *(float4*)dst = out;
+        } else {
+            if (e + 0 < a.ne) dst[0] = out.x;
+            if (e + 1 < a.ne) dst[1] = out.y;
+            if (e + 2 < a.ne) dst[2] = out.z;
+            if (e + 3 < a.ne) dst[3] = out.w;
+        }
+    }
+}
+
 // The shared expert's scalar gate for many rows (the tiled router covers the expert rows only): one
 // warp per row of activations at a time, the gate row held in registers, the same lane order, fused
 // multiply-adds and butterfly as everywhere else. grid ceil(T / 32), block 256: a warp takes 4 rows.
@@ -559,7 +671,22 @@ cudaError_t launch_router(const shrike_moe* m, cudaStream_t st, const shrike_rou
             attr_set[dev] = true;
         }
         const dim3 grid((a.ne + kTileRows - 1) / kTileRows, (T + kTileTokens - 1) / kTileTokens);
-        router_logits_tiled_kernel<<<grid, 256, kTileSmemBytes, st>>>(a);
+        if (a.dt != SHRIKE_DTYPE_FP32 && !a.eff_scale) {
+            static bool attr16_set[64] = {};
+            if (dev < 64 && !attr16_set[dev]) {
+                e = cudaFuncSetAttribute(router_logits_tiled16_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)kTile16SmemBytes);
+                if (e == cudaSuccess)
+                    e = cudaFuncSetAttribute(router_logits_tiled16_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)kTile16SmemBytes);
+                if (e != cudaSuccess) return e;
+                attr16_set[dev] = true;
+            }
+            if (a.dt == SHRIKE_DTYPE_FP16) router_logits_tiled16_kernel<true><<<grid, 256, kTile16SmemBytes, st>>>(a);
+            else router_logits_tiled16_kernel<false><<<grid, 256, kTile16SmemBytes, st>>>(a);
+        } else {
+            router_logits_tiled_kernel<<<grid, 256, kTileSmemBytes, st>>>(a);
+        }
         e = cudaGetLastError();
         if (e != cudaSuccess) return e;
         if (a.gate_row) {
