@@ -600,40 +600,52 @@ __global__ void __launch_bounds__(kRouterWarps * 32) route_fused_kernel(const Ro
     if (!fast) plan_body(sm, n_pairs, a.T, a.with_shared, a.inst, a.n_inst, a.sorted, a.max_inst, a.status);
 }
 
-// moe_classify_residency_body for T rows; one thread walks the pairs in order
-// so that the miss lists keep router order.
-__global__ void classify_kernel(const uint32_t* __restrict__ ids, const uint64_t* __restrict__ table,
-                                uint32_t n_pairs, uint32_t ne, uint32_t* __restrict__ slots,
-                                uint32_t* __restrict__ counts, uint32_t* __restrict__ miss_pos,
-                                uint32_t* __restrict__ miss_exp) {
+// moe_classify_residency_body for T rows. The miss lists keep router order: block b takes pairs
+// [1024 b, 1024 b + 1024) and first counts the misses of all the pairs before them itself (independent loads,
+// no hand-over between blocks), so its misses go to their final places.
+__global__ void __launch_bounds__(1024) classify_kernel(const uint32_t* __restrict__ ids, const uint64_t* __restrict__ table,
+                                                        uint32_t n_pairs, uint32_t ne, uint32_t* __restrict__ slots,
+                                                        uint32_t* __restrict__ counts, uint32_t* __restrict__ miss_pos,
+                                                        uint32_t* __restrict__ miss_exp) {
     __shared__ uint32_t s_miss[1024];
-    uint32_t base = 0;
-    for (uint32_t p0 = 0; p0 < n_pairs; p0 += blockDim.x) {
-        const uint32_t p = p0 + threadIdx.x;
-        bool miss = false;
-        uint32_t e = 0;
-        if (p < n_pairs) {
-            e = min(ids[p], ne - 1u);
-            const uint64_t word = table[e];
-            const uint32_t slot = (uint32_t)(word & 0xffffffffu), state = (uint32_t)(word >> 32);
-            const bool hit = state == 2u && slot != SHRIKE_SLOT_MISS;
-            slots[p] = hit ? slot : SHRIKE_SLOT_MISS;
-            miss = !hit;
-        }
-        s_miss[threadIdx.x] = miss ? 1u : 0u;
-        const uint32_t chunk = __syncthreads_count(miss);
-        if (miss && (miss_pos || miss_exp)) {
-            uint32_t before = 0;
-            for (uint32_t j = 0; j < threadIdx.x; ++j) before += s_miss[j];
-            if (miss_pos) miss_pos[base + before] = p;
-            if (miss_exp) miss_exp[base + before] = e;
-        }
-        base += chunk;
-        __syncthreads();
+    __shared__ uint32_t s_base;
+    auto lookup = [&](uint32_t p, uint32_t& e, uint32_t& slot) {
+        e = min(ids[p], ne - 1u);
+        const uint64_t word = table[e];
+        slot = (uint32_t)(word & 0xffffffffu);
+        return (uint32_t)(word >> 32) == 2u && slot != SHRIKE_SLOT_MISS;
+    };
+    if (threadIdx.x == 0) s_base = 0;
+    __syncthreads();
+    uint32_t before_me = 0;
+#pragma unroll 4
+    for (uint32_t j = 0; j < blockIdx.x; ++j) {
+        uint32_t e, slot;
+        before_me += lookup(j * 1024u + threadIdx.x, e, slot) ? 0u : 1u;
     }
-    if (threadIdx.x == 0 && counts) {
-        counts[0] = n_pairs - base;
-        counts[1] = base;
+    for (int o = 16; o; o >>= 1) before_me += __shfl_xor_sync(0xffffffffu, before_me, o);
+    if ((threadIdx.x & 31u) == 0 && before_me) atomicAdd(&s_base, before_me);
+    const uint32_t p = blockIdx.x * 1024u + threadIdx.x;
+    bool miss = false;
+    uint32_t e = 0;
+    if (p < n_pairs) {
+        uint32_t slot;
+        const bool hit = lookup(p, e, slot);
+        slots[p] = hit ? slot : SHRIKE_SLOT_MISS;
+        miss = !hit;
+    }
+    s_miss[threadIdx.x] = miss ? 1u : 0u;
+    const uint32_t chunk = __syncthreads_count(miss);
+    const uint32_t base = s_base;
+    if (miss && (miss_pos || miss_exp)) {
+        uint32_t before = 0;
+        for (uint32_t j = 0; j < threadIdx.x; ++j) before += s_miss[j];
+        if (miss_pos) miss_pos[base + before] = p;
+        if (miss_exp) miss_exp[base + before] = e;
+    }
+    if (threadIdx.x == 0 && counts && blockIdx.x == gridDim.x - 1) {
+        counts[0] = n_pairs - (base + chunk);
+        counts[1] = base + chunk;
     }
 }
 
@@ -738,8 +750,9 @@ cudaError_t launch_route_fused(const shrike_moe* m, cudaStream_t st, const shrik
 cudaError_t launch_classify(const shrike_moe* m, cudaStream_t st, const uint32_t* ids,
                             const uint64_t* table, uint32_t T, uint32_t* slots, uint32_t* counts,
                             uint32_t* miss_pos, uint32_t* miss_exp) {
-    classify_kernel<<<1, 1024, 0, st>>>(ids, table, T * m->cfg.top_k, m->cfg.num_experts, slots, counts,
-                                        miss_pos, miss_exp);
+    const uint32_t n_pairs = T * m->cfg.top_k;
+    classify_kernel<<<n_pairs > 1024u ? (n_pairs + 1023u) / 1024u : 1u, 1024, 0, st>>>(ids, table, n_pairs, m->cfg.num_experts, slots, counts,
+                                                                              miss_pos, miss_exp);
     return cudaGetLastError();
 }
 

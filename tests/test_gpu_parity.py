@@ -242,18 +242,20 @@ def test_router_strided_hidden_equals_dense(cuda_device):
     layer.close()
 
 
-def test_residency_classification_and_misses(cuda_device):
-    cfg = small_config()
-    layer = Layer(cfg)
+@pytest.mark.parametrize("T", [32, 700])
+def test_residency_classification_and_misses(cuda_device, T):
+    """T = 700: 2800 pairs, three blocks of the classification kernel, the miss lists still in router order."""
+    cfg = small_config(max_tokens=1024)
+    layer = Layer(cfg, router_sigma=0.05)
     layer.moe.residency_set(0, 3, 0, 1)            # expert 3: loading, not resident
     layer.moe.residency_set(0, 7, capi.SLOT_MISS, 2)
-    x = inputs(32, 128, seed=10)
+    x = inputs(T, 128, seed=10)
     x_dev = to_act_tensor(x, cfg.act_dtype, layer.device)
     ids, w, gate = layer.route(x_dev)
     slots = torch.empty_like(ids)
     counts = torch.zeros(2, dtype=torch.int32, device=layer.device)
-    miss_pos = torch.full((32 * 4,), -1, dtype=torch.int32, device=layer.device)
-    miss_exp = torch.full((32 * 4,), -1, dtype=torch.int32, device=layer.device)
+    miss_pos = torch.full((T * 4,), -1, dtype=torch.int32, device=layer.device)
+    miss_exp = torch.full((T * 4,), -1, dtype=torch.int32, device=layer.device)
     layer.moe.encode_residency_classification(ids, 0, slots, counts, miss_pos, miss_exp)
     layer.moe.status()
     ids_np = ids.cpu().numpy().astype(np.uint32)
@@ -261,21 +263,22 @@ def test_residency_classification_and_misses(cuda_device):
     table[3] = (1 << 32) | 0
     table[7] = (2 << 32) | 0xFFFFFFFF
     exp_slots, exp_pos, exp_exp = [], [], []
-    for t in range(32):
+    for t in range(T):
         s, misses, mp, me = O.classify_residency(ids_np[t], table, 16)
         exp_slots.append(s)
         exp_pos += [t * 4 + int(p) for p in mp]
         exp_exp += [int(e) for e in me]
     assert (slots.cpu().numpy().astype(np.uint32) == np.stack(exp_slots)).all()
     c = counts.cpu().numpy()
-    assert c[1] == len(exp_pos) and c[0] == 32 * 4 - len(exp_pos) and len(exp_pos) > 0
+    assert c[1] == len(exp_pos) and c[0] == T * 4 - len(exp_pos) and len(exp_pos) > 0
     assert list(miss_pos.cpu().numpy()[:c[1]]) == exp_pos and list(miss_exp.cpu().numpy()[:c[1]]) == exp_exp
-    # a missing expert contributes nothing: the oracle with those weights zeroed
-    y = torch.empty_like(x_dev)
-    layer.moe.encode_decode(layer.pool, layer.offsets, slots, w, x_dev, y, None, layer.shared, gate)
-    layer.moe.status()
-    y_ref = layer.oracle_forward(x, ids_np, w.cpu().numpy(), skip_experts={3, 7})
-    assert rel_l2(y.float().cpu().numpy(), y_ref) <= TOL
+    if T <= 64:   # (the decode call takes at most 64 rows)
+        # a missing expert contributes nothing: the oracle with those weights zeroed
+        y = torch.empty_like(x_dev)
+        layer.moe.encode_decode(layer.pool, layer.offsets, slots, w, x_dev, y, None, layer.shared, gate)
+        layer.moe.status()
+        y_ref = layer.oracle_forward(x, ids_np, w.cpu().numpy(), skip_experts={3, 7})
+        assert rel_l2(y.float().cpu().numpy(), y_ref) <= TOL
     layer.close()
 
 
