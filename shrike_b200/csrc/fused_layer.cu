@@ -69,7 +69,8 @@ constexpr uint32_t kCW = kGroups * kGroupWarps;      // consumer warps
 constexpr uint32_t kSelWarps = 8;                    // consumer warps that take part in the selection (32 experts each)
 constexpr uint32_t kFusedThreads = (1 + kCW) * 32;   // + the producer warp (its lanes issue the copies)
 constexpr uint32_t kMaxUnits = 64;                   // units of one block
-constexpr uint32_t kSelectors = 2;                   // blocks that select and publish the instance list (measured: 1-3 best, 8 +0.3 us, all +2 us)
+constexpr uint32_t kSelectors = 2;                   // blocks that select and publish the instance list (measured: 1-3 best, 8 +0.3 us, all +1.5 us;
+                                                     // all of them with the logits in 32 copies still +0.2 us)
 constexpr uint32_t kRouteCopies = 1;                 // copies of the list each of them writes (measured: 4 and 8 change nothing)
 constexpr uint32_t kActCopies = 8;                   // copies of the published activations, block b polls copy b % 8
                                                      // (measured: 1 copy +0.5 us, 4 to 16 alike, one per block +2.2 us)
@@ -136,7 +137,6 @@ struct FusedArgs {
     uint64_t* trace;   // debug builds: 16 timestamps per block
 #endif
     uint32_t rcp_cpc;               // ceil(2^32 / cells_per_chunk): cell / cells_per_chunk = mulhi(cell, rcp_cpc)
-    uint32_t n_pool_chunks;
     FusedGeom g;
     FusedMaps maps;
 };
@@ -465,12 +465,6 @@ __device__ __noinline__ float2 group_sums(const uint16_t* row, uint32_t grp) {
 #define FUSED_TS(slot) do { } while (0)
 #endif
 
-// Asks the TMA unit to fetch a descriptor ahead of its first use (a first use otherwise waits for the fetch:
-// a block whose experts sit in eight pool chunks met a different descriptor with almost every copy).
-__device__ __forceinline__ void prefetch_map(const CUtensorMap* map) {
-    asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
-}
-
 // Tiled TMA loads (no multicast): the box lands densely, innermost dimension first.
 __device__ __forceinline__ void tma_4d(uint32_t dst, const CUtensorMap* map, int32_t c0, int32_t c1, int32_t c2, int32_t c3,
                                        uint64_t* bar) {
@@ -589,6 +583,8 @@ __global__ void __launch_bounds__(kFusedThreads, 1) decode_layer_kernel(const __
     plan.init(a);
 
     // ---- before the previous kernel in the stream is known to be complete: nothing that it produces ----
+    // (Measured: the dependency wait and the row's load moved up here, ahead of this set-up, +0.5 us -- the wait
+    // returns only some time after the previous kernel's last block has left, and the set-up fills that time.)
     if (tid < G.n_slots) {
         mbar_init(&st.full[tid], 1);
         mbar_init(&st.empty[tid], kGroupWarps);
@@ -596,13 +592,8 @@ __global__ void __launch_bounds__(kFusedThreads, 1) decode_layer_kernel(const __
     if (tid == 32) { mbar_init(&st.rw_bar, 1); mbar_init(&st.tab_bar, 1); }
     if (tid <= 32) fence_mbar_init();
     if (tid == 0) st.failed = 0;
-    {   // the descriptors this block may use: the shared expert's, and every pool chunk's
-        const uint32_t n_chunks = a.n_pool_chunks;
-        const uint32_t which = tid >> 2, kind = tid & 3;
-        const bool wanted = which < n_chunks || (which == SHRIKE_MAX_POOL_CHUNKS && a.shared_block);
-        if (tid < 4 * (SHRIKE_MAX_POOL_CHUNKS + 1) && wanted)
-            prefetch_map(kind == 0 ? &a.maps.w1[which] : kind == 1 ? &a.maps.m1[which] : kind == 2 ? &a.maps.w2[which] : &a.maps.m2[which]);
-    }
+    // (No prefetch.tensormap of the descriptors here: measured, it holds the prologue back by 0.6 us -- the
+    // first copy through a descriptor fetches it just as well.)
     const uint32_t router_rows = a.ne + (a.gate_row ? 1u : 0u);
     const uint32_t my_row = blockIdx.x + cw * gridDim.x;
     const bool routes = !is_producer && cw < G.router_rows_per_block && my_row < router_rows;
@@ -1419,7 +1410,6 @@ cudaError_t launch_fused_layer(const shrike_moe* m, cudaStream_t st, const Exper
         const uint64_t cpc = ea.pool.cells_per_chunk ? ea.pool.cells_per_chunk : 1;
         if (cpc < 2 || (uint64_t)ea.pool.cells * cpc >= (1ull << 32)) return cudaErrorNotSupported;   // (the three launches)
         a.rcp_cpc = (uint32_t)(((1ull << 32) + cpc - 1) / cpc);
-        a.n_pool_chunks = (uint32_t)((ea.pool.cells + cpc - 1) / cpc);
     }
     a.d = c.d; a.f = c.f; a.f_shared = c.has_shared ? c.shared_f : 0; a.top_k = c.top_k;
     a.activation = c.activation; a.expert_bias = c.expert_bias; a.act_dtype = c.act_dtype; a.y_dtype = c.y_dtype;
