@@ -35,16 +35,18 @@
 //            publish the instance list as 16-byte entries that each carry the epoch; every other
 //            block's producer warp reads one of the two copies;
 //   acts     a gate/up unit (8 gate rows + 8 up rows of one expert) publishes its 8 fp16
-//            activations as 16 bytes whose halves are never the sentinel 0xFFFF; the blocks that
-//            own a tile of output rows poll until no half is the sentinel. The buffer of the
-//            previous call (other parity of the epoch) is reset by this call.
+//            activations as 16 bytes whose halves are never the sentinel 0xFFFF, into each of a few
+//            copies of the buffer (block b reads copy b mod kActCopies: polls of many blocks on the
+//            same lines slow the writes to them); in a block that owns a tile of output rows every
+//            warp polls just the words its own items multiply until no half is the sentinel. The
+//            buffer of the previous call (other parity of the epoch) is reset by this call.
 // Every wait -- mbarrier or global poll -- is bounded: it gives up, reports through the status
 // word and the block runs on to its end.
 //
 // What bounds the kernel (measured with per-warp cycle stamps): not HBM. A warp of this code issues
 // an instruction every 5 to 10 cycles (dependent shared-memory loads, logic ops and tiles; four warps
 // share an issue port), so the serial chain router row -> gather -> rank -> publish -> read ->
-// request -> first bytes -> gate/up -> exchange -> down costs about 15 us at the Qwen shape, of which
+// request -> first bytes -> gate/up -> exchange -> down costs about 14 us at the Qwen shape, of which
 // the bytes need 2.4. Code that runs once per launch also pays for its instruction fetches (a body
 // beyond about 32 KB streams at 6 bytes a cycle), which is why the waits, the walkers and the tile
 // bodies are out of line and shared.
