@@ -638,17 +638,19 @@ chunk_instances_kernel(const uint32_t* __restrict__ offsets, const uint32_t* __r
         total += warp_sums[w];
         total_rows += warp_rows[w];
     }
-    base += inc - n;
+    // The shared expert's instances come first in the list: they are full (256 rows), and the blocks of the
+    // list's end are the last to start -- a launch that ends on its longest blocks ends late.
+    const uint32_t n_shared = with_shared ? (T + kUmmaMaxN - 1) / kUmmaMaxN : 0;
+    base += inc - n + n_shared;
     for (uint32_t j = 0; j < n; ++j) {
         ChunkInstance in;
         in.kind = 0; in.slot = slot; in.first = offsets[e] + kUmmaMaxN * j; in.count = min(kUmmaMaxN, c - kUmmaMaxN * j);
         inst[base + j] = in;
     }
-    const uint32_t n_shared = with_shared ? (T + kUmmaMaxN - 1) / kUmmaMaxN : 0;
     for (uint32_t j = threadIdx.x; j < n_shared; j += blockDim.x) {
         ChunkInstance in;
         in.kind = 1; in.slot = 0; in.first = kUmmaMaxN * j; in.count = min(kUmmaMaxN, T - kUmmaMaxN * j);
-        inst[total + j] = in;
+        inst[j] = in;
     }
     if (threadIdx.x == 0) {
         n_inst[0] = total + n_shared;
