@@ -30,7 +30,10 @@ struct QT {
     static constexpr int kWords = GROUP * BITS / 128;  // u32 per thread, row and group
     static constexpr int kMmas = GROUP / 16;           // k16 steps per group
     static constexpr int kBRegs = GROUP / 8;           // u32 of activations per thread and group
-    static constexpr int kBatch = 8 / kWords;          // groups whose weights are in flight together
+    // groups whose weights a thread has in flight together: 16 bytes per row. (Measured at 4 and 16 rows of the
+    // Qwen shape: 32 bytes per row cost 125 registers and two gate/up blocks per SM; with 16 the kernel takes 80,
+    // three blocks fit, and a layer is 3 to 6 % faster -- these kernels wait on latencies, not on bytes in flight.)
+    static constexpr int kBatch = kWords >= 4 ? 1 : 4 / kWords;
     // The tiles multiply (1024 + q): sum((1024 + q) x) = 1024 sum(x) + sum(q x), so a group contributes
     // scale * c + (bias - 1024 * scale) * sum(x); products and sums stay exact in fp32 (|c| < 2^24 * ulp).
     static constexpr float kOffset = -1024.0f;
@@ -225,7 +228,7 @@ __device__ __forceinline__ uint32_t pick(const uint32_t (&v)[8], uint32_t i) {
 // grid (max(f, f_shared)/16, max instances); block 256. The eight warps split
 // K by groups (warp w takes groups w, w+8, ...).
 template <int BITS, int GROUP, int META>
-__global__ void __launch_bounds__(kP1Warps * 32) phase1_kernel(const ExpertArgs a) {
+__global__ void __launch_bounds__(kP1Warps * 32, 3) phase1_kernel(const ExpertArgs a) {
     using Q = QT<BITS, GROUP>;
     extern __shared__ __align__(16) uint8_t smem[];
     const uint32_t ii = blockIdx.y;
